@@ -1,0 +1,183 @@
+/*
+ * b200moe -- C ABI of the B200 (sm_100a) MoE grouped-FP8-GEMM hot path.
+ *
+ * Plain C: device pointers, sizes and strides only.  Every entry point returns
+ * 0 on success and a negative code on failure; moe_last_error() then holds a
+ * message for the calling thread.  All launches go to the stream passed in
+ * (a cudaStream_t cast to void*, NULL = the legacy default stream) on the
+ * CURRENT device of the calling thread, which must own the pointers.
+ *
+ * Citations name the interface of mlc-ai/TIRx-harness each entry point stands
+ * in for (paths inside that project).
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)   /* the library is built with hidden visibility */
+#endif
+
+#define MOE_OK 0
+#define MOE_ERR_INVALID (-1)   /* bad argument (shape, alignment, null pointer) */
+#define MOE_ERR_CUDA (-2)      /* a CUDA runtime / driver call failed */
+#define MOE_ERR_DEVICE (-3)    /* a kernel reported a device-side error (bounded wait ran out) */
+#define MOE_ERR_UNSUPPORTED (-4)
+
+#define MOE_DTYPE_BF16 0
+#define MOE_DTYPE_F32 1
+
+/* Arguments of the m-grouped FP8 block-scaled GEMM  D_g = deq(A_g) * deq(B_g)^T.
+ *   a       e4m3, K-major.  contiguous: [M, K];  masked: [G, M, K] with M = max rows per group
+ *   b       e4m3 [G, N, K], K-major
+ *   sfa     fp32, one scale per (row, 128-wide K block); element (row r, block kb) is
+ *           sfa[r * sfa_stride_row + kb * sfa_stride_kblk]   (masked: r = g * M + row)
+ *           -> row-major [rows, K/128] is (K/128, 1); MN-major [K/128, rows] is (1, rows)
+ *   sfb     fp32 [G, ceil(N/128), K/128] row major: one scale per 128x128 block of B_g
+ *   layout  contiguous: grouped_layout int32[M], group id per row, negative = padding row
+ *           masked:     masked_m int32[G], number of valid rows of each group
+ *   d       contiguous [M, N] / masked [G, M, N]; row stride ldd elements; bf16 (d_dtype =
+ *           MOE_DTYPE_BF16, the workload's output type) or the unrounded fp32 accumulator
+ *           (MOE_DTYPE_F32).  Only valid rows are written; padding / masked-out rows are left
+ *           untouched.
+ * Requirements: K % 128 == 0, N % 8 == 0, a/b 16-byte aligned, d 16-byte aligned, ldd % 8 == 0.
+ */
+typedef struct moe_gg_args {
+    const void* a;
+    const void* b;
+    const float* sfa;
+    int64_t sfa_stride_row;
+    int64_t sfa_stride_kblk;
+    const float* sfb;
+    const int32_t* layout;
+    void* d;
+    int64_t ldd;
+    int32_t G, M, N, K;
+    int32_t d_dtype;
+} moe_gg_args;
+
+/* Contiguous layout.  Stands in for the timed call of the registered workload
+ * `grouped_gemm/fp8`: DeepGEMM m_grouped_fp8_gemm_nt_contiguous as launched by
+ * evolution/benchmark/flashinfer_bench_evolve/tasks/grouped_gemm_fp8/baseline.py:30-42, with the
+ * tensor contract of evolution/tasks/grouped_gemm_fp8.yaml:15-25. */
+int moe_gg_fp8_contiguous(const moe_gg_args* args, void* stream);
+
+/* Masked layout.  Stands in for the masked grouped kernel exercised by
+ * tools/tests/numsim/corpus/kernels/gemm.py:705-795 (deepgemm_sm100_m_grouped_fp8_gemm_masked). */
+int moe_gg_fp8_masked(const moe_gg_args* args, void* stream);
+
+
+/* ---- memory-bound stages around the GEMMs ------------------------------------------------- */
+
+/* Per-token 1x128 activation quantisation: s = max(amax,1e-8)/448, q = e4m3(clamp(x/s, +-448)),
+ * true division.  x bf16 [rows, cols] -> q e4m3 [rows, cols], scale (r, block b) stored at
+ * scales[r*ss_row + b*ss_blk].  Stands in for alphamoe/baseline.py:14-26 (`_quantize`) and the
+ * rule `_quantize_per_token_group` of tasks/alphamoe/definition.json. */
+int moe_quant_1x128(const void* x_bf16, void* q, float* scales, int64_t ss_row, int64_t ss_blk,
+                    int32_t rows, int32_t cols, void* stream);
+
+/* Fused SiLU(gate)*up + 1x128 FP8 requantisation between the gate_up and down GEMMs.
+ * gate_up bf16 [rows, 2*inter]; gate_first != 0: gate = columns [0, inter) (alphamoe/definition.json
+ * `_reference_quantized`), else gate = [inter, 2*inter) (moe/definition.json: silu(G1[:, I:]) * G1[:, :I]).
+ * layout (nullable): rows with a negative entry are skipped.  q e4m3 [rows, inter]. */
+int moe_silu_mul_requant(const void* gate_up_bf16, void* q, float* scales, int64_t ss_row, int64_t ss_blk,
+                         const int32_t* layout, int32_t rows, int32_t inter, int32_t gate_first, void* stream);
+
+/* Softmax-of-logits top-k routing (ties -> lowest expert index; weights = selected probabilities
+ * renormalised to sum 1; ids in descending score order).  logits f32 [T, E], E <= 512, top_k <= 32.
+ * The routing rule of the MoE-layer workload; takes the place of the routing block inside
+ * trtllm_fp8_block_scale_moe as called at tasks/moe/baseline.py:31-51. */
+int moe_route_topk(const float* logits, int32_t* ids, float* weights, int32_t T, int32_t E, int32_t top_k,
+                   void* stream);
+
+/* Stable permutation plan into the contiguous grouped layout for local experts
+ * [e_lo, e_lo + E_local): counts[E_local], offsets[E_local+1] (each expert padded to `align` rows,
+ * offsets[E_local] = rows in use), pos[n_pairs] (destination row of pair p = t*top_k + j, -1 if
+ * not local), src_pair[cap_rows] (pair stored in a row, -1 on padding) and
+ * grouped_layout[cap_rows] (local expert id, -1 on padding).  Pairs keep their order inside an
+ * expert.  cap_rows >= n_pairs rounded up to align + E_local*align always suffices.
+ * Replaces the permute stage inside trtllm_fp8_block_scale_moe (tasks/moe/baseline.py:31-51);
+ * the counts equal bincount(routes) as the reference checks for its receive counters
+ * (tools/tests/numsim/corpus/kernels/deepgemm.py:1444-1491). */
+size_t moe_permute_workspace_bytes(int64_t n_pairs, int32_t E_local);
+int moe_permute_plan(const int32_t* ids, int64_t n_pairs, int32_t e_lo, int32_t E_local, int32_t align,
+                     int32_t cap_rows, int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_pair,
+                     int32_t* grouped_layout, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Row gather: for each row with src_pair >= 0 copies token (src_pair / top_k)'s e4m3 row (H bytes)
+ * and its H/128 scales.  Source scale (t, b) at x_scale[t*xs_row + b*xs_blk]; destination
+ * (row, b) at a_scale[row*as_row + b*as_blk]. */
+int moe_permute(const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk, const int32_t* src_pair,
+                int32_t top_k, void* a, float* a_scale, int64_t as_row, int64_t as_blk, int32_t rows, int32_t H,
+                void* stream);
+
+/* Weighted combine: out[t,:] = bf16( sum_j w[t,j] * y[pos[t,j],:] ), fp32 multiply-then-add in
+ * slot order, pos < 0 skipped: the fp32 weighted accumulation of tasks/moe/definition.json
+ * (output.index_add_(0, token_idx, O * w_tok) ... .to(bfloat16)). */
+int moe_combine(const void* y_bf16, const int32_t* pos, const float* w, void* out_bf16, int32_t T, int32_t top_k,
+                int32_t H, void* stream);
+
+/* ---- one MoE layer on one GPU --------------------------------------------------------------- */
+
+/* route -> plan -> gather -> gate_up grouped GEMM -> SiLU*mul requant -> down grouped GEMM ->
+ * combine, all on `stream`, using caller-provided workspace (moe_workspace_bytes).  Mirrors the
+ * candidate contract of the registered `moe` workload (tasks/moe/benchmark.py:143-182:
+ * setup(data, T) -> callable writing the preallocated bf16 output).
+ *   x_q e4m3 [T,H], x_scale f32 at [t*xs_stride_row + b*xs_stride_blk]
+ *   logits f32 [T, E_global] (softmax top-k routing) or, if NULL, topk_ids/topk_weights [T, top_k]
+ *   w13 e4m3 [E, 2I, H], w13_scale f32 [E, 2I/128, H/128]; w2 e4m3 [E, H, I], w2_scale f32 [E, H/128, I/128]
+ *   E local experts = global ids [e_lo, e_lo+E); out bf16 [T, H] */
+typedef struct moe_layer_args {
+    const void* x_q;
+    const float* x_scale;
+    int64_t xs_stride_row, xs_stride_blk;
+    const float* logits;
+    const int32_t* topk_ids;
+    const float* topk_weights;
+    const void* w13;
+    const float* w13_scale;
+    const void* w2;
+    const float* w2_scale;
+    void* out;
+    void* workspace;
+    uint64_t workspace_bytes;
+    int32_t T, H, I, E, E_global, e_lo, top_k, align, gate_first;
+} moe_layer_args;
+
+size_t moe_workspace_bytes(int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k, int32_t align);
+int moe_layer_forward(const moe_layer_args* args, void* stream);
+
+/* Where moe_layer_forward keeps its intermediates inside the workspace (for inspection / tests). */
+typedef struct moe_layer_view {
+    int32_t *ids, *counts, *offsets, *pos, *src_pair, *grouped_layout;
+    float *weights, *s1, *s2;
+    void *a1, *g1, *a2, *y;
+    int64_t cap_rows;
+} moe_layer_view;
+int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k,
+                             int32_t align, moe_layer_view* view);
+
+/* Reads (and clears) the device-side status word of the current device; synchronises the
+ * stream first.  0 = no kernel reported a problem.  Non-zero: a bounded wait inside a kernel ran
+ * out (value encodes which) -- the failure surface that replaces a hang; the reference reports
+ * failures as Python exceptions (benchmark_common.py:1013-1020), the host wrapper raises. */
+int moe_device_status(int32_t* status_out, void* stream);
+
+/* Message describing the last failure on the calling thread ("" if none). */
+const char* moe_last_error(void);
+
+/* Library / build description, e.g. "b200moe 0.1 sm_100a". */
+const char* moe_version(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -303,8 +303,8 @@ ORC_API int orc_gg_contiguous(const uint8_t* A, const uint8_t* B, const float* s
  * strides (group, row, K-block). */
 ORC_API int orc_gg_masked(const uint8_t* A, const uint8_t* B, const float* sfa, int64_t sfa_sg,
                           int64_t sfa_sr, int64_t sfa_sk, const float* sfb,
-                          const int32_t* masked_m, uint16_t* D, int64_t G, int64_t max_m,
-                          int64_t N, int64_t K, int model) {
+                          const int32_t* masked_m, void* D, int64_t G, int64_t max_m,
+                          int64_t N, int64_t K, int model, int out_f32) {
     if (K % 128 != 0) return -1;
     const int64_t KB = K / 128, NB = (N + 127) / 128;
     float* bt = (float*)malloc(sizeof(float) * (size_t)K * (size_t)N);
@@ -316,7 +316,7 @@ ORC_API int orc_gg_masked(const uint8_t* A, const uint8_t* B, const float* sfa, 
         const float* sfb_g = sfb + g * NB * KB;
         decode_bt(B + g * N * K, sfb_g, KB, 1, bt, N, K, model == ORC_MODEL_SIM_CHAIN);
         gemm_rows(A + g * max_m * K, sfa + g * sfa_sg, sfa_sr, sfa_sk, bt, sfb_g, KB, 1, NULL,
-                  D + g * max_m * N, N, rows, N, K, model, 0);
+                  (char*)D + (size_t)g * max_m * N * (out_f32 ? 4 : 2), N, rows, N, K, model, out_f32);
     }
     free(bt);
     return 0;

@@ -151,7 +151,7 @@ def gg_contiguous(A, B, sfa, sfb, grouped_layout, model=SIM_CHAIN, out=None, row
     return D
 
 
-def gg_masked(A, B, sfa, sfb, masked_m, model=SIM_CHAIN, out=None):
+def gg_masked(A, B, sfa, sfb, masked_m, model=SIM_CHAIN, out=None, out_f32=False):
     """A u8[G,max_m,K], B u8[G,N,K], sfa f32[G,max_m,K/128] (any strides), sfb f32[G,N/128,K/128],
     masked_m i32[G] -> D bf16 bits [G,max_m,N] (rows >= masked_m[g] untouched)."""
     A = _c_arr(A, np.uint8)
@@ -162,10 +162,12 @@ def gg_masked(A, B, sfa, sfb, masked_m, model=SIM_CHAIN, out=None):
     G, max_m, K = A.shape
     N = B.shape[1]
     assert sfa.shape == (G, max_m, K // 128)
-    D = np.zeros((G, max_m, N), np.uint16) if out is None else out
+    D = np.zeros((G, max_m, N), np.float32 if out_f32 else np.uint16) if out is None else out
+    assert D.dtype == (np.float32 if out_f32 else np.uint16) and D.flags.c_contiguous
     sg, sr, sk = _strides_elems(sfa)
     rc = lib().orc_gg_masked(_p(A), _p(B), _p(sfa), _i64(sg), _i64(sr), _i64(sk), _p(sfb), _p(mm),
-                             _p(D), _i64(G), _i64(max_m), _i64(N), _i64(K), _c.c_int(model))
+                             _p(D), _i64(G), _i64(max_m), _i64(N), _i64(K), _c.c_int(model),
+                             _c.c_int(1 if out_f32 else 0))
     if rc != 0:
         raise ValueError(f"orc_gg_masked failed: {rc}")
     return D

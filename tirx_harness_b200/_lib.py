@@ -1,0 +1,84 @@
+"""ctypes binding of the C ABI in ``include/b200moe.h``.
+
+There is no fallback: if the CUDA library has not been built the import of any operator fails
+with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200moe.so")
+
+_c = ctypes
+
+
+class GGArgs(_c.Structure):
+    """``moe_gg_args`` of include/b200moe.h."""
+    _fields_ = [
+        ("a", _c.c_void_p), ("b", _c.c_void_p), ("sfa", _c.c_void_p),
+        ("sfa_stride_row", _c.c_int64), ("sfa_stride_kblk", _c.c_int64),
+        ("sfb", _c.c_void_p), ("layout", _c.c_void_p), ("d", _c.c_void_p), ("ldd", _c.c_int64),
+        ("G", _c.c_int32), ("M", _c.c_int32), ("N", _c.c_int32), ("K", _c.c_int32),
+        ("d_dtype", _c.c_int32),
+    ]
+
+
+class LayerArgs(_c.Structure):
+    """``moe_layer_args`` of include/b200moe.h."""
+    _fields_ = [
+        ("x_q", _c.c_void_p), ("x_scale", _c.c_void_p), ("xs_stride_row", _c.c_int64), ("xs_stride_blk", _c.c_int64),
+        ("logits", _c.c_void_p), ("topk_ids", _c.c_void_p), ("topk_weights", _c.c_void_p),
+        ("w13", _c.c_void_p), ("w13_scale", _c.c_void_p), ("w2", _c.c_void_p), ("w2_scale", _c.c_void_p),
+        ("out", _c.c_void_p), ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
+        ("T", _c.c_int32), ("H", _c.c_int32), ("I", _c.c_int32), ("E", _c.c_int32), ("E_global", _c.c_int32),
+        ("e_lo", _c.c_int32), ("top_k", _c.c_int32), ("align", _c.c_int32), ("gate_first", _c.c_int32),
+    ]
+
+
+class LayerView(_c.Structure):
+    """``moe_layer_view`` of include/b200moe.h."""
+    _fields_ = [(n, _c.c_void_p) for n in ("ids", "counts", "offsets", "pos", "src_pair", "grouped_layout",
+                                           "weights", "s1", "s2", "a1", "g1", "a2", "y")] + [("cap_rows", _c.c_int64)]
+
+
+class B200MoeError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200MoeError(
+                f"{LIB_PATH} is missing: build it with `python -m tirx_harness_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.moe_last_error.restype = _c.c_char_p
+        _lib.moe_version.restype = _c.c_char_p
+        for name in EXPORTS:
+            fn = getattr(_lib, name)      # raises AttributeError if the symbol is absent
+            if name in _SIZE_T_RETURN:
+                fn.restype = _c.c_size_t
+            elif name not in ("moe_last_error", "moe_version"):
+                fn.restype = _c.c_int
+    return _lib
+
+
+# every symbol include/b200moe.h declares
+EXPORTS = (
+    "moe_gg_fp8_contiguous", "moe_gg_fp8_masked", "moe_quant_1x128", "moe_silu_mul_requant",
+    "moe_route_topk", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute", "moe_combine",
+    "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
+    "moe_last_error", "moe_version",
+)
+_SIZE_T_RETURN = ("moe_permute_workspace_bytes", "moe_workspace_bytes")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise B200MoeError(f"b200moe error {rc}: {lib().moe_last_error().decode()}")

@@ -1,0 +1,411 @@
+// Host side of the C ABI declared in include/b200moe.h: argument validation, TMA descriptor
+// encoding, kernel launches and error reporting.  No torch types, no allocation on the GEMM path.
+#include "b200moe.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "gg_fp8.cuh"
+#include "moe_ops.cuh"
+
+namespace {
+
+using namespace b200;
+
+// Device status word: kernels OR a code into it when a bounded wait runs out.
+__device__ int g_status_word = 0;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                       \
+    do {                                                                                     \
+        cudaError_t e_ = (expr);                                                             \
+        if (e_ != cudaSuccess)                                                               \
+            return fail(MOE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                                                 \
+    } while (0)
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library carries no link-time
+// dependency on libcuda (it must load on machines without a driver, e.g. for symbol checks).
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    });
+    return fn;
+}
+
+// 2-D K-major e4m3 matrix [rows, K]; box = box_rows x 128 bytes, SWIZZLE_128B, OOB reads give 0.
+int encode_fp8_kmajor(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    auto fn = get_encode_fn();
+    if (!fn) return fail(MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return MOE_OK;
+}
+
+struct DeviceInfo {
+    int num_sms = 0;
+    bool attr_set = false;
+};
+
+int device_info(DeviceInfo** out) {
+    static DeviceInfo infos[64];
+    static std::mutex mu;
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MOE_ERR_INVALID, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo& di = infos[dev];
+    if (!di.attr_set) {
+        cudaDeviceProp prop;
+        CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major != 10)
+            return fail(MOE_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library needs sm_100a (B200)", dev,
+                        prop.major, prop.minor);
+        di.num_sms = prop.multiProcessorCount;
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg::SMEM_BYTES));
+        di.attr_set = true;
+    }
+    *out = &di;
+    return MOE_OK;
+}
+
+int* status_ptr() {
+    int* p = nullptr;
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word);
+    return p;
+}
+
+template <bool MASKED>
+int launch_gg(const moe_gg_args* a, void* stream) {
+    if (!a) return fail(MOE_ERR_INVALID, "args is NULL");
+    if (a->M == 0 && a->G > 0 && a->N > 0 && a->K > 0) return MOE_OK;      // nothing to compute
+    if (!a->a || !a->b || !a->sfa || !a->sfb || !a->layout || !a->d)
+        return fail(MOE_ERR_INVALID, "a, b, sfa, sfb, layout and d must all be non-NULL");
+    if (a->G <= 0 || a->N <= 0 || a->K <= 0 || a->M < 0)
+        return fail(MOE_ERR_INVALID, "G, N, K must be positive and M non-negative (G=%d M=%d N=%d K=%d)", a->G,
+                    a->M, a->N, a->K);
+    if (a->K % 128 != 0) return fail(MOE_ERR_INVALID, "K=%d must be a multiple of 128", a->K);
+    if (a->N % 8 != 0) return fail(MOE_ERR_INVALID, "N=%d must be a multiple of 8", a->N);
+    if (a->d_dtype != MOE_DTYPE_BF16 && a->d_dtype != MOE_DTYPE_F32)
+        return fail(MOE_ERR_INVALID, "d_dtype must be MOE_DTYPE_BF16 or MOE_DTYPE_F32");
+    if (a->ldd < a->N || a->ldd % 8 != 0) return fail(MOE_ERR_INVALID, "ldd=%lld must be >= N and a multiple of 8", (long long)a->ldd);
+    if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->b) & 15) ||
+        (reinterpret_cast<uintptr_t>(a->d) & 15))
+        return fail(MOE_ERR_INVALID, "a, b and d must be 16-byte aligned");
+    if (MASKED && a->G > gg::MAX_MASKED_GROUPS)
+        return fail(MOE_ERR_INVALID, "masked layout supports at most %d groups", gg::MAX_MASKED_GROUPS);
+    const long long rows_total = MASKED ? (long long)a->G * a->M : (long long)a->M;
+    if (rows_total > 0x7FFFFFFFll || (long long)a->G * a->N > 0x7FFFFFFFll)
+        return fail(MOE_ERR_INVALID, "row counts exceed 2^31-1");
+    if (rows_total == 0) return MOE_OK;
+
+    DeviceInfo* di = nullptr;
+    int rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
+
+    CUtensorMap tmap_a, tmap_b;
+    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::BM);
+    if (rc != MOE_OK) return rc;
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, gg::BN);
+    if (rc != MOE_OK) return rc;
+
+    GGParams p;
+    p.sfa = a->sfa;
+    p.sfa_sr = a->sfa_stride_row;
+    p.sfa_sk = a->sfa_stride_kblk;
+    p.sfb = a->sfb;
+    p.layout = a->layout;
+    p.d = a->d;
+    p.ldd = a->ldd;
+    p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
+    p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
+    p.rows_total = (int)rows_total;
+    p.num_n_blocks = (a->N + gg::BN - 1) / gg::BN;
+    p.num_k_blocks = a->K / 128;
+    p.nb128 = (a->N + 127) / 128;
+    p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
+
+    long long max_tiles = MASKED ? (long long)a->G * p.num_m_blocks * p.num_n_blocks
+                                 : (long long)p.num_m_blocks * p.num_n_blocks;
+    int grid = (int)(max_tiles < di->num_sms ? max_tiles : di->num_sms);
+    if (grid < 1) grid = 1;
+    gg_fp8_kernel<MASKED><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        tmap_a, tmap_b, p, status_ptr());
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+// Carves the layer workspace.  Every region is 256-byte aligned.
+struct LayerWorkspace {
+    int32_t *ids, *counts, *offsets, *pos, *src_pair, *layout, *chunk_counts;
+    float *weights, *s1, *s2;
+    uint8_t *a1, *a2;
+    __nv_bfloat16 *g1, *y;
+    int64_t cap_rows;
+    size_t bytes;
+};
+
+int64_t layer_cap_rows(int64_t n_pairs, int32_t E, int32_t align) {
+    return (n_pairs + align - 1) / align * align + (int64_t)E * align;
+}
+
+LayerWorkspace carve_layer(void* base, int64_t T, int32_t H, int32_t I, int32_t E, int32_t top_k, int32_t align) {
+    LayerWorkspace w;
+    const int64_t n_pairs = T * top_k;
+    const int64_t cap = layer_cap_rows(n_pairs, E, align);
+    const int64_t n_chunks = (n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK;
+    size_t off = 0;
+    char* b = static_cast<char*>(base);
+    auto take = [&](size_t bytes) { char* p = b ? b + off : nullptr; off += align256(bytes); return p; };
+    w.ids = reinterpret_cast<int32_t*>(take(n_pairs * 4));
+    w.weights = reinterpret_cast<float*>(take(n_pairs * 4));
+    w.counts = reinterpret_cast<int32_t*>(take((size_t)E * 4));
+    w.offsets = reinterpret_cast<int32_t*>(take((size_t)(E + 1) * 4));
+    w.pos = reinterpret_cast<int32_t*>(take(n_pairs * 4));
+    w.src_pair = reinterpret_cast<int32_t*>(take(cap * 4));
+    w.layout = reinterpret_cast<int32_t*>(take(cap * 4));
+    w.chunk_counts = reinterpret_cast<int32_t*>(take((size_t)n_chunks * E * 4));
+    w.a1 = reinterpret_cast<uint8_t*>(take((size_t)cap * H));
+    w.s1 = reinterpret_cast<float*>(take((size_t)cap * (H / 128) * 4));
+    w.g1 = reinterpret_cast<__nv_bfloat16*>(take((size_t)cap * 2 * I * 2));
+    w.a2 = reinterpret_cast<uint8_t*>(take((size_t)cap * I));
+    w.s2 = reinterpret_cast<float*>(take((size_t)cap * (I / 128) * 4));
+    w.y = reinterpret_cast<__nv_bfloat16*>(take((size_t)cap * H * 2));
+    w.cap_rows = cap;
+    w.bytes = off;
+    return w;
+}
+
+int check_plan_args(int64_t n_pairs, int32_t E_local, int32_t align, int64_t cap_rows) {
+    if (n_pairs < 0 || n_pairs > 0x7FFFFFFFll) return fail(MOE_ERR_INVALID, "n_pairs out of range");
+    if (E_local <= 0 || E_local > 256) return fail(MOE_ERR_INVALID, "E_local=%d must be in [1, 256]", E_local);
+    if (align <= 0) return fail(MOE_ERR_INVALID, "align must be positive");
+    if (cap_rows < 0 || cap_rows > 0x7FFFFFFFll) return fail(MOE_ERR_INVALID, "cap_rows out of range");
+    return MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int moe_gg_fp8_contiguous(const moe_gg_args* args, void* stream) { return launch_gg<false>(args, stream); }
+int moe_gg_fp8_masked(const moe_gg_args* args, void* stream) { return launch_gg<true>(args, stream); }
+
+int moe_device_status(int32_t* status_out, void* stream) {
+    CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int v = 0;
+    CUDA_TRY(cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int)));
+    if (v != 0) {
+        int zero = 0;
+        CUDA_TRY(cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int)));
+    }
+    if (status_out) *status_out = v;
+    if (v != 0) return fail(MOE_ERR_DEVICE, "device status 0x%x: a bounded wait inside a kernel ran out", v);
+    return MOE_OK;
+}
+
+
+int moe_quant_1x128(const void* x_bf16, void* q, float* scales, int64_t ss_row, int64_t ss_blk,
+                    int32_t rows, int32_t cols, void* stream) {
+    if (!x_bf16 || !q || !scales) return fail(MOE_ERR_INVALID, "x, q and scales must be non-NULL");
+    if (rows < 0 || cols <= 0 || cols % 128) return fail(MOE_ERR_INVALID, "cols=%d must be a positive multiple of 128", cols);
+    if (rows == 0) return MOE_OK;
+    const long long warps = (long long)rows * (cols / 128);
+    const int wpb = 8;
+    quant_1x128_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(q), scales, ss_row, ss_blk, rows, cols);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_silu_mul_requant(const void* gate_up_bf16, void* q, float* scales, int64_t ss_row, int64_t ss_blk,
+                         const int32_t* layout, int32_t rows, int32_t inter, int32_t gate_first, void* stream) {
+    if (!gate_up_bf16 || !q || !scales) return fail(MOE_ERR_INVALID, "gate_up, q and scales must be non-NULL");
+    if (rows < 0 || inter <= 0 || inter % 128) return fail(MOE_ERR_INVALID, "inter=%d must be a positive multiple of 128", inter);
+    if (rows == 0) return MOE_OK;
+    const long long warps = (long long)rows * (inter / 128);
+    const int wpb = 8;
+    silu_mul_requant_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), scales, ss_row, ss_blk, layout,
+        rows, inter, gate_first);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_route_topk(const float* logits, int32_t* ids, float* weights, int32_t T, int32_t E, int32_t top_k,
+                   void* stream) {
+    if (!logits || !ids || !weights) return fail(MOE_ERR_INVALID, "logits, ids and weights must be non-NULL");
+    if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE) return fail(MOE_ERR_INVALID, "E=%d must be in [1, %d]", E, 32 * ROUTE_MAX_PER_LANE);
+    if (top_k <= 0 || top_k > 32 || top_k > E) return fail(MOE_ERR_INVALID, "top_k=%d must be in [1, min(32, E)]", top_k);
+    if (T < 0) return fail(MOE_ERR_INVALID, "T must be non-negative");
+    if (T == 0) return MOE_OK;
+    const int wpb = 8;
+    route_softmax_topk_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, ids, weights, T, E, top_k);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+size_t moe_permute_workspace_bytes(int64_t n_pairs, int32_t E_local) {
+    const int64_t n_chunks = (n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK;
+    return align256((size_t)(n_chunks > 0 ? n_chunks : 1) * (size_t)E_local * 4);
+}
+
+int moe_permute_plan(const int32_t* ids, int64_t n_pairs, int32_t e_lo, int32_t E_local, int32_t align,
+                     int32_t cap_rows, int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_pair,
+                     int32_t* grouped_layout, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_plan_args(n_pairs, E_local, align, cap_rows);
+    if (rc != MOE_OK) return rc;
+    if (!ids || !counts || !offsets || !pos || !src_pair || !grouped_layout || !workspace)
+        return fail(MOE_ERR_INVALID, "all plan pointers must be non-NULL");
+    if (workspace_bytes < moe_permute_workspace_bytes(n_pairs, E_local))
+        return fail(MOE_ERR_INVALID, "plan workspace too small: %zu < %zu", workspace_bytes,
+                    moe_permute_workspace_bytes(n_pairs, E_local));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* chunk_counts = static_cast<int*>(workspace);
+    const int n_chunks = (int)((n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK);
+    const size_t hist_bytes = (size_t)32 * E_local * 4;
+    if (n_chunks > 0) {
+        plan_count_kernel<<<n_chunks, PLAN_CHUNK, hist_bytes, st>>>(ids, n_pairs, e_lo, E_local, chunk_counts);
+        CUDA_TRY(cudaGetLastError());
+    }
+    plan_scan_kernel<<<1, 256, (size_t)E_local * 4, st>>>(chunk_counts, n_chunks, E_local, align, counts, offsets);
+    CUDA_TRY(cudaGetLastError());
+    const int place_blocks = n_chunks > 0 ? n_chunks : 1;
+    plan_place_kernel<<<place_blocks, PLAN_CHUNK, hist_bytes, st>>>(ids, n_pairs, e_lo, E_local, chunk_counts, counts,
+                                                                   offsets, pos, src_pair, grouped_layout, cap_rows);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_permute(const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk, const int32_t* src_pair,
+                int32_t top_k, void* a, float* a_scale, int64_t as_row, int64_t as_blk, int32_t rows, int32_t H,
+                void* stream) {
+    if (!x_q || !x_scale || !src_pair || !a || !a_scale) return fail(MOE_ERR_INVALID, "permute pointers must be non-NULL");
+    if (H <= 0 || H % 128 || top_k <= 0) return fail(MOE_ERR_INVALID, "H must be a positive multiple of 128, top_k positive");
+    if ((reinterpret_cast<uintptr_t>(x_q) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
+        return fail(MOE_ERR_INVALID, "x_q and a must be 16-byte aligned");
+    if (rows <= 0) return rows == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "rows must be non-negative");
+    const int wpb = 8;
+    gather_rows_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(x_q), x_scale, xs_row, xs_blk, src_pair, top_k, static_cast<uint8_t*>(a), a_scale,
+        as_row, as_blk, rows, H);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_combine(const void* y_bf16, const int32_t* pos, const float* w, void* out_bf16, int32_t T, int32_t top_k,
+                int32_t H, void* stream) {
+    if (!y_bf16 || !pos || !w || !out_bf16) return fail(MOE_ERR_INVALID, "combine pointers must be non-NULL");
+    if (H <= 0 || H % 8 || top_k <= 0 || top_k > 32) return fail(MOE_ERR_INVALID, "H must be a multiple of 8 and top_k in [1, 32]");
+    if (T <= 0) return T == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "T must be non-negative");
+    combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(y_bf16), pos, w, static_cast<__nv_bfloat16*>(out_bf16), T, top_k, H);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+size_t moe_workspace_bytes(int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k, int32_t align) {
+    if (T < 0 || H <= 0 || I <= 0 || E <= 0 || top_k <= 0 || align <= 0) return 0;
+    return carve_layer(nullptr, T, H, I, E, top_k, align).bytes;
+}
+
+int moe_layer_forward(const moe_layer_args* L, void* stream) {
+    if (!L) return fail(MOE_ERR_INVALID, "args is NULL");
+    if (!L->x_q || !L->x_scale || !L->w13 || !L->w13_scale || !L->w2 || !L->w2_scale || !L->out || !L->workspace)
+        return fail(MOE_ERR_INVALID, "x_q, x_scale, w13, w13_scale, w2, w2_scale, out and workspace must be non-NULL");
+    if (!L->logits && !(L->topk_ids && L->topk_weights))
+        return fail(MOE_ERR_INVALID, "pass router logits, or both topk_ids and topk_weights");
+    if (L->H % 128 || L->I % 128) return fail(MOE_ERR_INVALID, "H and I must be multiples of 128");
+    if (L->T < 0 || L->E <= 0 || L->E > 256 || L->top_k <= 0 || L->top_k > 32)
+        return fail(MOE_ERR_INVALID, "T>=0, 1<=E<=256, 1<=top_k<=32 required");
+    if (L->align <= 0 || L->align % 128) return fail(MOE_ERR_INVALID, "align must be a positive multiple of 128");
+    const size_t need = moe_workspace_bytes(L->T, L->H, L->I, L->E, L->top_k, L->align);
+    if (L->workspace_bytes < need)
+        return fail(MOE_ERR_INVALID, "workspace too small: %zu < %zu bytes", (size_t)L->workspace_bytes, need);
+    if (L->T == 0) return MOE_OK;
+    LayerWorkspace w = carve_layer(L->workspace, L->T, L->H, L->I, L->E, L->top_k, L->align);
+    const int64_t n_pairs = (int64_t)L->T * L->top_k;
+    const int32_t cap = (int32_t)w.cap_rows;
+    int rc;
+    const int32_t* ids = L->topk_ids;
+    const float* wts = L->topk_weights;
+    if (L->logits) {
+        rc = moe_route_topk(L->logits, w.ids, w.weights, L->T, L->E_global > 0 ? L->E_global : L->E, L->top_k, stream);
+        if (rc != MOE_OK) return rc;
+        ids = w.ids;
+        wts = w.weights;
+    }
+    rc = moe_permute_plan(ids, n_pairs, L->e_lo, L->E, L->align, cap, w.counts, w.offsets, w.pos, w.src_pair,
+                          w.layout, w.chunk_counts, moe_permute_workspace_bytes(n_pairs, L->E), stream);
+    if (rc != MOE_OK) return rc;
+    // scales of the gathered rows are stored MN-major ([K/128, cap]) so that the GEMM's per-row
+    // scale loads are coalesced
+    rc = moe_permute(L->x_q, L->x_scale, L->xs_stride_row, L->xs_stride_blk, w.src_pair, L->top_k, w.a1, w.s1, 1, cap,
+                     cap, L->H, stream);
+    if (rc != MOE_OK) return rc;
+    moe_gg_args g1 = {};
+    g1.a = w.a1; g1.b = L->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = cap;
+    g1.sfb = L->w13_scale; g1.layout = w.layout; g1.d = w.g1; g1.ldd = 2 * (int64_t)L->I;
+    g1.G = L->E; g1.M = cap; g1.N = 2 * L->I; g1.K = L->H; g1.d_dtype = MOE_DTYPE_BF16;
+    rc = moe_gg_fp8_contiguous(&g1, stream);
+    if (rc != MOE_OK) return rc;
+    rc = moe_silu_mul_requant(w.g1, w.a2, w.s2, 1, cap, w.layout, cap, L->I, L->gate_first, stream);
+    if (rc != MOE_OK) return rc;
+    moe_gg_args g2 = {};
+    g2.a = w.a2; g2.b = L->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = cap;
+    g2.sfb = L->w2_scale; g2.layout = w.layout; g2.d = w.y; g2.ldd = L->H;
+    g2.G = L->E; g2.M = cap; g2.N = L->H; g2.K = L->I; g2.d_dtype = MOE_DTYPE_BF16;
+    rc = moe_gg_fp8_contiguous(&g2, stream);
+    if (rc != MOE_OK) return rc;
+    return moe_combine(w.y, w.pos, wts, L->out, L->T, L->top_k, L->H, stream);
+}
+
+int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k,
+                             int32_t align, moe_layer_view* view) {
+    if (!view) return fail(MOE_ERR_INVALID, "view is NULL");
+    LayerWorkspace w = carve_layer(workspace, T, H, I, E, top_k, align);
+    view->ids = w.ids; view->weights = w.weights; view->counts = w.counts; view->offsets = w.offsets;
+    view->pos = w.pos; view->src_pair = w.src_pair; view->grouped_layout = w.layout;
+    view->a1 = w.a1; view->s1 = w.s1; view->g1 = w.g1; view->a2 = w.a2; view->s2 = w.s2; view->y = w.y;
+    view->cap_rows = w.cap_rows;
+    return MOE_OK;
+}
+
+const char* moe_last_error(void) { return g_err; }
+const char* moe_version(void) { return "b200moe 0.1 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,381 @@
+// m-grouped FP8 block-scaled GEMM for sm_100a (contiguous and masked layouts).
+//
+//   D_g[rows, N] (bf16) = sum over 128-wide K blocks kb of
+//        (A_g[rows, kb] . B_g[N, kb]^T  in e4m3 x e4m3 -> fp32 on tcgen05)  *  sfa[row, kb] * sfb[g, n/128, kb]
+//
+// One persistent CTA per SM, 384 threads, three roles:
+//   warp 0        TMA producer: A tile 128 x 128 B and B tile 256 x 128 B per K block into a
+//                 4-stage shared-memory ring (SWIZZLE_128B), completion on mbarriers
+//   warp 1        MMA issuer: four tcgen05.mma (128 x 256 x 32) per K block into one of two
+//                 256-column TMEM accumulators; tcgen05.commit releases the smem stage and
+//                 publishes the accumulator
+//   warps 4..11   two promotion/epilogue warpgroups (128 columns each): per K block they drain
+//                 the TMEM accumulator (tcgen05.ld), apply the block scales
+//                 acc += partial * (sfa * sfb) in registers, hand the TMEM buffer back, and after
+//                 the last K block convert to bf16 and store the valid rows
+// The MMA of K block i+1 runs while block i is being promoted (double-buffered TMEM).
+// Every wait is bounded (see mbar_wait_warp); on expiry the CTA unwinds and the host sees a status.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <limits.h>
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+namespace gg {
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;              // bytes == elements (fp8)
+constexpr int STAGES = 4;
+constexpr int ACC_STAGES = 2;
+constexpr int THREADS = 384;
+constexpr int A_STAGE_BYTES = BM * BK;             // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK;             // 32 KB
+constexpr int TMEM_COLS = 512;
+constexpr int MAX_MASKED_GROUPS = 1024;
+constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+// tiles + barriers/bookkeeping + masked-layout prefix table + slack for 1024-byte alignment
+constexpr int SMEM_BYTES = SMEM_TILE_BYTES + 256 + (MAX_MASKED_GROUPS + 1) * 4 + 1024;
+}  // namespace gg
+
+struct GGParams {
+    const float* sfa;
+    long long sfa_sr, sfa_sk;
+    const float* sfb;            // [G][nb128][KB]
+    const int* layout;           // grouped_layout[M] or masked_m[G]
+    void* d;                     // bf16 (or fp32 when d_f32 != 0)
+    long long ldd;
+    int d_f32;
+    int G, M, N, K;              // M: total rows (contiguous) / rows per group (masked)
+    int rows_total;              // rows of the flattened A / D (M or G*M)
+    int num_n_blocks;            // ceil(N / BN)
+    int num_k_blocks;            // K / 128
+    int nb128;                   // ceil(N / 128)
+    int num_m_blocks;            // contiguous: ceil(M / BM)
+};
+
+struct Tile {
+    int m0;          // first row of the tile in the flattened A / D
+    int n_blk;       // column block (BN wide)
+    int g;           // group
+    int rows;        // masked: number of valid rows in this tile (<= BM); contiguous: BM
+};
+
+// Smallest group id > prev among grouped_layout[m0 .. m0+127] (INT_MAX if none).  Warp-collective.
+__device__ __forceinline__ int next_group_in_block(const int* __restrict__ layout, int m0, int M,
+                                                   int prev, int lane) {
+    int best = INT_MAX;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int r = m0 + lane * 4 + j;
+        if (r < M) {
+            int v = __ldg(layout + r);
+            if (v > prev && v < best) best = v;
+        }
+    }
+    return __reduce_min_sync(0xffffffffu, best);
+}
+
+// Static persistent schedule.  All warps of a CTA walk the same sequence.
+//  contiguous: tile index t -> (128-row block, column block); a row block is visited once per
+//              distinct non-negative group id found in it (one when groups are 128-aligned).
+//  masked:     compact enumeration of (group, row block < ceil(masked_m/128), column block)
+//              through a prefix table in shared memory.
+template <bool MASKED>
+struct Scheduler {
+    const GGParams& p;
+    const int* prefix;   // masked: smem prefix of row blocks per group, [G+1]
+    int t, lane, prev_g, total;
+
+    __device__ __forceinline__ Scheduler(const GGParams& p_, const int* prefix_, int lane_)
+        : p(p_), prefix(prefix_), t(blockIdx.x), lane(lane_), prev_g(-1) {
+        total = MASKED ? prefix_[p_.G] * p_.num_n_blocks : p_.num_m_blocks * p_.num_n_blocks;
+    }
+
+    __device__ __forceinline__ bool next(Tile& tile) {
+        if (MASKED) {
+            if (t >= total) return false;
+            int mbg = t / p.num_n_blocks;
+            int lo = 0, hi = p.G;            // find g with prefix[g] <= mbg < prefix[g+1]
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (prefix[mid] <= mbg) lo = mid; else hi = mid;
+            }
+            int mb = mbg - prefix[lo];
+            tile.g = lo;
+            tile.n_blk = t % p.num_n_blocks;
+            tile.m0 = lo * p.M + mb * gg::BM;
+            int left = __ldg(p.layout + lo) - mb * gg::BM;
+            if (left > p.M - mb * gg::BM) left = p.M - mb * gg::BM;
+            tile.rows = left < gg::BM ? left : gg::BM;
+            t += gridDim.x;
+            return true;
+        } else {
+            while (t < total) {
+                int m_blk = t / p.num_n_blocks;
+                int g = next_group_in_block(p.layout, m_blk * gg::BM, p.M, prev_g, lane);
+                if (g == INT_MAX || g >= p.G) {
+                    t += gridDim.x;
+                    prev_g = -1;
+                    continue;
+                }
+                prev_g = g;
+                tile.m0 = m_blk * gg::BM;
+                tile.n_blk = t % p.num_n_blocks;
+                tile.g = g;
+                tile.rows = gg::BM;
+                return true;
+            }
+            return false;
+        }
+    }
+};
+
+template <bool MASKED>
+__global__ void __launch_bounds__(gg::THREADS, 1)
+gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const GGParams p, int* status) {
+    using namespace gg;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: required by the 128-byte swizzle atoms the MMA descriptors address
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    int* prefix = reinterpret_cast<int*>(smem + SMEM_TILE_BYTES + 256);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const uint32_t full_bar = smem_u32(bars);
+    const uint32_t empty_bar = smem_u32(bars + STAGES);
+    const uint32_t tfull_bar = smem_u32(bars + 2 * STAGES);
+    const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + ACC_STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int s = 0; s < ACC_STAGES; ++s) {
+            mbar_init(tfull_bar + 8 * s, 1);
+            mbar_init(tempty_bar + 8 * s, 8);     // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (MASKED) {
+        // prefix[g] = number of 128-row blocks of groups < g  (G <= MAX_MASKED_GROUPS)
+        if (warp == 2) {
+            int running = 0;
+            for (int base = 0; base < p.G; base += 32) {
+                int g = base + lane;
+                int mm = 0;
+                if (g < p.G) {
+                    mm = __ldg(p.layout + g);
+                    mm = mm < 0 ? 0 : (mm > p.M ? p.M : mm);
+                }
+                int blocks = (mm + BM - 1) / BM;
+                int incl = blocks;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                if (g < p.G) prefix[g] = running + incl - blocks;
+                running += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) prefix[p.G] = running;
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_base_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    const int KB = p.num_k_blocks;
+
+    if (warp < 4) {
+        setmaxnreg_dec<40>();
+        if (warp == 0) {
+            // ------------------------------------------------ TMA producer
+            Scheduler<MASKED> sched(p, prefix, lane);
+            Tile tile;
+            uint32_t stage = 0, phase = 0;
+            uint32_t issued = 0, issued_parity = 0;   // per-stage: a load was issued / its phase parity
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                const int b_row = tile.g * p.N + tile.n_blk * BN;
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
+                                        STATUS_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t fb = full_bar + 8 * stage;
+                        mbar_arrive_expect_tx(fb, A_STAGE_BYTES + B_STAGE_BYTES);
+                        tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tile.m0);
+                        tma_load_2d(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
+                    }
+                    __syncwarp();
+                    issued |= 1u << stage;
+                    issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // Unwinding after a failed wait: give every copy this warp issued a bounded chance to
+            // land before the CTA exits (on the normal path the MMA warp has consumed them all).
+            if (!ok && lane == 0) {
+                for (int s = 0; s < STAGES; ++s) {
+                    if (!((issued >> s) & 1u)) continue;
+                    const uint32_t par = (issued_parity >> s) & 1u;
+                    for (int it = 0; it < (1 << 20); ++it)
+                        if (mbar_try_wait(full_bar + 8 * s, par)) break;
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------ MMA issuer
+            Scheduler<MASKED> sched(p, prefix, lane);
+            Tile tile;
+            constexpr uint32_t idesc = make_idesc_e4m3_f32(BM, BN);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status,
+                                        STATUS_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status,
+                                        STATUS_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint64_t adesc = make_smem_desc_sw128(smem_u32(smem_a + stage * A_STAGE_BYTES));
+                        const uint64_t bdesc = make_smem_desc_sw128(smem_u32(smem_b + stage * B_STAGE_BYTES));
+                        const uint32_t tmem_d = tmem_base + acc * BN;
+#pragma unroll
+                        for (int k = 0; k < BK / 32; ++k) {
+                            // advance 32 bytes of K inside the 128-byte swizzled row: +2 in 16-byte units
+                            umma_f8f6f4(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                        }
+                        umma_commit(empty_bar + 8 * stage);   // stage reusable once the MMAs have read it
+                        umma_commit(tfull_bar + 8 * acc);     // accumulator of this K block complete
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------- promotion + epilogue
+        setmaxnreg_inc<216>();
+        const int ew = warp - 4;
+        const int quarter = warp & 3;                 // TMEM lanes this warp may touch
+        const int half = ew >> 2;                     // which 128 columns of the 256-wide tile
+        const int row_in_tile = quarter * 32 + lane;
+        Scheduler<MASKED> sched(p, prefix, lane);
+        Tile tile;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        while (ok && sched.next(tile)) {
+            const int n0 = tile.n_blk * BN + half * 128;
+            const int row = tile.m0 + row_in_tile;
+            bool row_valid;
+            if (MASKED) row_valid = row_in_tile < tile.rows;
+            else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
+            const int srow = row < p.rows_total ? row : p.rows_total - 1;
+            const float* sfa_ptr = p.sfa + (long long)srow * p.sfa_sr;
+            int nb = n0 >> 7;
+            if (nb >= p.nb128) nb = p.nb128 - 1;
+            const float* sfb_ptr = p.sfb + ((long long)tile.g * p.nb128 + nb) * KB;
+
+            float accr[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) accr[j] = 0.0f;
+
+            float sa = __ldg(sfa_ptr), sb = __ldg(sfb_ptr);
+            for (int kb = 0; kb < KB; ++kb) {
+                const float s = sa * sb;
+                if (kb + 1 < KB) {             // prefetch the next block's scales behind the wait
+                    sa = __ldg(sfa_ptr + (long long)(kb + 1) * p.sfa_sk);
+                    sb = __ldg(sfb_ptr + kb + 1);
+                }
+                ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status,
+                                    STATUS_TIMEOUT_TMEM_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + half * 128;
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(taddr, v0);
+                tmem_ld_wait(v0);
+                tmem_ld_32x32b_x32(taddr + 32, v1);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) accr[j] = fmaf(__uint_as_float(v0[j]), s, accr[j]);
+                tmem_ld_wait(v1);
+                tmem_ld_32x32b_x32(taddr + 64, v0);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) accr[32 + j] = fmaf(__uint_as_float(v1[j]), s, accr[32 + j]);
+                tmem_ld_wait(v0);
+                tmem_ld_32x32b_x32(taddr + 96, v1);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) accr[64 + j] = fmaf(__uint_as_float(v0[j]), s, accr[64 + j]);
+                tmem_ld_wait(v1);
+                // all four loads have landed: hand the accumulator back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) accr[96 + j] = fmaf(__uint_as_float(v1[j]), s, accr[96 + j]);
+                if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+            if (!ok) break;
+            if (row_valid && p.d_f32) {
+                float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 4) {
+                    if (n0 + j + 4 <= p.N)
+                        *reinterpret_cast<float4*>(drow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+                }
+            } else if (row_valid) {
+                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 8) {
+                    if (n0 + j + 8 <= p.N) {
+                        uint4 out;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(accr[j + 0], accr[j + 1]);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(accr[j + 2], accr[j + 3]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(accr[j + 4], accr[j + 5]);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(accr[j + 6], accr[j + 7]);
+                        out.x = *reinterpret_cast<uint32_t*>(&h0);
+                        out.y = *reinterpret_cast<uint32_t*>(&h1);
+                        out.z = *reinterpret_cast<uint32_t*>(&h2);
+                        out.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(drow + j) = out;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace b200

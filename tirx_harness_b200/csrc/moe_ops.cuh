@@ -1,0 +1,318 @@
+// HBM-bound kernels either side of the grouped GEMMs: 1x128 activation quantisation, fused
+// SiLU*mul + FP8 requantisation, softmax top-k routing, the stable permutation plan (counts,
+// aligned group offsets, destination rows, grouped_layout), row gather and weighted combine.
+// All are plain coalesced 16-byte-vector kernels; none uses tensor cores.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// four fp32 -> four e4m3 bytes (cvt.rn.satfinite.e4m3x2.f32), byte j = value j
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+__device__ __forceinline__ float clamp448(float v) { return fminf(fmaxf(v, -448.0f), 448.0f); }
+
+// Quantise one 128-wide block held as 4 values per lane: s = max(amax, 1e-8) / 448,
+// q = e4m3(clamp(x / s)) with IEEE division.  Returns the packed bytes; *scale_out = s.
+__device__ __forceinline__ uint32_t quant_block_4(const float (&x)[4], float* scale_out) {
+    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+    amax = warp_max(amax);
+    const float s = __fdiv_rn(fmaxf(amax, 1.0e-8f), 448.0f);
+    *scale_out = s;
+    return pack4_e4m3(clamp448(__fdiv_rn(x[0], s)), clamp448(__fdiv_rn(x[1], s)),
+                      clamp448(__fdiv_rn(x[2], s)), clamp448(__fdiv_rn(x[3], s)));
+}
+
+__device__ __forceinline__ void bf16x4_to_float(uint2 raw, float (&out)[4]) {
+    out[0] = __uint_as_float(raw.x << 16);
+    out[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+    out[2] = __uint_as_float(raw.y << 16);
+    out[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+}
+
+// x bf16 [rows, cols] -> q e4m3 [rows, cols], scales f32 at [r*ss_r + b*ss_b].  One warp per block.
+__global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                   float* __restrict__ scales, long long ss_r, long long ss_b,
+                                   int rows, int cols) {
+    const int nb = cols >> 7;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)rows * nb) return;
+    const int r = (int)(w / nb), b = (int)(w % nb);
+    const long long off = (long long)r * cols + b * 128 + lane * 4;
+    float v[4];
+    bf16x4_to_float(__ldg(reinterpret_cast<const uint2*>(x + off)), v);
+    float s;
+    const uint32_t packed = quant_block_4(v, &s);
+    *reinterpret_cast<uint32_t*>(q + off) = packed;
+    if (lane == 0) scales[r * ss_r + b * ss_b] = s;
+}
+
+// SiLU in the device form the reference's corpus models: x / (1 + exp2(-x * log2(e))).
+__device__ __forceinline__ float silu_f32(float x) {
+    return __fdiv_rn(x, 1.0f + exp2f(-x * 1.4426950408889634f));
+}
+
+// gate_up bf16 [rows, 2I] -> act = silu(gate) * up (fp32) -> 1x128 requant: q e4m3 [rows, I],
+// scales at [r*ss_r + b*ss_b].  gate_first: gate = columns [0, I), else gate = [I, 2I).
+// Rows whose layout entry is negative (padding) are skipped.  One warp per (row, 128-block).
+__global__ void silu_mul_requant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ q,
+                                        float* __restrict__ scales, long long ss_r, long long ss_b,
+                                        const int* __restrict__ layout, int rows, int inter,
+                                        int gate_first) {
+    const int nb = inter >> 7;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)rows * nb) return;
+    const int r = (int)(w / nb), b = (int)(w % nb);
+    if (layout != nullptr && __ldg(layout + r) < 0) return;
+    const long long base = (long long)r * 2 * inter + b * 128 + lane * 4;
+    float g[4], u[4], a[4];
+    bf16x4_to_float(__ldg(reinterpret_cast<const uint2*>(gu + base + (gate_first ? 0 : inter))), g);
+    bf16x4_to_float(__ldg(reinterpret_cast<const uint2*>(gu + base + (gate_first ? inter : 0))), u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a[j] = __fmul_rn(silu_f32(g[j]), u[j]);
+    float s;
+    const uint32_t packed = quant_block_4(a, &s);
+    *reinterpret_cast<uint32_t*>(q + (long long)r * inter + b * 128 + lane * 4) = packed;
+    if (lane == 0) scales[r * ss_r + b * ss_b] = s;
+}
+
+// Softmax over E logits + top-k (ties -> lowest expert index), weights renormalised over the
+// selected experts.  One warp per token; lane l holds experts l, l+32, ...  E <= 512, top_k <= 32.
+constexpr int ROUTE_MAX_PER_LANE = 16;
+__global__ void route_softmax_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids,
+                                          float* __restrict__ weights, int T, int E, int top_k) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float v[ROUTE_MAX_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? __ldg(logits + (long long)t * E + e) : -INFINITY;
+        mx = fmaxf(mx, v[j]);
+    }
+    mx = warp_max(mx);
+    unsigned taken = 0;          // bit j: this lane's j-th expert already selected
+    float my_w = 0.0f;           // lane k keeps the k-th selection
+    int my_id = 0;
+    float sum = 0.0f;
+    for (int k = 0; k < top_k; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7FFFFFFF;
+#pragma unroll
+        for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) {
+            const int e = lane + 32 * j;
+            if (e < E && !((taken >> j) & 1u) && (v[j] > best || best_e == 0x7FFFFFFF)) {
+                best = v[j];
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe != 0x7FFFFFFF && (best_e == 0x7FFFFFFF || ob > best || (ob == best && oe < best_e))) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+        const float p = expf(best - mx);
+        sum += p;
+        if (lane == k) { my_w = p; my_id = best_e; }
+    }
+    if (lane < top_k) {
+        ids[(long long)t * top_k + lane] = my_id;
+        weights[(long long)t * top_k + lane] = __fdiv_rn(my_w, sum);
+    }
+}
+
+// ------------------------------------------------------------------ permutation plan
+// Pairs p = t*top_k + j are processed in chunks of 1024 (one block each, 32 warps in pair order).
+// Step 1 (count):  chunk_counts[chunk][e] = pairs of the chunk routed to local expert e.
+// Step 2 (scan):   per expert, exclusive scan over chunks (in place), counts[e], 128-aligned
+//                  offsets[e], offsets[E] = total rows.
+// Step 3 (place):  pos[p] = offsets[e] + chunk offset + rank inside the chunk (pair order kept ->
+//                  the permutation is stable); src_pair[row] = p; grouped_layout[row] = e / -1.
+constexpr int PLAN_CHUNK = 1024;
+
+// per-warp histogram of the chunk into smem hist[32][E]; returns this pair's local expert (or -1)
+// and its rank among equal experts inside the warp
+__device__ __forceinline__ int plan_warp_hist(const int* __restrict__ ids, long long n_pairs, int e_lo,
+                                              int E, int* hist, int* rank_in_warp) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const long long p = (long long)blockIdx.x * PLAN_CHUNK + threadIdx.x;
+    int e = -1;
+    if (p < n_pairs) {
+        e = __ldg(ids + p) - e_lo;
+        if (e < 0 || e >= E) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    *rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && *rank_in_warp == 0) hist[warp * E + e] = __popc(peers);
+    __syncthreads();
+    return e;
+}
+
+__global__ void plan_count_kernel(const int* __restrict__ ids, long long n_pairs, int e_lo, int E,
+                                  int* __restrict__ chunk_counts) {
+    extern __shared__ int hist[];
+    int rank;
+    plan_warp_hist(ids, n_pairs, e_lo, E, hist, &rank);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int s = 0;
+#pragma unroll 8
+        for (int w = 0; w < 32; ++w) s += hist[w * E + e];
+        chunk_counts[(long long)blockIdx.x * E + e] = s;
+    }
+}
+
+// one block; thread e scans its expert's column of chunk_counts, then thread 0.. build offsets
+__global__ void plan_scan_kernel(int* __restrict__ chunk_counts, int n_chunks, int E, int align,
+                                 int* __restrict__ counts, int* __restrict__ offsets) {
+    extern __shared__ int cnt[];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int run = 0;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int v = chunk_counts[(long long)c * E + e];
+            chunk_counts[(long long)c * E + e] = run;
+            run += v;
+        }
+        counts[e] = run;
+        cnt[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = total;
+            total += (cnt[e] + align - 1) / align * align;
+        }
+        offsets[E] = total;
+    }
+}
+
+__global__ void plan_place_kernel(const int* __restrict__ ids, long long n_pairs, int e_lo, int E,
+                                  const int* __restrict__ chunk_offsets, const int* __restrict__ counts,
+                                  const int* __restrict__ offsets, int* __restrict__ pos,
+                                  int* __restrict__ src_pair, int* __restrict__ grouped_layout,
+                                  int cap_rows) {
+    extern __shared__ int hist[];
+    int rank;
+    const int e = plan_warp_hist(ids, n_pairs, e_lo, E, hist, &rank);
+    // exclusive scan over the 32 warps, per expert
+    for (int x = threadIdx.x; x < E; x += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int v = hist[w * E + x];
+            hist[w * E + x] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    const long long p = (long long)blockIdx.x * PLAN_CHUNK + threadIdx.x;
+    if (p < n_pairs) {
+        int row = -1;
+        if (e >= 0) {
+            row = offsets[e] + chunk_offsets[(long long)blockIdx.x * E + e] + hist[(threadIdx.x >> 5) * E + e] + rank;
+            if (row < cap_rows) src_pair[row] = (int)p; else row = -1;
+        }
+        pos[p] = row;
+    }
+    // grouped_layout / src_pair of padding rows: grid-stride over all capacity rows
+    const int total = offsets[E];
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < cap_rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        int g = -1;
+        if (r < total) {
+            int lo = 0, hi = E;                 // offsets[lo] <= r < offsets[hi]
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (offsets[mid] <= r) lo = mid; else hi = mid;
+            }
+            if (r - offsets[lo] < counts[lo]) g = lo;
+        }
+        grouped_layout[r] = g;
+        if (g < 0) src_pair[r] = -1;
+    }
+}
+
+// Row gather into the contiguous grouped layout: for every row with src_pair >= 0 copy the token's
+// e4m3 row (H bytes, 16-byte vectors) and its H/128 scales.  One warp per destination row.
+// Source scales at [t*xs_r + b*xs_b]; destination scales at [row*ds_r + b*ds_b].
+__global__ void gather_rows_kernel(const uint8_t* __restrict__ x, const float* __restrict__ xs,
+                                   long long xs_r, long long xs_b, const int* __restrict__ src_pair,
+                                   int top_k, uint8_t* __restrict__ a, float* __restrict__ as_,
+                                   long long ds_r, long long ds_b, int rows, int H) {
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const int p = __ldg(src_pair + r);
+    if (p < 0) return;
+    const int t = p / top_k;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * H);
+    uint4* dst = reinterpret_cast<uint4*>(a + (long long)r * H);
+    for (int i = lane; i < (H >> 4); i += 32) dst[i] = __ldg(src + i);
+    for (int b = lane; b < (H >> 7); b += 32) as_[r * ds_r + b * ds_b] = __ldg(xs + t * xs_r + b * xs_b);
+}
+
+// out[t, :] = bf16( sum_j w[t,j] * y[pos[t,j], :] ), fp32 multiply then add in slot order, pos < 0
+// skipped.  One block per token, 8 bf16 (16 bytes) per thread per step.
+__global__ void combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos,
+                               const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int T,
+                               int top_k, int H) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    __shared__ int s_pos[32];
+    __shared__ float s_w[32];
+    if (threadIdx.x < top_k) {
+        s_pos[threadIdx.x] = pos[(long long)t * top_k + threadIdx.x];
+        s_w[threadIdx.x] = w[(long long)t * top_k + threadIdx.x];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int j = 0; j < top_k; ++j) {
+            const int r = s_pos[j];
+            if (r < 0) continue;
+            const float wj = s_w[j];
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y + (long long)r * H) + c);
+            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(wj, __uint_as_float(u[i] << 16)));
+                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(wj, __uint_as_float(u[i] & 0xFFFF0000u)));
+            }
+        }
+        uint4 o;
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+        reinterpret_cast<uint4*>(out + (long long)t * H)[c] = o;
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,133 @@
+"""Host side of the m-grouped FP8 GEMM: PyTorch tensors in, one CUDA launch out.
+
+Mirrors the reference's candidate interface for the registered workload ``grouped_gemm/fp8``
+(mlc-ai/TIRx-harness: evolution/benchmark/flashinfer_bench_evolve/tasks/grouped_gemm_fp8/
+benchmark.py:52-62 and evolution/tasks/grouped_gemm_fp8.yaml:15-25):
+
+    launch = setup(data, G, M, N, K)     # untimed: validates, binds pointers
+    launch()                             # timed: recomputes D in place from the current inputs
+
+PyTorch is used for device memory and streams only; all arithmetic happens in the CUDA library
+reached through the C ABI of include/b200moe.h.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return t.data_ptr()
+
+
+def _check_fp8(t: torch.Tensor, name: str) -> None:
+    if t.dtype not in (torch.float8_e4m3fn, torch.uint8):
+        raise TypeError(f"{name} must be float8_e4m3fn (or its uint8 bytes), got {t.dtype}")
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous CUDA tensor")
+
+
+def _scale_strides(sfa: torch.Tensor, rows: int, kblocks: int, name: str):
+    """Accepts [rows, K/128] in any stride order (row-major or MN-major/transposed view)."""
+    if sfa.dtype != torch.float32 or not sfa.is_cuda:
+        raise TypeError(f"{name} must be a float32 CUDA tensor")
+    if tuple(sfa.shape) != (rows, kblocks):
+        raise ValueError(f"{name} must have shape ({rows}, {kblocks}), got {tuple(sfa.shape)}")
+    return sfa.stride(0), sfa.stride(1)
+
+
+class _BoundGG:
+    """A validated argument block; ``__call__`` launches on the current stream of the tensors' device."""
+
+    def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K):
+        self._keep = (a, b, sfa, sfb, layout, d)
+        self._fn = getattr(_lib.lib(), fn_name)
+        self._device = d.device
+        self._args = _lib.GGArgs(
+            a=_ptr(a), b=_ptr(b), sfa=_ptr(sfa), sfa_stride_row=sfa_strides[0], sfa_stride_kblk=sfa_strides[1],
+            sfb=_ptr(sfb), layout=_ptr(layout), d=_ptr(d), ldd=d.stride(-2), G=G, M=M, N=N, K=K,
+            d_dtype=1 if d.dtype == torch.float32 else 0)
+        self._argp = ctypes.byref(self._args)
+        self.out = d
+
+    def __call__(self):
+        with torch.cuda.device(self._device):
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(self._fn(self._argp, ctypes.c_void_p(stream)))
+        return self.out
+
+
+def bind_contiguous(a, sfa, b, sfb, d, grouped_layout) -> _BoundGG:
+    """a fp8[M,K], sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128],
+    d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row)."""
+    _check_fp8(a, "a"); _check_fp8(b, "b")
+    M, K = a.shape
+    G, N, Kb = b.shape
+    if Kb != K or K % 128:
+        raise ValueError(f"K mismatch or not a multiple of 128: a K={K}, b K={Kb}")
+    strides = _scale_strides(sfa, M, K // 128, "sfa")
+    if sfb.dtype != torch.float32 or tuple(sfb.shape) != (G, (N + 127) // 128, K // 128) or not sfb.is_contiguous():
+        raise ValueError(f"sfb must be contiguous float32 [{G}, {(N + 127) // 128}, {K // 128}]")
+    if d.dtype not in (torch.bfloat16, torch.float32) or tuple(d.shape) != (M, N) or d.stride(1) != 1:
+        raise ValueError(f"d must be bfloat16 (or float32) [{M}, {N}] with unit column stride")
+    if grouped_layout.dtype != torch.int32 or grouped_layout.numel() != M or not grouped_layout.is_contiguous():
+        raise ValueError(f"grouped_layout must be contiguous int32 [{M}]")
+    return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K)
+
+
+def bind_masked(a, sfa, b, sfb, d, masked_m) -> _BoundGG:
+    """a fp8[G,max_m,K], sfa f32[G,max_m,K/128] (contiguous, or MN-major: a [G*max_m, K/128] view of any
+    strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128], d bf16[G,max_m,N], masked_m int32[G]."""
+    _check_fp8(a, "a"); _check_fp8(b, "b")
+    G, max_m, K = a.shape
+    Gb, N, Kb = b.shape
+    if Gb != G or Kb != K or K % 128:
+        raise ValueError("a and b disagree on G or K, or K is not a multiple of 128")
+    if sfa.dim() == 3:
+        if not sfa.is_contiguous():
+            raise ValueError("3-d sfa must be contiguous; pass a [G*max_m, K/128] view for other layouts")
+        sfa2 = sfa.view(G * max_m, K // 128)
+    else:
+        sfa2 = sfa
+    strides = _scale_strides(sfa2, G * max_m, K // 128, "sfa")
+    if sfb.dtype != torch.float32 or tuple(sfb.shape) != (G, (N + 127) // 128, K // 128) or not sfb.is_contiguous():
+        raise ValueError(f"sfb must be contiguous float32 [{G}, {(N + 127) // 128}, {K // 128}]")
+    if d.dtype not in (torch.bfloat16, torch.float32) or tuple(d.shape) != (G, max_m, N) or not d.is_contiguous():
+        raise ValueError(f"d must be contiguous bfloat16 (or float32) [{G}, {max_m}, {N}]")
+    if masked_m.dtype != torch.int32 or masked_m.numel() != G or not masked_m.is_contiguous():
+        raise ValueError(f"masked_m must be contiguous int32 [{G}]")
+    return _BoundGG("moe_gg_fp8_masked", a, b, sfa2, strides, sfb, masked_m, d, G, max_m, N, K)
+
+
+def m_grouped_fp8_gemm_nt_contiguous(a, sfa, b, sfb, d, grouped_layout):
+    """One-shot form (argument order of the kernel the reference baselines against: (a, sfa), (b, sfb), d, layout)."""
+    return bind_contiguous(a, sfa, b, sfb, d, grouped_layout)()
+
+
+def m_grouped_fp8_gemm_nt_masked(a, sfa, b, sfb, d, masked_m):
+    return bind_masked(a, sfa, b, sfb, d, masked_m)()
+
+
+def setup(data: dict, G: int, M: int, N: int, K: int):
+    """Candidate entry of the registered workload: returns the zero-argument timed callable.
+
+    ``data`` holds ``A`` fp8[M,K], ``B`` fp8[G,N,K], ``SFA`` f32[M,K/128] (any strides), ``SFB``
+    f32[G,N/128,K/128], ``D`` bf16[M,N] (written in place) and ``grouped_layout`` int32[M];
+    ``actual_ms`` / ``aligned_ms`` / ``alignment`` are accepted and not needed.
+    """
+    a, b, d = data["A"], data["B"], data["D"]
+    if tuple(a.shape) != (M, K) or tuple(b.shape) != (G, N, K):
+        raise ValueError(f"A/B shapes {tuple(a.shape)}/{tuple(b.shape)} do not match G={G} M={M} N={N} K={K}")
+    bound = bind_contiguous(a, data["SFA"], b, data["SFB"], d, data["grouped_layout"])
+    return bound
+
+
+def device_status(device=None) -> int:
+    """Synchronises and returns the device status word (0 = fine); raises if a kernel reported an error."""
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        out = ctypes.c_int32(0)
+        _lib.check(_lib.lib().moe_device_status(ctypes.byref(out), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out.value
