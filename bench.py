@@ -242,36 +242,42 @@ def run_ours(args):
     status = gg.device_status(device)
     value = world * flops / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end through the public call with HOST buffers: per step the activations (A, SFA,
-    # grouped_layout) go host->device from pinned memory, the GEMM runs, D comes back device->host.
-    # Weights (B, SFB) are resident model state.
-    e2e_steps = max(3, min(args.steps, 10))
-    hA = data["A"].view(torch.uint8).cpu().pin_memory()
-    hS = data["SFA"].cpu().pin_memory()
-    hL = data["grouped_layout"].cpu().pin_memory()
-    hD = torch.empty(data["D"].shape, dtype=torch.bfloat16).pin_memory()
-    dA8 = data["A"].view(torch.uint8)
+    e2e = None
+    if not args.no_e2e:
+        # ---- end to end through the public call with HOST buffers: per step the activations (A, SFA,
+        # grouped_layout) go host->device from pinned memory, the GEMM runs, D comes back device->host.
+        # Weights (B, SFB) are resident model state.
+        e2e_steps = max(3, min(args.steps, 10))
+        hA = data["A"].view(torch.uint8).cpu().pin_memory()
+        hS = data["SFA"].cpu().pin_memory()
+        hL = data["grouped_layout"].cpu().pin_memory()
+        hD = torch.empty(data["D"].shape, dtype=torch.bfloat16).pin_memory()
+        dA8 = data["A"].view(torch.uint8)
 
-    def e2e_step():
-        dA8.copy_(hA, non_blocking=True)
-        data["SFA"].copy_(hS, non_blocking=True)
-        data["grouped_layout"].copy_(hL, non_blocking=True)
-        launch()
-        hD.copy_(data["D"], non_blocking=True)
+        def e2e_step():
+            dA8.copy_(hA, non_blocking=True)
+            data["SFA"].copy_(hS, non_blocking=True)
+            data["grouped_layout"].copy_(hL, non_blocking=True)
+            launch()
+            hD.copy_(data["D"], non_blocking=True)
 
-    e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(e2e_steps):
         e2e_step()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
-    h2d = hA.numel() + hS.numel() * 4 + hL.numel() * 4
-    d2h = hD.numel() * 2
+        barrier()
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / e2e_steps
+        h2d = hA.numel() + hS.numel() * 4 + hL.numel() * 4
+        d2h = hD.numel() * 2
+        e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "note": "A, SFA, grouped_layout copied from pinned host memory and D copied back every step; "
+                       "weights resident"}
 
     if rank == 0:
         peaks = _peaks()
@@ -287,10 +293,7 @@ def run_ours(args):
                        "l2": "inputs (746 MB per launch) larger than L2, no flush", "seed": 0,
                        "timing": "CUDA events around K back-to-back launches, max over ranks"},
             "clocks": clocks.summary(),
-            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                    "note": "A, SFA, grouped_layout copied from pinned host memory and D copied back every step; "
-                            "weights resident"},
+            "e2e": e2e,
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": per_gpu / fp8_peak, "traffic": traffic,
@@ -318,6 +321,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gemm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

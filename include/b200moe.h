@@ -45,6 +45,9 @@ extern "C" {
  *           MOE_DTYPE_BF16, the workload's output type) or the unrounded fp32 accumulator
  *           (MOE_DTYPE_F32).  Only valid rows are written; padding / masked-out rows are left
  *           untouched.
+ *   rows_used  contiguous layout only, may be NULL: device pointer to the number of leading rows of
+ *           a/d that are in use (<= M).  Lets a fixed-capacity buffer be passed with M = capacity
+ *           while the kernel only visits the rows a routing step actually filled.
  * Requirements: K % 128 == 0, N % 8 == 0, a/b 16-byte aligned, d 16-byte aligned, ldd % 8 == 0.
  */
 typedef struct moe_gg_args {
@@ -59,6 +62,7 @@ typedef struct moe_gg_args {
     int64_t ldd;
     int32_t G, M, N, K;
     int32_t d_dtype;
+    const int32_t* rows_used;
 } moe_gg_args;
 
 /* Contiguous layout.  Stands in for the timed call of the registered workload
@@ -161,6 +165,64 @@ typedef struct moe_layer_view {
 } moe_layer_view;
 int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k,
                              int32_t align, moe_layer_view* view);
+
+/* ---- expert parallelism over NVLink peer memory --------------------------------------------- */
+/* The reference has no multi-GPU path: it emulates expert parallelism on one GPU through
+ * `local_expert_offset` (tasks/moe/definition.json, inputs `local_expert_offset`; offsets 0..224 in
+ * tasks/moe/workload.jsonl).  These entry points are the real exchange for that sharding: rank r owns
+ * experts [r*E_local, (r+1)*E_local) and a slice of the tokens, one process per GPU.            */
+
+/* Device memory that can be mapped by the other ranks of the node (CUDA IPC).  alloc zero-fills. */
+int moe_ipc_alloc(size_t bytes, void** ptr);
+int moe_ipc_free(void* ptr);
+int moe_ipc_get_handle(void* ptr, void* handle64);         /* 64-byte handle to send to the peers */
+int moe_ipc_open(const void* handle64, void** ptr);        /* map a peer's allocation */
+int moe_ipc_close(void* ptr);
+
+/* Peer table: entry i = rank i's buffers as mapped in THIS process (own buffers at i == rank).
+ *   a      e4m3 [cap_rows, H]       receive buffer in the contiguous grouped layout
+ *   sa     f32  [H/128, cap_rows]   its row scales, MN-major
+ *   y      bf16 [cap_rows, H]       down-GEMM output rows
+ *   counts int32 [world, E_total]   row s = number of pairs rank s routes to each expert
+ *   flags  int32 [world]            barrier epochs                                                */
+typedef struct moe_ep_peers {
+    void* a[8];
+    float* sa[8];
+    const void* y[8];
+    int32_t* counts[8];
+    int32_t* flags[8];
+} moe_ep_peers;
+
+/* Cross-GPU barrier on `stream`: publishes `epoch` (strictly increasing per call) to every peer and
+ * waits, at most 2 s, for theirs; a wait that runs out sets the device status word instead of hanging. */
+int moe_ep_barrier(const moe_ep_peers* peers, int32_t rank, int32_t world, int32_t epoch, void* stream);
+
+size_t moe_ep_workspace_bytes(int64_t n_pairs, int32_t E_total);
+
+/* Step 1 (before the first barrier): count this rank's pairs per global expert (my_counts[E_total]) and
+ * store them into row `rank` of every peer's counts table. */
+int moe_ep_count_publish(const moe_ep_peers* peers, const int32_t* ids, int64_t n_pairs, int32_t rank, int32_t world,
+                         int32_t E_total, int32_t* my_counts, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Step 2 (after that barrier): from the gathered counts derive the receive side (counts_local[E_local],
+ * offsets[E_local+1], grouped_layout[cap_rows]) and the send side (dst_base[E_total], pos[n_pairs] =
+ * destination row of every pair inside its owner's buffer; rows are ordered by source rank, then by pair
+ * order, so the result is independent of timing).  `workspace` must be the one step 1 used. */
+int moe_ep_plan(const moe_ep_peers* peers, const int32_t* ids, int64_t n_pairs, int32_t rank, int32_t world,
+                int32_t E_total, int32_t E_local, int32_t align, int32_t cap_rows, int32_t* counts_local,
+                int32_t* offsets, int32_t* grouped_layout, int32_t* dst_base, int32_t* pos, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* Dispatch all-to-all fused with the permutation: every pair's e4m3 row and scales are stored directly
+ * into the owner rank's grouped-layout buffers. */
+int moe_ep_dispatch(const moe_ep_peers* peers, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
+                    const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
+                    int32_t cap_rows, int32_t world, void* stream);
+
+/* Combine all-to-all fused with the weighted sum: each token loads its top_k expert rows from the owners'
+ * y buffers and accumulates w * row in fp32 (slot order), writing bf16. */
+int moe_ep_combine(const moe_ep_peers* peers, const int32_t* ids, const int32_t* pos, const float* w, void* out_bf16,
+                   int32_t T, int32_t top_k, int32_t E_local, int32_t H, int32_t world, void* stream);
 
 /* Reads (and clears) the device-side status word of the current device; synchronises the
  * stream first.  0 = no kernel reported a problem.  Non-zero: a bounded wait inside a kernel ran

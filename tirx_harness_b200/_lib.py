@@ -21,7 +21,7 @@ class GGArgs(_c.Structure):
         ("sfa_stride_row", _c.c_int64), ("sfa_stride_kblk", _c.c_int64),
         ("sfb", _c.c_void_p), ("layout", _c.c_void_p), ("d", _c.c_void_p), ("ldd", _c.c_int64),
         ("G", _c.c_int32), ("M", _c.c_int32), ("N", _c.c_int32), ("K", _c.c_int32),
-        ("d_dtype", _c.c_int32),
+        ("d_dtype", _c.c_int32), ("rows_used", _c.c_void_p),
     ]
 
 
@@ -41,6 +41,12 @@ class LayerView(_c.Structure):
     """``moe_layer_view`` of include/b200moe.h."""
     _fields_ = [(n, _c.c_void_p) for n in ("ids", "counts", "offsets", "pos", "src_pair", "grouped_layout",
                                            "weights", "s1", "s2", "a1", "g1", "a2", "y")] + [("cap_rows", _c.c_int64)]
+
+
+class EpPeers(_c.Structure):
+    """``moe_ep_peers`` of include/b200moe.h."""
+    _fields_ = [("a", _c.c_void_p * 8), ("sa", _c.c_void_p * 8), ("y", _c.c_void_p * 8),
+                ("counts", _c.c_void_p * 8), ("flags", _c.c_void_p * 8)]
 
 
 class B200MoeError(RuntimeError):
@@ -74,9 +80,12 @@ EXPORTS = (
     "moe_gg_fp8_contiguous", "moe_gg_fp8_masked", "moe_quant_1x128", "moe_silu_mul_requant",
     "moe_route_topk", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute", "moe_combine",
     "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
+    "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",
+    "moe_ep_barrier", "moe_ep_workspace_bytes", "moe_ep_count_publish", "moe_ep_plan", "moe_ep_dispatch",
+    "moe_ep_combine",
     "moe_last_error", "moe_version",
 )
-_SIZE_T_RETURN = ("moe_permute_workspace_bytes", "moe_workspace_bytes")
+_SIZE_T_RETURN = ("moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes")
 
 
 def check(rc: int) -> None:

@@ -145,6 +145,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.sfa_sk = a->sfa_stride_kblk;
     p.sfb = a->sfb;
     p.layout = a->layout;
+    p.rows_used = MASKED ? nullptr : a->rows_used;
     p.d = a->d;
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
@@ -380,6 +381,7 @@ int moe_layer_forward(const moe_layer_args* L, void* stream) {
     moe_gg_args g1 = {};
     g1.a = w.a1; g1.b = L->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = cap;
     g1.sfb = L->w13_scale; g1.layout = w.layout; g1.d = w.g1; g1.ldd = 2 * (int64_t)L->I;
+    g1.rows_used = w.offsets + L->E;
     g1.G = L->E; g1.M = cap; g1.N = 2 * L->I; g1.K = L->H; g1.d_dtype = MOE_DTYPE_BF16;
     rc = moe_gg_fp8_contiguous(&g1, stream);
     if (rc != MOE_OK) return rc;
@@ -388,6 +390,7 @@ int moe_layer_forward(const moe_layer_args* L, void* stream) {
     moe_gg_args g2 = {};
     g2.a = w.a2; g2.b = L->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = cap;
     g2.sfb = L->w2_scale; g2.layout = w.layout; g2.d = w.y; g2.ldd = L->H;
+    g2.rows_used = w.offsets + L->E;
     g2.G = L->E; g2.M = cap; g2.N = L->H; g2.K = L->I; g2.d_dtype = MOE_DTYPE_BF16;
     rc = moe_gg_fp8_contiguous(&g2, stream);
     if (rc != MOE_OK) return rc;
@@ -402,6 +405,153 @@ int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, i
     view->pos = w.pos; view->src_pair = w.src_pair; view->grouped_layout = w.layout;
     view->a1 = w.a1; view->s1 = w.s1; view->g1 = w.g1; view->a2 = w.a2; view->s2 = w.s2; view->y = w.y;
     view->cap_rows = w.cap_rows;
+    return MOE_OK;
+}
+
+/* ---------------------------------------------------------------- expert parallelism */
+
+int moe_ipc_alloc(size_t bytes, void** ptr) {
+    if (!ptr || bytes == 0) return fail(MOE_ERR_INVALID, "ptr must be non-NULL and bytes positive");
+    CUDA_TRY(cudaMalloc(ptr, bytes));
+    CUDA_TRY(cudaMemset(*ptr, 0, bytes));
+    return MOE_OK;
+}
+int moe_ipc_free(void* ptr) {
+    if (ptr) CUDA_TRY(cudaFree(ptr));
+    return MOE_OK;
+}
+int moe_ipc_get_handle(void* ptr, void* handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    if (!ptr || !handle64) return fail(MOE_ERR_INVALID, "ptr and handle must be non-NULL");
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+    memcpy(handle64, &h, 64);
+    return MOE_OK;
+}
+int moe_ipc_open(const void* handle64, void** ptr) {
+    if (!ptr || !handle64) return fail(MOE_ERR_INVALID, "ptr and handle must be non-NULL");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return MOE_OK;
+}
+int moe_ipc_close(void* ptr) {
+    if (ptr) CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return MOE_OK;
+}
+
+static int ep_check(const moe_ep_peers* P, int rank, int world) {
+    if (!P) return fail(MOE_ERR_INVALID, "peers is NULL");
+    if (world < 1 || world > EP_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(MOE_ERR_INVALID, "world=%d must be in [1, %d] and rank=%d inside it", world, EP_MAX_WORLD, rank);
+    for (int i = 0; i < world; ++i)
+        if (!P->a[i] || !P->sa[i] || !P->y[i] || !P->counts[i] || !P->flags[i])
+            return fail(MOE_ERR_INVALID, "peer table entry %d has a NULL pointer", i);
+    return MOE_OK;
+}
+static EpPeers ep_convert(const moe_ep_peers* P) {
+    EpPeers d;
+    for (int i = 0; i < EP_MAX_WORLD; ++i) {
+        d.a[i] = static_cast<uint8_t*>(P->a[i]);
+        d.sa[i] = P->sa[i];
+        d.y[i] = static_cast<const __nv_bfloat16*>(P->y[i]);
+        d.counts[i] = P->counts[i];
+        d.flags[i] = P->flags[i];
+    }
+    return d;
+}
+
+int moe_ep_barrier(const moe_ep_peers* P, int32_t rank, int32_t world, int32_t epoch, void* stream) {
+    int rc = ep_check(P, rank, world);
+    if (rc != MOE_OK) return rc;
+    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ep_convert(P), rank, world, epoch, status_ptr());
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+size_t moe_ep_workspace_bytes(int64_t n_pairs, int32_t E_total) {
+    return moe_permute_workspace_bytes(n_pairs, E_total) + align256((size_t)(E_total + 1) * 4);
+}
+
+int moe_ep_count_publish(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int32_t rank, int32_t world,
+                         int32_t E_total, int32_t* my_counts, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = ep_check(P, rank, world);
+    if (rc != MOE_OK) return rc;
+    rc = check_plan_args(n_pairs, E_total, 1, 0);
+    if (rc != MOE_OK) return rc;
+    if (!ids || !my_counts || !workspace) return fail(MOE_ERR_INVALID, "ids, my_counts and workspace must be non-NULL");
+    if (workspace_bytes < moe_ep_workspace_bytes(n_pairs, E_total)) return fail(MOE_ERR_INVALID, "EP workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* chunk_counts = static_cast<int*>(workspace);
+    int* scratch_offsets = reinterpret_cast<int*>(static_cast<char*>(workspace) + moe_permute_workspace_bytes(n_pairs, E_total));
+    const int n_chunks = (int)((n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK);
+    if (n_chunks > 0) {
+        plan_count_kernel<<<n_chunks, PLAN_CHUNK, (size_t)32 * E_total * 4, st>>>(ids, n_pairs, 0, E_total, chunk_counts);
+        CUDA_TRY(cudaGetLastError());
+    }
+    plan_scan_kernel<<<1, 256, (size_t)E_total * 4, st>>>(chunk_counts, n_chunks, E_total, 1, my_counts, scratch_offsets);
+    CUDA_TRY(cudaGetLastError());
+    ep_publish_counts_kernel<<<1, 256, 0, st>>>(ep_convert(P), my_counts, rank, world, E_total);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int32_t rank, int32_t world,
+                int32_t E_total, int32_t E_local, int32_t align, int32_t cap_rows, int32_t* counts_local,
+                int32_t* offsets, int32_t* grouped_layout, int32_t* dst_base, int32_t* pos, void* workspace,
+                size_t workspace_bytes, void* stream) {
+    int rc = ep_check(P, rank, world);
+    if (rc != MOE_OK) return rc;
+    rc = check_plan_args(n_pairs, E_total, align, cap_rows);
+    if (rc != MOE_OK) return rc;
+    if (E_local * world != E_total) return fail(MOE_ERR_INVALID, "E_total must equal world * E_local");
+    if (!ids || !counts_local || !offsets || !grouped_layout || !dst_base || !pos || !workspace)
+        return fail(MOE_ERR_INVALID, "plan pointers must be non-NULL");
+    if (workspace_bytes < moe_ep_workspace_bytes(n_pairs, E_total)) return fail(MOE_ERR_INVALID, "EP workspace too small");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int* chunk_offsets = static_cast<const int*>(workspace);      // left by moe_ep_count_publish
+    ep_plan_kernel<<<1, 256, (size_t)2 * E_total * 4, st>>>(P->counts[rank], rank, world, E_total, E_local, align,
+                                                          counts_local, offsets, dst_base);
+    CUDA_TRY(cudaGetLastError());
+    ep_layout_kernel<<<(cap_rows + 1023) / 1024, 1024, 0, st>>>(offsets, counts_local, E_local, grouped_layout, cap_rows);
+    CUDA_TRY(cudaGetLastError());
+    const int n_chunks = (int)((n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK);
+    if (n_chunks > 0) {
+        // cap = INT_MAX: destination rows live in the owners' buffers; the owner bounds them by its own capacity
+        plan_place_kernel<<<n_chunks, PLAN_CHUNK, (size_t)32 * E_total * 4, st>>>(
+            ids, n_pairs, 0, E_total, chunk_offsets, nullptr, dst_base, pos, nullptr, nullptr, 0x7FFFFFFF);
+        CUDA_TRY(cudaGetLastError());
+    }
+    return MOE_OK;
+}
+
+int moe_ep_dispatch(const moe_ep_peers* P, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
+                    const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
+                    int32_t cap_rows, int32_t world, void* stream) {
+    int rc = ep_check(P, 0, world);
+    if (rc != MOE_OK) return rc;
+    if (!x_q || !x_scale || !ids || !pos) return fail(MOE_ERR_INVALID, "dispatch pointers must be non-NULL");
+    if (H <= 0 || H % 128 || top_k <= 0 || E_local <= 0) return fail(MOE_ERR_INVALID, "H must be a multiple of 128; top_k, E_local positive");
+    if (n_pairs <= 0) return n_pairs == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "n_pairs must be non-negative");
+    const int wpb = 8;
+    ep_dispatch_kernel<<<(unsigned)((n_pairs + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        ep_convert(P), static_cast<const uint8_t*>(x_q), x_scale, xs_row, xs_blk, ids, pos, n_pairs, top_k, E_local, H,
+        cap_rows);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_ep_combine(const moe_ep_peers* P, const int32_t* ids, const int32_t* pos, const float* w, void* out_bf16,
+                   int32_t T, int32_t top_k, int32_t E_local, int32_t H, int32_t world, void* stream) {
+    int rc = ep_check(P, 0, world);
+    if (rc != MOE_OK) return rc;
+    if (!ids || !pos || !w || !out_bf16) return fail(MOE_ERR_INVALID, "combine pointers must be non-NULL");
+    if (H <= 0 || H % 8 || top_k <= 0 || top_k > 32) return fail(MOE_ERR_INVALID, "H must be a multiple of 8 and top_k in [1, 32]");
+    if (T <= 0) return T == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "T must be non-negative");
+    ep_combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(ep_convert(P), ids, pos, w,
+                                                                        static_cast<__nv_bfloat16*>(out_bf16), T, top_k,
+                                                                        E_local, H);
+    CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
 

@@ -9,6 +9,9 @@
 //   warp 1        MMA issuer: four tcgen05.mma (128 x 256 x 32) per K block into one of two
 //                 256-column TMEM accumulators; tcgen05.commit releases the smem stage and
 //                 publishes the accumulator
+//   warp 2        scale loader: per K block the 128 row scales of the tile and the two 128x128
+//                 block scales go from global memory into an 8-slot shared-memory ring, several
+//                 blocks ahead of their use, so the promotion never waits on L2 latency
 //   warps 4..11   two promotion/epilogue warpgroups (128 columns each): per K block they drain
 //                 the TMEM accumulator (tcgen05.ld), apply the block scales
 //                 acc += partial * (sfa * sfb) in registers, hand the TMEM buffer back, and after
@@ -37,8 +40,13 @@ constexpr int B_STAGE_BYTES = BN * BK;             // 32 KB
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_MASKED_GROUPS = 1024;
 constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
-// tiles + barriers/bookkeeping + masked-layout prefix table + slack for 1024-byte alignment
-constexpr int SMEM_BYTES = SMEM_TILE_BYTES + 256 + (MAX_MASKED_GROUPS + 1) * 4 + 1024;
+constexpr int SF_SLOTS = 8;                        // scale ring: per slot 128 row scales + 2 block scales
+constexpr int SF_SLOT_FLOATS = 132;
+constexpr int OFF_BARS = SMEM_TILE_BYTES;          // mbarriers, TMEM base, abort flag
+constexpr int OFF_SF = OFF_BARS + 512;
+constexpr int OFF_PREFIX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;
+// + masked-layout prefix table + slack for 1024-byte alignment
+constexpr int SMEM_BYTES = OFF_PREFIX + (MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
 }  // namespace gg
 
 struct GGParams {
@@ -46,6 +54,7 @@ struct GGParams {
     long long sfa_sr, sfa_sk;
     const float* sfb;            // [G][nb128][KB]
     const int* layout;           // grouped_layout[M] or masked_m[G]
+    const int* rows_used;        // contiguous, optional: device count of leading rows in use (<= M)
     void* d;                     // bf16 (or fp32 when d_f32 != 0)
     long long ldd;
     int d_f32;
@@ -92,7 +101,17 @@ struct Scheduler {
 
     __device__ __forceinline__ Scheduler(const GGParams& p_, const int* prefix_, int lane_)
         : p(p_), prefix(prefix_), t(blockIdx.x), lane(lane_), prev_g(-1) {
-        total = MASKED ? prefix_[p_.G] * p_.num_n_blocks : p_.num_m_blocks * p_.num_n_blocks;
+        if (MASKED) {
+            total = prefix_[p_.G] * p_.num_n_blocks;
+        } else {
+            int m_blocks = p_.num_m_blocks;
+            if (p_.rows_used != nullptr) {       // only the leading rows hold data: skip the rest outright
+                int used = __ldg(p_.rows_used);
+                used = used < 0 ? 0 : (used > p_.M ? p_.M : used);
+                m_blocks = (used + gg::BM - 1) / gg::BM;
+            }
+            total = m_blocks * p_.num_n_blocks;
+        }
     }
 
     __device__ __forceinline__ bool next(Tile& tile) {
@@ -144,11 +163,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty,
+    // then SF_SLOTS scale-full and SF_SLOTS scale-empty barriers
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-    int* prefix = reinterpret_cast<int*>(smem + SMEM_TILE_BYTES + 256);
+    float* sf_ring = reinterpret_cast<float*>(smem + OFF_SF);
+    int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -157,6 +178,8 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const uint32_t empty_bar = smem_u32(bars + STAGES);
     const uint32_t tfull_bar = smem_u32(bars + 2 * STAGES);
     const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + ACC_STAGES);
+    const uint32_t sffull_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES);
+    const uint32_t sfempty_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES + SF_SLOTS);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -167,6 +190,10 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             mbar_init(tfull_bar + 8 * s, 1);
             mbar_init(tempty_bar + 8 * s, 8);     // one arrival per epilogue warp
         }
+        for (int s = 0; s < SF_SLOTS; ++s) {
+            mbar_init(sffull_bar + 8 * s, 32);    // every lane of the loader warp arrives
+            mbar_init(sfempty_bar + 8 * s, 8);    // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
@@ -174,7 +201,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
     if (MASKED) {
         // prefix[g] = number of 128-row blocks of groups < g  (G <= MAX_MASKED_GROUPS)
-        if (warp == 2) {
+        if (warp == 3) {
             int running = 0;
             for (int base = 0; base < p.G; base += 32) {
                 int g = base + lane;
@@ -208,7 +235,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const int KB = p.num_k_blocks;
 
     if (warp < 4) {
-        setmaxnreg_dec<40>();
+        setmaxnreg_dec<88>();
         if (warp == 0) {
             // ------------------------------------------------ TMA producer
             Scheduler<MASKED> sched(p, prefix, lane);
@@ -277,17 +304,61 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                 }
             }
+        } else if (warp == 2) {
+            // ------------------------------------------------ scale loader
+            Scheduler<MASKED> sched(p, prefix, lane);
+            Tile tile;
+            uint32_t slot = 0, sphase = 0;
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                const float* rp[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int r = tile.m0 + lane + 32 * j;
+                    if (r >= p.rows_total) r = p.rows_total - 1;
+                    rp[j] = p.sfa + (long long)r * p.sfa_sr;
+                }
+                int nb = ((tile.n_blk * BN) >> 7) + (lane & 1);
+                if (nb >= p.nb128) nb = p.nb128 - 1;
+                const float* bp = p.sfb + ((long long)tile.g * p.nb128 + nb) * KB;
+                for (int kb0 = 0; kb0 < KB && ok; kb0 += 4) {
+                    float v[4][4], b[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (kb0 + u < KB) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[u][j] = __ldg(rp[j] + (long long)(kb0 + u) * p.sfa_sk);
+                            b[u] = __ldg(bp + kb0 + u);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (ok && kb0 + u < KB) {
+                            ok = mbar_wait_warp(sfempty_bar + 8 * slot, sphase ^ 1, abort_flag, status,
+                                                STATUS_TIMEOUT_SF_EMPTY);
+                            if (ok) {
+                                float* dst = sf_ring + slot * SF_SLOT_FLOATS;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = v[u][j];
+                                if (lane < 2) dst[128 + lane] = b[u];
+                                mbar_arrive(sffull_bar + 8 * slot);
+                                if (++slot == SF_SLOTS) { slot = 0; sphase ^= 1; }
+                            }
+                        }
+                    }
+                }
+            }
         }
     } else {
         // ---------------------------------------------------- promotion + epilogue
-        setmaxnreg_inc<216>();
+        setmaxnreg_inc<208>();
         const int ew = warp - 4;
         const int quarter = warp & 3;                 // TMEM lanes this warp may touch
         const int half = ew >> 2;                     // which 128 columns of the 256-wide tile
         const int row_in_tile = quarter * 32 + lane;
         Scheduler<MASKED> sched(p, prefix, lane);
         Tile tile;
-        uint32_t acc = 0, acc_phase = 0;
+        uint32_t acc = 0, acc_phase = 0, slot = 0, sphase = 0;
         bool ok = true;
         while (ok && sched.next(tile)) {
             const int n0 = tile.n_blk * BN + half * 128;
@@ -295,49 +366,49 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             bool row_valid;
             if (MASKED) row_valid = row_in_tile < tile.rows;
             else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
-            const int srow = row < p.rows_total ? row : p.rows_total - 1;
-            const float* sfa_ptr = p.sfa + (long long)srow * p.sfa_sr;
-            int nb = n0 >> 7;
-            if (nb >= p.nb128) nb = p.nb128 - 1;
-            const float* sfb_ptr = p.sfb + ((long long)tile.g * p.nb128 + nb) * KB;
-
-            float accr[128];
+            unsigned long long accr[64];          // 128 fp32 accumulators as f32x2 pairs
 #pragma unroll
-            for (int j = 0; j < 128; ++j) accr[j] = 0.0f;
+            for (int j = 0; j < 64; ++j) accr[j] = 0ull;
 
-            float sa = __ldg(sfa_ptr), sb = __ldg(sfb_ptr);
             for (int kb = 0; kb < KB; ++kb) {
-                const float s = sa * sb;
-                if (kb + 1 < KB) {             // prefetch the next block's scales behind the wait
-                    sa = __ldg(sfa_ptr + (long long)(kb + 1) * p.sfa_sk);
-                    sb = __ldg(sfb_ptr + kb + 1);
-                }
+                ok = mbar_wait_warp(sffull_bar + 8 * slot, sphase, abort_flag, status, STATUS_TIMEOUT_SF_FULL);
+                if (!ok) break;
+                const float* sfp = sf_ring + slot * SF_SLOT_FLOATS;
+                const float s = sfp[row_in_tile] * sfp[128 + half];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sfempty_bar + 8 * slot);
+                if (++slot == SF_SLOTS) { slot = 0; sphase ^= 1; }
+                const unsigned long long s2 = pack_f32x2(s, s);
+
                 ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status,
                                     STATUS_TIMEOUT_TMEM_FULL);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + half * 128;
-                uint32_t v0[32], v1[32];
-                tmem_ld_32x32b_x32(taddr, v0);
-                tmem_ld_wait(v0);
-                tmem_ld_32x32b_x32(taddr + 32, v1);
+                // eight 16-column chunks, double-buffered: chunk c+1 is in flight while chunk c is
+                // multiplied in (two fp32 FMAs per instruction)
+                uint32_t v0[16], v1[16];
+                tmem_ld_32x32b_x16(taddr, v0);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) accr[j] = fmaf(__uint_as_float(v0[j]), s, accr[j]);
-                tmem_ld_wait(v1);
-                tmem_ld_32x32b_x32(taddr + 64, v0);
+                for (int c = 0; c < 8; c += 2) {
+                    tmem_ld_wait(v0);
+                    tmem_ld_32x32b_x16(taddr + (c + 1) * 16, v1);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) accr[32 + j] = fmaf(__uint_as_float(v1[j]), s, accr[32 + j]);
-                tmem_ld_wait(v0);
-                tmem_ld_32x32b_x32(taddr + 96, v1);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) accr[64 + j] = fmaf(__uint_as_float(v0[j]), s, accr[64 + j]);
-                tmem_ld_wait(v1);
-                // all four loads have landed: hand the accumulator back to the MMA warp
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[c * 8 + j], v0[2 * j], v0[2 * j + 1], s2);
+                    tmem_ld_wait(v1);
+                    if (c + 2 < 8) {
+                        tmem_ld_32x32b_x16(taddr + (c + 2) * 16, v0);
+                    } else {
+                        // all loads have landed: hand the accumulator back to the MMA warp
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+                    }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) accr[96 + j] = fmaf(__uint_as_float(v1[j]), s, accr[96 + j]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[(c + 1) * 8 + j], v1[2 * j], v1[2 * j + 1], s2);
+                }
                 if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
             }
             if (!ok) break;
@@ -345,8 +416,12 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
                 for (int j = 0; j < 128; j += 4) {
-                    if (n0 + j + 4 <= p.N)
-                        *reinterpret_cast<float4*>(drow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+                    if (n0 + j + 4 <= p.N) {
+                        float4 o;
+                        unpack_f32x2(accr[j / 2], o.x, o.y);
+                        unpack_f32x2(accr[j / 2 + 1], o.z, o.w);
+                        *reinterpret_cast<float4*>(drow + j) = o;
+                    }
                 }
             } else if (row_valid) {
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
@@ -354,14 +429,10 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 for (int j = 0; j < 128; j += 8) {
                     if (n0 + j + 8 <= p.N) {
                         uint4 out;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(accr[j + 0], accr[j + 1]);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(accr[j + 2], accr[j + 3]);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(accr[j + 4], accr[j + 5]);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(accr[j + 6], accr[j + 7]);
-                        out.x = *reinterpret_cast<uint32_t*>(&h0);
-                        out.y = *reinterpret_cast<uint32_t*>(&h1);
-                        out.z = *reinterpret_cast<uint32_t*>(&h2);
-                        out.w = *reinterpret_cast<uint32_t*>(&h3);
+                        out.x = cvt_bf16x2(accr[j / 2 + 0]);
+                        out.y = cvt_bf16x2(accr[j / 2 + 1]);
+                        out.z = cvt_bf16x2(accr[j / 2 + 2]);
+                        out.w = cvt_bf16x2(accr[j / 2 + 3]);
                         *reinterpret_cast<uint4*>(drow + j) = out;
                     }
                 }

@@ -234,11 +234,13 @@ __global__ void plan_place_kernel(const int* __restrict__ ids, long long n_pairs
         int row = -1;
         if (e >= 0) {
             row = offsets[e] + chunk_offsets[(long long)blockIdx.x * E + e] + hist[(threadIdx.x >> 5) * E + e] + rank;
-            if (row < cap_rows) src_pair[row] = (int)p; else row = -1;
+            if (row >= cap_rows) row = -1;
+            else if (src_pair != nullptr) src_pair[row] = (int)p;
         }
         pos[p] = row;
     }
     // grouped_layout / src_pair of padding rows: grid-stride over all capacity rows
+    if (grouped_layout == nullptr) return;
     const int total = offsets[E];
     for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < cap_rows;
          r += (long long)gridDim.x * blockDim.x) {
@@ -252,7 +254,7 @@ __global__ void plan_place_kernel(const int* __restrict__ ids, long long n_pairs
             if (r - offsets[lo] < counts[lo]) g = lo;
         }
         grouped_layout[r] = g;
-        if (g < 0) src_pair[r] = -1;
+        if (g < 0 && src_pair != nullptr) src_pair[r] = -1;
     }
 }
 
@@ -298,6 +300,182 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ y, const int* _
             if (r < 0) continue;
             const float wj = s_w[j];
             const uint4 raw = __ldg(reinterpret_cast<const uint4*>(y + (long long)r * H) + c);
+            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(wj, __uint_as_float(u[i] << 16)));
+                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(wj, __uint_as_float(u[i] & 0xFFFF0000u)));
+            }
+        }
+        uint4 o;
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+        reinterpret_cast<uint4*>(out + (long long)t * H)[c] = o;
+    }
+}
+
+}  // namespace b200
+
+// ====================================================================== expert parallelism
+// One process per GPU.  Every rank owns E_local consecutive experts and a slice of the tokens.
+// Receive buffers live in peer-mapped ("symmetric") memory: a rank's dispatch kernel STORES token
+// rows straight into the owner rank's grouped-layout A buffer over NVLink, and the combine kernel
+// LOADS the expert outputs it needs from the owners' Y buffers while it forms the weighted sum.
+// No TMA touches peer memory; all peer traffic is plain 16-byte loads/stores.
+namespace b200 {
+
+constexpr int EP_MAX_WORLD = 8;
+
+struct EpPeers {
+    uint8_t* a[EP_MAX_WORLD];            // e4m3 [cap_rows, H] receive buffer of each rank
+    float* sa[EP_MAX_WORLD];             // f32 [H/128, cap_rows] (MN-major) scales of each rank
+    const __nv_bfloat16* y[EP_MAX_WORLD];// bf16 [cap_rows, H] expert outputs of each rank
+    int* counts[EP_MAX_WORLD];           // int32 [world, E_total]: row s = pairs rank s routes to each expert
+    int* flags[EP_MAX_WORLD];            // int32 [world]: barrier epochs written by each peer
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Cross-GPU barrier: thread s publishes `epoch` into peer s's flag slot for this rank, then waits
+// (bounded: 2 s) until peer s's epoch shows up in the local slot.  Launched after the kernel whose
+// peer stores must be visible; __threadfence_system orders them before the flag.
+__global__ void ep_barrier_kernel(EpPeers peers, int rank, int world, int epoch, int* status) {
+    const int s = threadIdx.x;
+    if (s >= world) return;
+    __threadfence_system();
+    st_release_sys(peers.flags[s] + rank, epoch);
+    const int* mine = peers.flags[rank] + s;
+    const uint64_t t0 = globaltimer_ns();
+    while (ld_acquire_sys(mine) < epoch) {
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            atomicOr(status, STATUS_TIMEOUT_PEER_FLAG);
+            break;
+        }
+    }
+}
+
+// Publishes this rank's per-expert pair counts (E_total ints) into row `rank` of every peer's table.
+__global__ void ep_publish_counts_kernel(EpPeers peers, const int* __restrict__ my_counts, int rank,
+                                         int world, int E_total) {
+    for (int i = threadIdx.x; i < world * E_total; i += blockDim.x) {
+        const int d = i / E_total, e = i % E_total;
+        peers.counts[d][rank * E_total + e] = my_counts[e];
+    }
+}
+
+// From the gathered table counts_all[world][E_total] (local copy) derive, in one block:
+//   recv side: offsets[E_local+1] of this rank's experts (each padded to `align` rows)
+//   send side: dst_base[E_total] = first destination row, in the owner's buffer, of this rank's
+//              pairs for expert e (owner's expert start + rows of lower-ranked senders)
+__global__ void ep_plan_kernel(const int* __restrict__ counts_all, int rank, int world, int E_total,
+                               int E_local, int align, int* __restrict__ counts_local,
+                               int* __restrict__ offsets, int* __restrict__ dst_base) {
+    extern __shared__ int sh[];           // total[E_total], start[E_total]
+    int* total = sh;
+    int* start = sh + E_total;
+    for (int e = threadIdx.x; e < E_total; e += blockDim.x) {
+        int t = 0;
+        for (int s = 0; s < world; ++s) t += counts_all[s * E_total + e];
+        total[e] = t;
+    }
+    __syncthreads();
+    // per owner rank: exclusive scan of aligned totals over its E_local experts
+    for (int d = threadIdx.x; d < world; d += blockDim.x) {
+        int run = 0;
+        for (int j = 0; j < E_local; ++j) {
+            const int e = d * E_local + j;
+            start[e] = run;
+            run += (total[e] + align - 1) / align * align;
+        }
+        if (d == rank) offsets[E_local] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E_total; e += blockDim.x) {
+        int before = 0;
+        for (int s = 0; s < rank; ++s) before += counts_all[s * E_total + e];
+        dst_base[e] = start[e] + before;
+        if (e / E_local == rank) {
+            offsets[e - rank * E_local] = start[e];
+            counts_local[e - rank * E_local] = total[e];
+        }
+    }
+}
+
+// grouped_layout of the receive buffer: row r belongs to local expert e iff
+// offsets[e] <= r < offsets[e] + counts_local[e]; everything else is padding (-1).
+__global__ void ep_layout_kernel(const int* __restrict__ offsets, const int* __restrict__ counts_local,
+                                 int E_local, int* __restrict__ grouped_layout, int cap_rows) {
+    const int total = offsets[E_local];
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < cap_rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        int g = -1;
+        if (r < total) {
+            int lo = 0, hi = E_local;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (offsets[mid] <= r) lo = mid; else hi = mid;
+            }
+            if (r - offsets[lo] < counts_local[lo]) g = lo;
+        }
+        grouped_layout[r] = g;
+    }
+}
+
+// Dispatch: pair p = t*top_k + j goes to row pos[p] of the rank that owns expert ids[p].
+// One warp per pair: H bytes of e4m3 + H/128 scales stored into the owner's buffers.
+__global__ void ep_dispatch_kernel(EpPeers peers, const uint8_t* __restrict__ x, const float* __restrict__ xs,
+                                   long long xs_r, long long xs_b, const int* __restrict__ ids,
+                                   const int* __restrict__ pos, long long n_pairs, int top_k, int E_local,
+                                   int H, int cap_rows) {
+    const long long p = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (p >= n_pairs) return;
+    const int row = __ldg(pos + p);
+    if (row < 0 || row >= cap_rows) return;
+    const int d = __ldg(ids + p) / E_local;
+    const long long t = p / top_k;
+    const uint4* src = reinterpret_cast<const uint4*>(x + t * H);
+    uint4* dst = reinterpret_cast<uint4*>(peers.a[d] + (long long)row * H);
+    for (int i = lane; i < (H >> 4); i += 32) dst[i] = __ldg(src + i);
+    float* sdst = peers.sa[d];
+    for (int b = lane; b < (H >> 7); b += 32) sdst[(long long)b * cap_rows + row] = __ldg(xs + t * xs_r + b * xs_b);
+}
+
+// Combine: out[t,:] = bf16( sum_j w[t,j] * Y_owner(ids[t,j])[pos[t,j], :] ), rows fetched from the
+// owners' buffers with 16-byte peer loads; fp32 multiply then add in slot order.
+__global__ void ep_combine_kernel(EpPeers peers, const int* __restrict__ ids, const int* __restrict__ pos,
+                                  const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int T, int top_k,
+                                  int E_local, int H) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    __shared__ const __nv_bfloat16* s_row[32];
+    __shared__ float s_w[32];
+    if (threadIdx.x < top_k) {
+        const int r = pos[(long long)t * top_k + threadIdx.x];
+        const int d = ids[(long long)t * top_k + threadIdx.x] / E_local;
+        s_row[threadIdx.x] = r < 0 ? nullptr : peers.y[d] + (long long)r * H;
+        s_w[threadIdx.x] = w[(long long)t * top_k + threadIdx.x];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int j = 0; j < top_k; ++j) {
+            const __nv_bfloat16* rp = s_row[j];
+            if (rp == nullptr) continue;
+            const float wj = s_w[j];
+            const uint4 raw = *(reinterpret_cast<const uint4*>(rp) + c);
             const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {

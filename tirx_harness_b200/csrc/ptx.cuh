@@ -16,6 +16,8 @@ enum : int {
     STATUS_TIMEOUT_TMEM_FULL = 1 << 2,    // epilogue: accumulator never completed
     STATUS_TIMEOUT_TMEM_EMPTY = 1 << 3,   // MMA warp: accumulator never drained
     STATUS_TIMEOUT_PEER_FLAG = 1 << 4,    // exchange kernels: a peer flag never arrived
+    STATUS_TIMEOUT_SF_FULL = 1 << 5,      // epilogue: block scales never arrived in shared memory
+    STATUS_TIMEOUT_SF_EMPTY = 1 << 6,     // scale loader: ring slot never released
     STATUS_BAD_ARGUMENT = 1 << 8,
 };
 
@@ -188,6 +190,54 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
 // operands so that no use of them can be scheduled above the wait.
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" : B200_RW32(v)::"memory");
+}
+
+// 16-column variants (half the registers in flight)
+#define B200_R16(v)                                                                               \
+    "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),          \
+    "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),      \
+    "=r"(v[14]), "=r"(v[15])
+#define B200_RW16(v)                                                                              \
+    "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),          \
+    "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]),      \
+    "+r"(v[14]), "+r"(v[15])
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : B200_R16(v)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : B200_RW16(v)::"memory");
+}
+
+// ------------------------------------------------------------------ packed fp32 pairs
+// sm_100 executes two fp32 FMAs per lane per instruction on 64-bit register pairs.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// acc = {v0, v1} * s2 + acc, each half rounded to nearest even like fmaf
+__device__ __forceinline__ void fma_f32x2(unsigned long long& acc, uint32_t v0, uint32_t v1,
+                                          unsigned long long s2) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(v0), "r"(v1));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(s2));
+}
+
+// {lo, hi} fp32 pair -> packed bf16x2 (lo in the low half), round to nearest even
+__device__ __forceinline__ uint32_t cvt_bf16x2(unsigned long long v) {
+    float lo, hi;
+    unpack_f32x2(v, lo, hi);
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 
 // ------------------------------------------------------------------ register budget

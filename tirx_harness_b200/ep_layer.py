@@ -1,0 +1,195 @@
+"""Expert-parallel MoE layer: one process per GPU, experts sharded, tokens sharded.
+
+    layer = EpMoeLayer(data, T_local, top_k=8)      # collective: every rank of the group calls it
+    layer()                                          # one forward on the current stream
+
+Rank r owns experts [r*E_local, (r+1)*E_local) with their weights resident and T_local tokens.
+Per forward: route -> publish per-expert counts to all peers -> barrier -> plan -> dispatch (rows are
+stored straight into the owner's grouped-layout buffer over NVLink) -> barrier -> gate_up grouped GEMM
+-> SiLU*mul requant -> down grouped GEMM -> barrier -> combine (each token loads its expert rows from
+the owners' buffers and forms the weighted sum).  The reference emulates this sharding on one GPU
+with ``local_expert_offset`` (mlc-ai/TIRx-harness: evolution/benchmark/flashinfer_bench_evolve/tasks/
+moe/definition.json); with world size 1 this class computes exactly what ``moe_layer.MoeLayer`` does.
+
+torch.distributed is used only to exchange the 64-byte IPC handles at set-up; the data path is this
+library's own kernels over peer-mapped memory, synchronised by a bounded flag barrier.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib, grouped_gemm
+
+_vp = ctypes.c_void_p
+_i32 = ctypes.c_int32
+_i64 = ctypes.c_int64
+
+
+def _a256(n: int) -> int:
+    return (n + 255) // 256 * 256
+
+
+class SymmetricBuffer:
+    """One IPC-exportable allocation per rank, mapped by every other rank of the node."""
+
+    def __init__(self, nbytes: int, group=None):
+        import torch.distributed as dist
+        self.L = _lib.lib()
+        self.nbytes = nbytes
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        p = _vp()
+        _lib.check(self.L.moe_ipc_alloc(ctypes.c_size_t(nbytes), ctypes.byref(p)))
+        self.local = p.value
+        self.ptrs = [None] * self.world
+        self.ptrs[self.rank] = self.local
+        self._opened = []
+        if self.world > 1:
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(self.L.moe_ipc_get_handle(_vp(self.local), handle))
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, bytes(handle.raw), group=group)
+            for r, h in enumerate(gathered):
+                if r == self.rank:
+                    continue
+                q = _vp()
+                _lib.check(self.L.moe_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(q)))
+                self.ptrs[r] = q.value
+                self._opened.append(q.value)
+
+    def close(self):
+        torch.cuda.synchronize()
+        for q in self._opened:
+            self.L.moe_ipc_close(_vp(q))
+        self._opened = []
+        if self.local:
+            self.L.moe_ipc_free(_vp(self.local))
+            self.local = None
+
+
+class EpMoeLayer:
+    def __init__(self, data: dict, T_local: int, top_k: int = 8, align: int = 128, gate_first: bool = False,
+                 group=None):
+        import torch.distributed as dist
+        self.L = _lib.lib()
+        x_q, xs = data["hidden_states"], data["hidden_states_scale"]
+        self.logits = data["routing_logits"]
+        w13, s13 = data["gemm1_weights"], data["gemm1_weights_scale"].contiguous()
+        w2, s2 = data["gemm2_weights"], data["gemm2_weights_scale"].contiguous()
+        self.out = data["output"]
+        dev = x_q.device
+        self.device = dev
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one NVLink domain)")
+        H = x_q.shape[1]
+        E_local, two_i, _ = w13.shape
+        inter = two_i // 2
+        E_total = self.logits.shape[1]
+        if E_total != E_local * self.world:
+            raise ValueError(f"router has {E_total} experts but {self.world} ranks x {E_local} local experts")
+        if tuple(xs.shape) == (H // 128, T_local) and T_local != H // 128:
+            xs = xs.t()
+        if tuple(x_q.shape) != (T_local, H) or tuple(xs.shape) != (T_local, H // 128):
+            raise ValueError("hidden_states must be [T_local, H] with scales [T_local, H/128]")
+        self.x_q, self.xs, self.gate_first = x_q, xs, gate_first
+        self.T, self.H, self.I, self.E_local, self.E_total, self.top_k, self.align = T_local, H, inter, E_local, E_total, top_k, align
+        n_pairs = T_local * top_k
+        self.n_pairs = n_pairs
+        # worst case: every pair of every rank lands on this rank
+        cap = (n_pairs * self.world + align - 1) // align * align + E_local * align
+        self.cap = cap
+        # ---- symmetric region: a | sa | y | counts | flags
+        sizes = [cap * H, (H // 128) * cap * 4, cap * H * 2, self.world * E_total * 4, 256]
+        offs, o = [], 0
+        for s in sizes:
+            offs.append(o)
+            o += _a256(s)
+        with torch.cuda.device(dev):
+            self.symm = SymmetricBuffer(o, group)
+        self.peers = _lib.EpPeers()
+        for r in range(self.world):
+            base = self.symm.ptrs[r]
+            self.peers.a[r], self.peers.sa[r], self.peers.y[r] = base + offs[0], base + offs[1], base + offs[2]
+            self.peers.counts[r], self.peers.flags[r] = base + offs[3], base + offs[4]
+        self._local = dict(a=self.symm.local + offs[0], sa=self.symm.local + offs[1], y=self.symm.local + offs[2])
+        # ---- private scratch
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.ids = torch.empty((T_local, top_k), **i32)
+        self.weights = torch.empty((T_local, top_k), dtype=torch.float32, device=dev)
+        self.pos = torch.empty((T_local, top_k), **i32)
+        self.my_counts = torch.empty(E_total, **i32)
+        self.dst_base = torch.empty(E_total, **i32)
+        self.counts_local = torch.empty(E_local, **i32)
+        self.offsets = torch.empty(E_local + 1, **i32)
+        self.layout = torch.full((cap,), -1, **i32)
+        self.ws_bytes = self.L.moe_ep_workspace_bytes(_i64(n_pairs), _i32(E_total))
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
+        self.g1 = torch.empty((cap, two_i), dtype=torch.bfloat16, device=dev)
+        self.a2 = torch.empty((cap, inter), dtype=torch.float8_e4m3fn, device=dev)
+        self.s2 = torch.empty((inter // 128, cap), dtype=torch.float32, device=dev)
+        self._keep = (w13, s13, w2, s2)
+        # the grouped GEMMs see the symmetric buffers as ordinary tensors of this process
+        self.a1_t = self._wrap(self._local["a"], (cap, H), torch.uint8).view(torch.float8_e4m3fn)
+        self.s1_t = self._wrap(self._local["sa"], (H // 128, cap), torch.float32).t()
+        self.y_t = self._wrap(self._local["y"], (cap, H), torch.bfloat16)
+        rows_used = self.offsets[E_local:E_local + 1]
+        self.gemm1 = grouped_gemm.bind_contiguous(self.a1_t, self.s1_t, w13, s13, self.g1, self.layout, rows_used)
+        self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used)
+        self.epoch = 0
+        if self.world > 1:
+            dist.barrier(group)
+
+    def _wrap(self, ptr: int, shape, dtype):
+        """A torch tensor over raw device memory (no copy, no ownership)."""
+        n = 1
+        for s in shape:
+            n *= s
+        itemsize = torch.empty((), dtype=dtype).element_size()
+
+        class _Cai:
+            __cuda_array_interface__ = {"shape": (n * itemsize,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+        t = torch.as_tensor(_Cai(), device=self.device)
+        return t.view(dtype).view(shape)
+
+    def _barrier(self, st):
+        self.epoch += 1
+        _lib.check(self.L.moe_ep_barrier(ctypes.byref(self.peers), self.rank, self.world, self.epoch, st))
+
+    def __call__(self):
+        L, P = self.L, ctypes.byref(self.peers)
+        with torch.cuda.device(self.device):
+            st = _vp(torch.cuda.current_stream().cuda_stream)
+            _lib.check(L.moe_route_topk(_vp(self.logits.data_ptr()), _vp(self.ids.data_ptr()), _vp(self.weights.data_ptr()),
+                                        _i32(self.T), _i32(self.E_total), _i32(self.top_k), st))
+            _lib.check(L.moe_ep_count_publish(P, _vp(self.ids.data_ptr()), _i64(self.n_pairs), self.rank, self.world,
+                                              self.E_total, _vp(self.my_counts.data_ptr()), _vp(self.ws.data_ptr()),
+                                              ctypes.c_size_t(self.ws_bytes), st))
+            self._barrier(st)
+            _lib.check(L.moe_ep_plan(P, _vp(self.ids.data_ptr()), _i64(self.n_pairs), self.rank, self.world, self.E_total,
+                                     self.E_local, self.align, self.cap, _vp(self.counts_local.data_ptr()),
+                                     _vp(self.offsets.data_ptr()), _vp(self.layout.data_ptr()), _vp(self.dst_base.data_ptr()),
+                                     _vp(self.pos.data_ptr()), _vp(self.ws.data_ptr()), ctypes.c_size_t(self.ws_bytes), st))
+            _lib.check(L.moe_ep_dispatch(P, _vp(self.x_q.data_ptr()), _vp(self.xs.data_ptr()), _i64(self.xs.stride(0)),
+                                         _i64(self.xs.stride(1)), _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
+                                         _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap, self.world, st))
+            self._barrier(st)
+            self.gemm1()
+            _lib.check(L.moe_silu_mul_requant(_vp(self.g1.data_ptr()), _vp(self.a2.data_ptr()), _vp(self.s2.data_ptr()),
+                                              _i64(1), _i64(self.cap), _vp(self.layout.data_ptr()), _i32(self.cap),
+                                              _i32(self.I), _i32(1 if self.gate_first else 0), st))
+            self.gemm2()
+            self._barrier(st)
+            _lib.check(L.moe_ep_combine(P, _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()), _vp(self.weights.data_ptr()),
+                                        _vp(self.out.data_ptr()), self.T, self.top_k, self.E_local, self.H, self.world, st))
+        return self.out
+
+    def close(self):
+        self.symm.close()
+
+
+def setup(data: dict, T_local: int, **kw) -> EpMoeLayer:
+    return EpMoeLayer(data, T_local, **kw)

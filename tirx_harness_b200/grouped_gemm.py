@@ -42,14 +42,15 @@ def _scale_strides(sfa: torch.Tensor, rows: int, kblocks: int, name: str):
 class _BoundGG:
     """A validated argument block; ``__call__`` launches on the current stream of the tensors' device."""
 
-    def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K):
-        self._keep = (a, b, sfa, sfb, layout, d)
+    def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K, rows_used=None):
+        self._keep = (a, b, sfa, sfb, layout, d, rows_used)
         self._fn = getattr(_lib.lib(), fn_name)
         self._device = d.device
         self._args = _lib.GGArgs(
             a=_ptr(a), b=_ptr(b), sfa=_ptr(sfa), sfa_stride_row=sfa_strides[0], sfa_stride_kblk=sfa_strides[1],
             sfb=_ptr(sfb), layout=_ptr(layout), d=_ptr(d), ldd=d.stride(-2), G=G, M=M, N=N, K=K,
-            d_dtype=1 if d.dtype == torch.float32 else 0)
+            d_dtype=1 if d.dtype == torch.float32 else 0,
+            rows_used=_ptr(rows_used) if rows_used is not None else None)
         self._argp = ctypes.byref(self._args)
         self.out = d
 
@@ -60,9 +61,10 @@ class _BoundGG:
         return self.out
 
 
-def bind_contiguous(a, sfa, b, sfb, d, grouped_layout) -> _BoundGG:
+def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None) -> _BoundGG:
     """a fp8[M,K], sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128],
-    d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row)."""
+    d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row); rows_used: optional
+    int32[1] device tensor with the number of leading rows in use."""
     _check_fp8(a, "a"); _check_fp8(b, "b")
     M, K = a.shape
     G, N, Kb = b.shape
@@ -75,7 +77,9 @@ def bind_contiguous(a, sfa, b, sfb, d, grouped_layout) -> _BoundGG:
         raise ValueError(f"d must be bfloat16 (or float32) [{M}, {N}] with unit column stride")
     if grouped_layout.dtype != torch.int32 or grouped_layout.numel() != M or not grouped_layout.is_contiguous():
         raise ValueError(f"grouped_layout must be contiguous int32 [{M}]")
-    return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K)
+    if rows_used is not None and (rows_used.dtype != torch.int32 or not rows_used.is_cuda):
+        raise ValueError("rows_used must be an int32 CUDA tensor")
+    return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K, rows_used)
 
 
 def bind_masked(a, sfa, b, sfb, d, masked_m) -> _BoundGG:
