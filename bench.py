@@ -193,6 +193,116 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+LAYER = dict(T=16384, H=7168, I=2048, E=256, top_k=8,
+             desc="MoE layer forward, expert parallel: 16384 tokens, hidden 7168, 256 experts x intermediate 2048, "
+                  "softmax top-8; dispatch -> gate_up grouped GEMM -> SiLU*mul FP8 requant -> down grouped GEMM -> combine")
+
+
+def _layer_case(world, rank, device, cfg=LAYER, seed=0):
+    """This rank's token slice and experts (synthetic, generated on the device)."""
+    import torch
+    T, H, I, E = cfg["T"], cfg["H"], cfg["I"], cfg["E"]
+    Tl, El = T // world, E // world
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 1000 + rank)
+    hs = torch.randn((Tl, H), generator=gen, device=device).bfloat16()
+    from tirx_harness_b200 import moe_ops
+    xq, xs = moe_ops.quant_1x128(hs)
+
+    def weights(n, k):
+        nb, kb = n // 128, k // 128
+        sc = torch.exp2(torch.randint(-4, 1, (El, nb, kb), generator=gen, device=device).float())
+        w = torch.empty((El, n, k), dtype=torch.float8_e4m3fn, device=device)
+        for e in range(El):
+            x = torch.randn((n, k), generator=gen, device=device)
+            w[e] = (x / sc[e].repeat_interleave(128, 0).repeat_interleave(128, 1)).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        return w, sc * (0.5 / k ** 0.5)       # keeps activations O(1) through the layer
+    w13, s13 = weights(2 * I, H)
+    w2, s2 = weights(H, I)
+    logits = torch.randn((Tl, E), generator=gen, device=device)
+    return dict(hidden_states=xq, hidden_states_scale=xs, routing_logits=logits, gemm1_weights=w13,
+                gemm1_weights_scale=s13, gemm2_weights=w2, gemm2_weights_scale=s2,
+                output=torch.zeros((Tl, H), dtype=torch.bfloat16, device=device))
+
+
+def run_layer(args, world, rank, device, barrier, steps, warmup):
+    """Times the expert-parallel MoE layer: strong scaling, T fixed, value = tokens/s of the whole job."""
+    import torch
+    import torch.distributed as dist
+    from tirx_harness_b200 import ep_layer
+    from tirx_harness_b200 import grouped_gemm as gg
+    cfg = LAYER
+    data = _layer_case(world, rank, device)
+    Tl = cfg["T"] // world
+    layer = ep_layer.setup(data, Tl, top_k=cfg["top_k"])
+    for _ in range(max(warmup, 3)):
+        layer()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(device.index) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            layer()
+        e1.record()
+        barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    status = gg.device_status(device)
+    # per-stage device times on this rank (events between the stages of one forward, a few extra steps)
+    stages = layer.stage_times(5)
+    barrier()
+    counts = layer.counts_local.sum().item()
+    # end to end with host buffers: tokens in (fp8 + scales + logits), output back
+    hx = data["hidden_states"].view(torch.uint8).cpu().pin_memory()
+    hs_ = data["hidden_states_scale"].cpu().pin_memory()
+    hl = data["routing_logits"].cpu().pin_memory()
+    ho = torch.empty(data["output"].shape, dtype=torch.bfloat16).pin_memory()
+    dx8 = data["hidden_states"].view(torch.uint8)
+
+    def e2e_step():
+        dx8.copy_(hx, non_blocking=True)
+        data["hidden_states_scale"].copy_(hs_, non_blocking=True)
+        data["routing_logits"].copy_(hl, non_blocking=True)
+        layer()
+        ho.copy_(data["output"], non_blocking=True)
+    e2e_steps = max(3, min(steps, 10))
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+    H, I, k = cfg["H"], cfg["I"], cfg["top_k"]
+    flops = 2.0 * cfg["T"] * k * (2 * I * H + H * I)
+    res = {
+        "metric": "moe_layer_tokens_per_s", "value": cfg["T"] / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": cfg["desc"], "tokens_per_rank": Tl, "experts_per_rank": cfg["E"] // world,
+                   "routing": "softmax top-8, ties to lowest index, weights renormalised",
+                   "l2": "weights (1.4-11 GB per rank) larger than L2, no flush", "rows_this_rank": int(counts)},
+        "clocks": clocks.summary(),
+        "e2e": {"value": cfg["T"] / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": hx.numel() + hs_.numel() * 4 + hl.numel() * 4, "d2h_bytes_per_step": ho.numel() * 2,
+                "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "note": "per rank: fp8 tokens, scales and router logits copied from pinned host memory, bf16 output copied back"},
+        "gpu_launches": steps * 15,
+        "tflops_grouped_gemms": flops / (ms * 1e-3) / 1e12,
+        "stages_ms_rank0": {k: round(v, 4) for k, v in stages.items()},
+        "device_status": status,
+    }
+    layer.close()
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -213,6 +323,14 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.workload == "layer":
+        res = run_layer(args, world, rank, device, barrier, args.steps, args.warmup)
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     cfg = WORKLOADS[args.workload]
     data = _device_case(cfg, seed=rank, device=device)
@@ -308,6 +426,14 @@ def run_ours(args):
             cb = cpu_baseline(cfg)
             cb.pop("seconds", None)
             line["cpu_baseline"] = cb
+    layer_res = None
+    if args.with_layer:
+        del data, launch
+        torch.cuda.empty_cache()
+        layer_res = run_layer(args, world, rank, device, barrier, min(args.steps, 20), args.warmup)
+    if rank == 0:
+        if layer_res is not None:
+            line["moe_layer"] = layer_res
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -319,7 +445,9 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gemm")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["layer"], default="gemm")
+    ap.add_argument("--with-layer", action="store_true",
+                    help="after the grouped-GEMM measurement also time the expert-parallel MoE layer (extra object)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()

@@ -159,33 +159,61 @@ class EpMoeLayer:
         self.epoch += 1
         _lib.check(self.L.moe_ep_barrier(ctypes.byref(self.peers), self.rank, self.world, self.epoch, st))
 
-    def __call__(self):
+    def __call__(self, marks=None):
+        """One forward.  ``marks``: optional list; a (name, cuda event) pair is appended after every stage
+        (the benchmark's stage timing hook)."""
         L, P = self.L, ctypes.byref(self.peers)
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
         with torch.cuda.device(self.device):
             st = _vp(torch.cuda.current_stream().cuda_stream)
+            mark("start")
             _lib.check(L.moe_route_topk(_vp(self.logits.data_ptr()), _vp(self.ids.data_ptr()), _vp(self.weights.data_ptr()),
                                         _i32(self.T), _i32(self.E_total), _i32(self.top_k), st))
+            mark("route")
             _lib.check(L.moe_ep_count_publish(P, _vp(self.ids.data_ptr()), _i64(self.n_pairs), self.rank, self.world,
                                               self.E_total, _vp(self.my_counts.data_ptr()), _vp(self.ws.data_ptr()),
                                               ctypes.c_size_t(self.ws_bytes), st))
             self._barrier(st)
+            mark("counts+barrier")
             _lib.check(L.moe_ep_plan(P, _vp(self.ids.data_ptr()), _i64(self.n_pairs), self.rank, self.world, self.E_total,
                                      self.E_local, self.align, self.cap, _vp(self.counts_local.data_ptr()),
                                      _vp(self.offsets.data_ptr()), _vp(self.layout.data_ptr()), _vp(self.dst_base.data_ptr()),
                                      _vp(self.pos.data_ptr()), _vp(self.ws.data_ptr()), ctypes.c_size_t(self.ws_bytes), st))
+            mark("plan")
             _lib.check(L.moe_ep_dispatch(P, _vp(self.x_q.data_ptr()), _vp(self.xs.data_ptr()), _i64(self.xs.stride(0)),
                                          _i64(self.xs.stride(1)), _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
                                          _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap, self.world, st))
             self._barrier(st)
+            mark("dispatch+barrier")
             self.gemm1()
+            mark("gate_up_gemm")
             _lib.check(L.moe_silu_mul_requant(_vp(self.g1.data_ptr()), _vp(self.a2.data_ptr()), _vp(self.s2.data_ptr()),
                                               _i64(1), _i64(self.cap), _vp(self.layout.data_ptr()), _i32(self.cap),
                                               _i32(self.I), _i32(1 if self.gate_first else 0), st))
+            mark("silu_mul_requant")
             self.gemm2()
+            mark("down_gemm")
             self._barrier(st)
             _lib.check(L.moe_ep_combine(P, _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()), _vp(self.weights.data_ptr()),
                                         _vp(self.out.data_ptr()), self.T, self.top_k, self.E_local, self.H, self.world, st))
+            mark("barrier+combine")
         return self.out
+
+    def stage_times(self, steps: int = 5) -> dict:
+        """Median device time of every stage in ms (CUDA events between the stages; collective: all ranks call)."""
+        acc: dict = {}
+        for _ in range(steps):
+            marks: list = []
+            self(marks)
+            torch.cuda.synchronize(self.device)
+            for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
+                acc.setdefault(name, []).append(e0.elapsed_time(e1))
+        return {k: sorted(v)[len(v) // 2] for k, v in acc.items()}
 
     def close(self):
         self.symm.close()
