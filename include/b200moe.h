@@ -113,6 +113,25 @@ int moe_permute_plan(const int32_t* ids, int64_t n_pairs, int32_t e_lo, int32_t 
                      int32_t cap_rows, int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_pair,
                      int32_t* grouped_layout, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free form of moe_permute_plan.  It has no counterpart in the reference.
+ * Some hosts cannot give this library device memory at call time: a serving engine that reserved the
+ * whole GPU for its own pool at start-up, or a plugin host that forbids driver allocations once it is
+ * running (cudaMalloc may fail there, and it stalls the device while it runs).  For them the plan's
+ * only scratch, the per-chunk expert counters, lives in a 128 KiB array inside the library's device
+ * image; the call itself never allocates (no cudaMalloc/cudaFree, no torch or other allocating
+ * routine).  Inputs and outputs are still the caller's, with the same meaning as in moe_permute_plan.
+ * Limit: ceil(n_pairs / 1024) * E_local <= 32768 (for example 131072 pairs x 256 experts); larger
+ * requests return MOE_ERR_INVALID and leave the outputs untouched.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call during start-up, before any stream capture begins.
+ * All calls on a device share the one array.  Nothing in it has to be cleared between calls (every
+ * counter that is read is written first by the same call), but two calls whose kernels overlap on
+ * the GPU -- different streams, or different host threads -- race on it: serialise them.
+ * Every GPU that loads the library keeps the 128 KiB until the process exits. */
+int moe_permute_plan_static(const int32_t* ids, int64_t n_pairs, int32_t e_lo, int32_t E_local, int32_t align,
+                            int32_t cap_rows, int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_pair,
+                            int32_t* grouped_layout, void* stream);
+
 /* Row gather: for each row with src_pair >= 0 copies token (src_pair / top_k)'s e4m3 row (H bytes)
  * and its H/128 scales.  Source scale (t, b) at x_scale[t*xs_row + b*xs_blk]; destination
  * (row, b) at a_scale[row*as_row + b*as_blk]. */

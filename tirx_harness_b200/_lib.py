@@ -78,7 +78,8 @@ def lib():
 # every symbol include/b200moe.h declares
 EXPORTS = (
     "moe_gg_fp8_contiguous", "moe_gg_fp8_masked", "moe_quant_1x128", "moe_silu_mul_requant",
-    "moe_route_topk", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute", "moe_combine",
+    "moe_route_topk", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute_plan_static", "moe_permute",
+    "moe_combine",
     "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
     "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",
     "moe_ep_barrier", "moe_ep_workspace_bytes", "moe_ep_count_publish", "moe_ep_plan", "moe_ep_dispatch",

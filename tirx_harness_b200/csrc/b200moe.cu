@@ -555,6 +555,65 @@ int moe_ep_combine(const moe_ep_peers* P, const int32_t* ids, const int32_t* pos
     return MOE_OK;
 }
 
+/* ---------------------------------------------------------------- allocation-free permutation plan */
+
+// Scratch of moe_permute_plan_static: the per-chunk expert counters, kept in the library's own device
+// image instead of caller memory.  128 KiB per GPU that loads the library, held until the process exits.
+constexpr int kPlanStaticMaxInts = 32768;
+static __device__ __align__(256) int g_plan_static_scratch[kPlanStaticMaxInts];
+
+// The array's name is only a host-side handle; kernels need its device address, which is looked up
+// once per device (with that device current) and cached.
+static int plan_static_scratch(int** out) {
+    static int* ptrs[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MOE_ERR_INVALID, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        int* p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_plan_static_scratch));
+        if (p == nullptr) return fail(MOE_ERR_CUDA, "cudaGetSymbolAddress returned a NULL scratch address");
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return MOE_OK;
+}
+
+int moe_permute_plan_static(const int32_t* ids, int64_t n_pairs, int32_t e_lo, int32_t E_local, int32_t align,
+                            int32_t cap_rows, int32_t* counts, int32_t* offsets, int32_t* pos, int32_t* src_pair,
+                            int32_t* grouped_layout, void* stream) {
+    int rc = check_plan_args(n_pairs, E_local, align, cap_rows);
+    if (rc != MOE_OK) return rc;
+    if (!ids || !counts || !offsets || !pos || !src_pair || !grouped_layout)
+        return fail(MOE_ERR_INVALID, "all plan pointers must be non-NULL");
+    const int64_t n_chunks64 = (n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK;
+    if (n_chunks64 * (int64_t)E_local > kPlanStaticMaxInts)
+        return fail(MOE_ERR_INVALID,
+                    "moe_permute_plan_static: ceil(n_pairs/1024) * E_local = %lld exceeds the built-in scratch of %d "
+                    "counters (e.g. 131072 pairs x 256 experts); use moe_permute_plan with caller workspace",
+                    (long long)(n_chunks64 * E_local), kPlanStaticMaxInts);
+    int* chunk_counts = nullptr;
+    rc = plan_static_scratch(&chunk_counts);
+    if (rc != MOE_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int n_chunks = (int)n_chunks64;
+    const size_t hist_bytes = (size_t)32 * E_local * 4;
+    // Nothing in the scratch has to start at zero: the count kernel writes every counter the later
+    // kernels read, so contents left by an earlier call are simply overwritten.
+    if (n_chunks > 0) {
+        plan_count_kernel<<<n_chunks, PLAN_CHUNK, hist_bytes, st>>>(ids, n_pairs, e_lo, E_local, chunk_counts);
+        CUDA_TRY(cudaGetLastError());
+    }
+    plan_scan_kernel<<<1, 256, (size_t)E_local * 4, st>>>(chunk_counts, n_chunks, E_local, align, counts, offsets);
+    CUDA_TRY(cudaGetLastError());
+    plan_place_kernel<<<n_chunks > 0 ? n_chunks : 1, PLAN_CHUNK, hist_bytes, st>>>(
+        ids, n_pairs, e_lo, E_local, chunk_counts, counts, offsets, pos, src_pair, grouped_layout, cap_rows);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
 const char* moe_last_error(void) { return g_err; }
 const char* moe_version(void) { return "b200moe 0.1 sm_100a"; }
 
