@@ -412,7 +412,7 @@ def run_ours(args):
                        "timing": "CUDA events around K back-to-back launches, max over ranks"},
             "clocks": clocks.summary(),
             "e2e": e2e,
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * 3,      # per step: scale check+pack, block-scaled GEMM, promotion GEMM (exits at once when not needed)
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": per_gpu / fp8_peak, "traffic": traffic,
                          "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "

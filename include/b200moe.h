@@ -48,6 +48,12 @@ extern "C" {
  *   rows_used  contiguous layout only, may be NULL: device pointer to the number of leading rows of
  *           a/d that are in use (<= M).  Lets a fixed-capacity buffer be passed with M = capacity
  *           while the kernel only visits the rows a routing step actually filled.
+ *   workspace  may be NULL.  If given (256-byte aligned, >= moe_gg_workspace_bytes), each call first
+ *           checks on the device whether every scale is an exact power of two; if so the scales are
+ *           applied inside the tensor core (block-scaled MMA, CTA pairs) instead of by per-K-block
+ *           promotion -- same exact products, fp32 accumulation, about 1.5x faster.  Otherwise, and
+ *           always without workspace, the promotion kernel runs.  The decision is taken per call on
+ *           the device from the current scale values; nothing is cached between calls.
  * Requirements: K % 128 == 0, N % 8 == 0, a/b 16-byte aligned, d 16-byte aligned, ldd % 8 == 0.
  */
 typedef struct moe_gg_args {
@@ -63,7 +69,13 @@ typedef struct moe_gg_args {
     int32_t G, M, N, K;
     int32_t d_dtype;
     const int32_t* rows_used;
+    void* workspace;
+    uint64_t workspace_bytes;
 } moe_gg_args;
+
+/* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With
+ * args.workspace = NULL the GEMM always takes the promotion path. */
+size_t moe_gg_workspace_bytes(int32_t G, int64_t rows_total, int32_t N, int32_t K);
 
 /* Contiguous layout.  Stands in for the timed call of the registered workload
  * `grouped_gemm/fp8`: DeepGEMM m_grouped_fp8_gemm_nt_contiguous as launched by

@@ -230,3 +230,49 @@ def test_full_size_properties_config1(gg):
     torch.cuda.synchronize()
     assert torch.equal(D2[:mpg], D1[mpg:2 * mpg]) and torch.equal(D2[mpg:2 * mpg], D1[:mpg])
     assert torch.equal(D2[2 * mpg:], D1[2 * mpg:])
+
+
+def test_power_of_two_scale_path_equals_promotion_path(gg, monkeypatch):
+    """With 2^e scales the block-scaled-MMA path and the promotion path compute the same exact products in
+    fp32; both must sit within tolerance of the oracle and agree with each other to fp32 rounding.  With one
+    scale that is not a power of two the fast path must stand down (decided on the device, per call)."""
+    from tirx_harness_b200.workloads import make_contiguous_case
+    data = make_contiguous_case(3, [256, 130, 512], 768, 1024, seed=21, law="pow2")
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in data.items()}
+    gl = data["grouped_layout"].numpy()
+    valid = gl >= 0
+    ref32 = _oracle_contig(data, orc.SIM_CHAIN, out_f32=True)
+    outs = {}
+    for name, ws in (("mx", True), ("promote", False)):
+        d32 = torch.full(dev["D"].shape, float("nan"), dtype=torch.float32, device="cuda")
+        gg.bind_contiguous(dev["A"], dev["SFA"], dev["B"], dev["SFB"], d32, dev["grouped_layout"], workspace=ws)()
+        assert gg.device_status() == 0
+        outs[name] = d32.cpu().numpy()
+        assert np.isnan(outs[name][~valid]).all()
+        assert rel_err(outs[name][valid], ref32[valid]) <= TOL
+    assert rel_err(outs["mx"][valid], outs["promote"][valid]) <= 1e-4
+    # env switch forces the promotion kernel even with workspace: bit-identical to the no-workspace run
+    monkeypatch.setenv("B200MOE_GG_MX", "0")
+    d32 = torch.zeros(dev["D"].shape, dtype=torch.float32, device="cuda")
+    launch = gg.bind_contiguous(dev["A"], dev["SFA"], dev["B"], dev["SFB"], d32, dev["grouped_layout"])
+    launch()
+    np.testing.assert_array_equal(d32.cpu().numpy()[valid], outs["promote"][valid])
+    monkeypatch.delenv("B200MOE_GG_MX")
+    # one non-power-of-two scale: the same bound launch must now give the promotion result for the new scales
+    dev["SFA"][5, 3] = 0.3
+    launch()
+    assert gg.device_status() == 0
+    data["SFA"][5, 3] = 0.3
+    ref_b = _oracle_contig(data, orc.BLOCK_PROMOTE, out_f32=True)
+    got = d32.cpu().numpy()
+    assert rel_err(got[valid], ref_b[valid]) <= 1e-4
+    dev["SFA"][5, 3] = 0.25                      # back to a power of two: fast path again, still correct
+    data["SFA"][5, 3] = 0.25
+    launch()
+    assert rel_err(d32.cpu().numpy()[valid], _oracle_contig(data, orc.SIM_CHAIN, out_f32=True)[valid]) <= TOL
+
+
+def test_masked_power_of_two_path(gg):
+    from tirx_harness_b200.workloads import make_masked_case
+    _check_masked(gg, make_masked_case(5, 256, 512, 1024, seed=31, law="pow2", masked_m=[256, 0, 129, 77, 255]))
+    _check_masked(gg, make_masked_case(3, 384, 384, 512, seed=32, law="pow2", masked_m=[384, 100, 257]))

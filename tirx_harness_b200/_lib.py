@@ -22,6 +22,7 @@ class GGArgs(_c.Structure):
         ("sfb", _c.c_void_p), ("layout", _c.c_void_p), ("d", _c.c_void_p), ("ldd", _c.c_int64),
         ("G", _c.c_int32), ("M", _c.c_int32), ("N", _c.c_int32), ("K", _c.c_int32),
         ("d_dtype", _c.c_int32), ("rows_used", _c.c_void_p),
+        ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
     ]
 
 
@@ -77,7 +78,7 @@ def lib():
 
 # every symbol include/b200moe.h declares
 EXPORTS = (
-    "moe_gg_fp8_contiguous", "moe_gg_fp8_masked", "moe_quant_1x128", "moe_silu_mul_requant",
+    "moe_gg_fp8_contiguous", "moe_gg_fp8_masked", "moe_gg_workspace_bytes", "moe_quant_1x128", "moe_silu_mul_requant",
     "moe_route_topk", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute_plan_static", "moe_permute",
     "moe_combine",
     "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
@@ -86,7 +87,7 @@ EXPORTS = (
     "moe_ep_combine",
     "moe_last_error", "moe_version",
 )
-_SIZE_T_RETURN = ("moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes")
+_SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes")
 
 
 def check(rc: int) -> None:

@@ -9,9 +9,12 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 #include "gg_fp8.cuh"
+#include "gg_fp8_2cta.cuh"
+#include "gg_fp8_mx.cuh"
 #include "moe_ops.cuh"
 
 namespace {
@@ -69,8 +72,40 @@ int encode_fp8_kmajor(CUtensorMap* map, const void* base, uint64_t rows, uint64_
     return MOE_OK;
 }
 
+// 1-D array of 32-bit words, box = 128 words (one 512-byte scale tile)
+int encode_words_1d(CUtensorMap* map, const void* base, uint64_t n_words) {
+    auto fn = get_encode_fn();
+    if (!fn) return fail(MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[1] = {n_words};
+    cuuint64_t strides[1] = {0};
+    cuuint32_t box[1] = {128};
+    cuuint32_t estr[1] = {1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 1, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MOE_ERR_CUDA, "cuTensorMapEncodeTiled (1-D) failed with CUresult %d", (int)r);
+    return MOE_OK;
+}
+
+struct MxLayout {
+    size_t flag_off, sfa_off, sfb_off, bytes;
+    int row_blocks, quads;
+};
+MxLayout mx_layout(int G, long long rows_total, int N, int K) {
+    MxLayout l;
+    l.row_blocks = (int)((rows_total + 127) / 128);
+    l.quads = (K / 128 + 3) / 4;
+    const int nb128 = (N + 127) / 128;
+    l.flag_off = 0;
+    l.sfa_off = 256;
+    l.sfb_off = l.sfa_off + (size_t)l.row_blocks * l.quads * 512;
+    l.bytes = l.sfb_off + (size_t)G * nb128 * l.quads * 512;
+    return l;
+}
+
 struct DeviceInfo {
     int num_sms = 0;
+    int max_pairs = 0;       // CTA pairs (clusters of 2) of the pair kernel that can be resident at once
     bool attr_set = false;
 };
 
@@ -93,6 +128,35 @@ int device_info(DeviceInfo** out) {
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg2::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg2::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      mx::SMEM_BYTES));
+        {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * di.num_sms, 1, 1);
+            cfg.blockDim = dim3(gg2::THREADS, 1, 1);
+            cfg.dynamicSmemBytes = gg2::SMEM_BYTES;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gg_fp8_2cta_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
+                (void)cudaGetLastError();
+                n = di.num_sms / 2;
+            }
+            di.max_pairs = n < di.num_sms / 2 ? n : di.num_sms / 2;
+            if (const char* e = getenv("B200MOE_PAIRS")) di.max_pairs = atoi(e);
+            if (getenv("B200MOE_VERBOSE")) fprintf(stderr, "b200moe: %d SMs, occupancy query %d clusters, using %d\n", di.num_sms, n, di.max_pairs);
+        }
         di.attr_set = true;
     }
     *out = &di;
@@ -133,10 +197,16 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     int rc = device_info(&di);
     if (rc != MOE_OK) return rc;
 
+    // developer switches, read on every call: B200MOE_GG_KERNEL=2cta selects the CTA-pair promotion
+    // kernel (slower: its per-K-block hand-off crosses SMs); B200MOE_GG_MX=0 disables the power-of-two path
+    const char* env_kernel = getenv("B200MOE_GG_KERNEL");
+    const char* env_mx = getenv("B200MOE_GG_MX");
+    const bool use_pair_kernel = env_kernel && strcmp(env_kernel, "2cta") == 0;
+    const bool allow_mx = !(env_mx && strcmp(env_mx, "0") == 0);
     CUtensorMap tmap_a, tmap_b;
     rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::BM);
     if (rc != MOE_OK) return rc;
-    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, gg::BN);
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, use_pair_kernel ? gg2::BN / 2 : gg::BN);
     if (rc != MOE_OK) return rc;
 
     GGParams p;
@@ -146,6 +216,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.sfb = a->sfb;
     p.layout = a->layout;
     p.rows_used = MASKED ? nullptr : a->rows_used;
+    p.mode_flag = nullptr;
     p.d = a->d;
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
@@ -156,6 +227,52 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.nb128 = (a->N + 127) / 128;
     p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
 
+    // ---- power-of-two-scale path: needs caller workspace; stands down on the device if a scale is not 2^e
+    if (allow_mx && a->workspace != nullptr && (!MASKED || a->M % 128 == 0)) {
+        const MxLayout ml = mx_layout(a->G, rows_total, a->N, a->K);
+        if (a->workspace_bytes < ml.bytes)
+            return fail(MOE_ERR_INVALID, "workspace too small: %llu < %zu bytes (moe_gg_workspace_bytes)",
+                        (unsigned long long)a->workspace_bytes, ml.bytes);
+        if (reinterpret_cast<uintptr_t>(a->workspace) & 255) return fail(MOE_ERR_INVALID, "workspace must be 256-byte aligned");
+        char* wsb = static_cast<char*>(a->workspace);
+        MxWorkspace ws;
+        ws.flag = reinterpret_cast<int*>(wsb + ml.flag_off);
+        ws.sfa_packed = reinterpret_cast<uint32_t*>(wsb + ml.sfa_off);
+        ws.sfb_packed = reinterpret_cast<uint32_t*>(wsb + ml.sfb_off);
+        ws.row_blocks = ml.row_blocks;
+        ws.quads = ml.quads;
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        CUDA_TRY(cudaMemsetAsync(ws.flag, 0, sizeof(int), st));
+        dim3 pgrid(ml.row_blocks + a->G * p.nb128, ml.quads, 1);
+        mx_prep_kernel<<<pgrid, 128, 0, st>>>(a->sfa, a->sfa_stride_row, a->sfa_stride_kblk, a->sfb, (int)rows_total,
+                                              p.num_k_blocks, a->G, p.nb128, ws);
+        CUDA_TRY(cudaGetLastError());
+        CUtensorMap tmap_b2, tmap_sfa, tmap_sfb;
+        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx::BN / 2);
+        if (rc != MOE_OK) return rc;
+        rc = encode_words_1d(&tmap_sfa, ws.sfa_packed, (uint64_t)ml.row_blocks * ml.quads * 128);
+        if (rc != MOE_OK) return rc;
+        rc = encode_words_1d(&tmap_sfb, ws.sfb_packed, (uint64_t)a->G * p.nb128 * ml.quads * 128);
+        if (rc != MOE_OK) return rc;
+        const long long row_blocks256 = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
+        const long long tiles = row_blocks256 * p.num_n_blocks;
+        int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
+        if (pairs < 1) pairs = 1;
+        gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
+                                                                               ws.flag, ml.quads, status_ptr());
+        CUDA_TRY(cudaGetLastError());
+        p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
+    }
+    if (use_pair_kernel) {
+        const long long row_blocks = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
+        const long long tiles = row_blocks * p.num_n_blocks;
+        int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
+        if (pairs < 1) pairs = 1;
+        gg_fp8_2cta_kernel<MASKED><<<2 * pairs, gg2::THREADS, gg2::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+            tmap_a, tmap_b, p, status_ptr());
+        CUDA_TRY(cudaGetLastError());
+        return MOE_OK;
+    }
     long long max_tiles = MASKED ? (long long)a->G * p.num_m_blocks * p.num_n_blocks
                                  : (long long)p.num_m_blocks * p.num_n_blocks;
     int grid = (int)(max_tiles < di->num_sms ? max_tiles : di->num_sms);
@@ -221,6 +338,11 @@ int check_plan_args(int64_t n_pairs, int32_t E_local, int32_t align, int64_t cap
 }  // namespace
 
 extern "C" {
+
+size_t moe_gg_workspace_bytes(int32_t G, int64_t rows_total, int32_t N, int32_t K) {
+    if (G <= 0 || rows_total < 0 || N <= 0 || K <= 0) return 0;
+    return mx_layout(G, rows_total, N, K).bytes;
+}
 
 int moe_gg_fp8_contiguous(const moe_gg_args* args, void* stream) { return launch_gg<false>(args, stream); }
 int moe_gg_fp8_masked(const moe_gg_args* args, void* stream) { return launch_gg<true>(args, stream); }

@@ -55,6 +55,7 @@ struct GGParams {
     const float* sfb;            // [G][nb128][KB]
     const int* layout;           // grouped_layout[M] or masked_m[G]
     const int* rows_used;        // contiguous, optional: device count of leading rows in use (<= M)
+    const int* mode_flag;        // optional: this kernel runs only if *mode_flag != 0 (see gg_fp8_mx.cuh)
     void* d;                     // bf16 (or fp32 when d_f32 != 0)
     long long ldd;
     int d_f32;
@@ -158,6 +159,7 @@ __global__ void __launch_bounds__(gg::THREADS, 1)
 gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const GGParams p, int* status) {
     using namespace gg;
+    if (p.mode_flag != nullptr && *p.mode_flag == 0) return;   // the power-of-two-scale path took this call
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms the MMA descriptors address
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));

@@ -1,0 +1,356 @@
+// m-grouped FP8 GEMM, power-of-two-scale fast path: block scales applied INSIDE the tensor core.
+//
+// When every block scale is an exact power of two in [2^-126, 2^127] (the UE8M0 scale format of the
+// registered grouped_gemm/fp8 workload, and the 2^{-4..0} law of the benchmark configurations), the
+// product a*sfa and b*sfb can be formed by tcgen05.mma.kind::mxf8f6f4.block_scale itself: the scales
+// are staged into TMEM as UE8M0 bytes and the accumulator simply runs over all of K.  No per-K-block
+// promotion is needed, so the tensor pipe is never waiting on the CUDA cores.  The result is the same
+// sum of exactly-scaled e4m3 products accumulated in fp32.
+//
+//   mx_prep_kernel     checks every scale and writes the UE8M0 bytes, four K blocks per 32-bit word,
+//                      in the 32x16-byte tile order tcgen05.cp expects; sets a flag if any scale is not a
+//                      power of two (then this path stands down and the promotion kernel runs instead)
+//   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256 x 256 tiles, 6-stage TMA ring; the scale words of
+//                      four K blocks travel with the first of their stages; the leader issues
+//                      tcgen05.cp (smem -> TMEM) and 16 block-scaled MMAs per group of four K blocks;
+//                      one accumulator drain per tile by the 8 epilogue warps of each CTA
+#pragma once
+
+#include "gg_fp8_2cta.cuh"
+
+namespace b200 {
+
+namespace mx {
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int STAGES = 6;
+constexpr int THREADS = 384;
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int B_STAGE_BYTES = (BN / 2) * BK;
+constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+constexpr int SFQ_SLOTS = 4;                          // ring of scale tiles, one per group of 4 K blocks
+constexpr int SFQ_SLOT_BYTES = 512 + 2 * 512;         // SFA (this CTA's 128 rows) + SFB (256 columns)
+constexpr int OFF_SFQ = SMEM_TILE_BYTES;
+constexpr int OFF_BARS = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
+constexpr int OFF_PREFIX = OFF_BARS + 256;
+constexpr int SMEM_BYTES = OFF_PREFIX + (gg::MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_SF_BASE = 256;                     // accumulator: columns [0, 256)
+constexpr int TMEM_SF_STRIDE = 12;                    // per buffer: 4 columns SFA + 8 columns SFB
+}  // namespace mx
+
+struct MxWorkspace {
+    int* flag;                 // 0 after mx_prep_kernel = every scale is a power of two
+    uint32_t* sfa_packed;      // [row_blocks128][quads][128]
+    uint32_t* sfb_packed;      // [G][nb128][quads][128]
+    int row_blocks, quads;
+};
+
+// position of row r (0..127) inside a 128-row scale tile: 32 rows of 16 bytes, word r/32 of row r%32
+__device__ __forceinline__ int sf_tile_index(int r) { return (r & 31) * 4 + (r >> 5); }
+
+__device__ __forceinline__ uint32_t ue8m0_of(float s, int* bad) {
+    const uint32_t bits = __float_as_uint(s);
+    const uint32_t e = bits >> 23;                    // sign must be 0, so this is the biased exponent
+    if ((bits & 0x807FFFFFu) != 0u || e == 0u || e == 255u) *bad = 1;
+    return e & 0xFFu;
+}
+
+// grid.x covers rows_total rounded up to 128, grid.y = quads (SFA); the tail blocks of grid.x beyond
+// that handle SFB.  One thread per (row, quad).
+__global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, long long sfa_sk,
+                               const float* __restrict__ sfb, int rows_total, int KB, int G, int nb128,
+                               MxWorkspace ws) {
+    int bad = 0;
+    const int q = blockIdx.y;
+    if ((int)blockIdx.x < ws.row_blocks) {
+        const int r = blockIdx.x * 128 + threadIdx.x;
+        uint32_t word = 0x7F7F7F7Fu;
+        if (r < rows_total) {
+            word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int kb = 4 * q + i;
+                const uint32_t b = kb < KB ? ue8m0_of(__ldg(sfa + (long long)r * sfa_sr + (long long)kb * sfa_sk), &bad) : 0x7Fu;
+                word |= b << (8 * i);
+            }
+        }
+        ws.sfa_packed[((long long)blockIdx.x * ws.quads + q) * 128 + sf_tile_index(threadIdx.x)] = word;
+    } else {
+        const int idx = blockIdx.x - ws.row_blocks;       // (g, nb) pair
+        if (idx < G * nb128) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int kb = 4 * q + i;
+                const uint32_t b = kb < KB ? ue8m0_of(__ldg(sfb + (long long)idx * KB + kb), &bad) : 0x7Fu;
+                word |= b << (8 * i);
+            }
+            ws.sfb_packed[((long long)idx * ws.quads + q) * 128 + threadIdx.x] = word;
+        }
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(ws.flag, 1);
+}
+
+// ------------------------------------------------------------------ PTX for this path
+__device__ __forceinline__ void tma_load_1d_pair(uint32_t smem_dst, const void* tmap, uint32_t cluster_bar, int32_t c0) {
+    asm volatile(
+        "cp.async.bulk.tensor.1d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3}], [%2];"
+        ::"r"(smem_dst), "l"(tmap), "r"(cluster_bar), "r"(c0)
+        : "memory");
+}
+// shared-memory descriptor of one 128-row scale tile: 8-row groups of 16-byte rows, 128 bytes apart, no swizzle
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(128 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+// 32 rows x 128 bits from shared memory, broadcast to the four 32-lane quarters of TMEM, in both CTAs
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+// block-scaled instruction descriptor: e4m3 x e4m3, UE8M0 scales, K-major operands; sf_id = which byte
+// of the 32-bit scale word (= which of the four K blocks) this instruction uses
+__device__ __forceinline__ uint32_t make_idesc_mxf8(int m, int n, uint32_t sf_id) {
+    return (sf_id << 4)                                   // B scale id
+           | (0u << 7) | (0u << 10)                       // A, B format: e4m3
+           | (static_cast<uint32_t>(n >> 3) << 17)        // N / 8
+           | (1u << 23)                                   // scale format: UE8M0
+           | (static_cast<uint32_t>(m >> 4) << 24)        // M / 16
+           | (sf_id << 29);                               // A scale id
+}
+
+template <bool MASKED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(mx::THREADS, 1)
+gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                 const GGParams p, const int* __restrict__ flag, int quads, int* status) {
+    using namespace mx;
+    if (*flag != 0) return;          // some scale is not a power of two: the promotion kernel handles this call
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+    uint8_t* smem_sfq = smem + OFF_SFQ;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
+    // [0,S) full (leader's used), [S,2S) empty, [2S] tmem_full, [2S+1] tmem_empty (leader's used)
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+
+    const uint32_t full_bar = smem_u32(bars);
+    const uint32_t empty_bar = smem_u32(bars + STAGES);
+    const uint32_t tfull_bar = smem_u32(bars + 2 * STAGES);
+    const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + 1);
+    const uint32_t leader_full_bar = map_to_cta(full_bar, 0);
+    const uint32_t leader_tempty_bar = map_to_cta(tempty_bar, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        mbar_init(tfull_bar, 1);
+        mbar_init(tempty_bar, 16);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_sfa);
+        tma_prefetch_desc(&tmap_sfb);
+    }
+    if (MASKED) {
+        if (warp == 3) {
+            int running = 0;
+            for (int base = 0; base < p.G; base += 32) {
+                int g = base + lane;
+                int mm = 0;
+                if (g < p.G) {
+                    mm = __ldg(p.layout + g);
+                    mm = mm < 0 ? 0 : (mm > p.M ? p.M : mm);
+                }
+                int blocks = (mm + 255) / 256;
+                int incl = blocks;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                if (g < p.G) prefix[g] = running + incl - blocks;
+                running += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) prefix[p.G] = running;
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_base_slot), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    const int KB = p.num_k_blocks;
+
+    if (warp < 4) {
+        setmaxnreg_dec<72>();
+        if (warp == 0) {
+            // ------------------------------------------------ TMA producer (both CTAs)
+            PairScheduler<MASKED> sched(p, prefix, lane, rank);
+            Tile tile;
+            uint32_t stage = 0, phase = 0, qcount = 0;
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                const int b_row = tile.g * p.N + tile.n_blk * BN + (int)rank * (BN / 2);
+                const int sfa_chunk = (tile.m0 >> 7) * quads;                       // this CTA's 128 rows
+                const int sfb_chunk = (tile.g * p.nb128 + tile.n_blk * 2) * quads;  // first of the two column blocks
+                const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
+                                        STATUS_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t fb = leader_full_bar + 8 * stage;
+                        const bool with_sf = (kb & 3) == 0;
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * (A_STAGE_BYTES + B_STAGE_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0)));
+                        tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tile.m0);
+                        tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
+                        if (with_sf) {
+                            const int q = kb >> 2;
+                            const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
+                            tma_load_1d_pair(dst, &tmap_sfa, fb, (sfa_chunk + q) * 128);
+                            tma_load_1d_pair(dst + 512, &tmap_sfb, fb, (sfb_chunk + q) * 128);
+                            // a last, half-wide column block has no second scale block: reuse the first
+                            tma_load_1d_pair(dst + 1024, &tmap_sfb, fb, (sfb_chunk + (second_nb ? quads : 0) + q) * 128);
+                        }
+                    }
+                    __syncwarp();
+                    if ((kb & 3) == 0) ++qcount;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        } else if (warp == 1 && rank == 0) {
+            // ------------------------------------------------ MMA issuer (leader)
+            PairScheduler<MASKED> sched(p, prefix, lane, rank);
+            Tile tile;
+            uint32_t stage = 0, phase = 0, tile_phase = 0, qcount = 0;
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                // the single accumulator must have been drained by both CTAs' epilogues
+                ok = mbar_wait_warp(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        if ((kb & 3) == 0) {
+                            const uint32_t src = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
+                            const uint32_t tsf = tmem_base + TMEM_SF_BASE + (qcount & 1) * TMEM_SF_STRIDE;
+                            tmem_cp_sf_pair(tsf, make_sf_desc(src));
+                            tmem_cp_sf_pair(tsf + 4, make_sf_desc(src + 512));
+                            tmem_cp_sf_pair(tsf + 8, make_sf_desc(src + 1024));
+                        }
+                        const uint32_t buf = ((kb & 3) == 0 ? qcount : qcount - 1) & 1;
+                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + buf * TMEM_SF_STRIDE;
+                        const uint32_t tsfb = tsfa + 4;
+                        const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, kb & 3);
+                        const uint64_t adesc = make_smem_desc_sw128(smem_u32(smem_a + stage * A_STAGE_BYTES));
+                        const uint64_t bdesc = make_smem_desc_sw128(smem_u32(smem_b + stage * B_STAGE_BYTES));
+#pragma unroll
+                        for (int k = 0; k < BK / 32; ++k)
+                            umma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, tsfa, tsfb,
+                                           (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_commit_pair(empty_bar + 8 * stage, 3);
+                        if (kb == KB - 1) umma_commit_pair(tfull_bar, 3);
+                    }
+                    __syncwarp();
+                    if ((kb & 3) == 0) ++qcount;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                tile_phase ^= 1;
+            }
+        }
+    } else {
+        // ---------------------------------------------------- epilogue (both CTAs): one drain per tile
+        setmaxnreg_inc<208>();
+        const int ew = warp - 4;
+        const int quarter = warp & 3;
+        const int half = ew >> 2;
+        const int row_in_tile = quarter * 32 + lane;
+        PairScheduler<MASKED> sched(p, prefix, lane, rank);
+        Tile tile;
+        uint32_t tile_phase = 0;
+        bool ok = true;
+        while (ok && sched.next(tile)) {
+            const int n0 = tile.n_blk * BN + half * 128;
+            const int row = tile.m0 + row_in_tile;
+            bool row_valid;
+            if (MASKED) row_valid = row_in_tile < tile.rows;
+            else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
+            ok = mbar_wait_warp(tfull_bar, tile_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+            if (!ok) break;
+            tile_phase ^= 1;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + half * 128;
+            uint32_t v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_wait(v[c]);
+            // the accumulator is in registers: the next tile's MMAs may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tempty_bar);
+            if (row_valid && p.d_f32) {
+                float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 4) {
+                    if (n0 + j + 4 <= p.N)
+                        *reinterpret_cast<float4*>(drow + j) =
+                            make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
+                                        __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
+                }
+            } else if (row_valid) {
+                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 8) {
+                    if (n0 + j + 8 <= p.N) {
+                        uint4 out;
+                        const uint32_t* s = &v[j / 32][j % 32];
+                        out.x = cvt_bf16x2(pack_f32x2(__uint_as_float(s[0]), __uint_as_float(s[1])));
+                        out.y = cvt_bf16x2(pack_f32x2(__uint_as_float(s[2]), __uint_as_float(s[3])));
+                        out.z = cvt_bf16x2(pack_f32x2(__uint_as_float(s[4]), __uint_as_float(s[5])));
+                        out.w = cvt_bf16x2(pack_f32x2(__uint_as_float(s[6]), __uint_as_float(s[7])));
+                        *reinterpret_cast<uint4*>(drow + j) = out;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace b200

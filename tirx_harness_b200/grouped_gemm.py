@@ -42,7 +42,13 @@ def _scale_strides(sfa: torch.Tensor, rows: int, kblocks: int, name: str):
 class _BoundGG:
     """A validated argument block; ``__call__`` launches on the current stream of the tensors' device."""
 
-    def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K, rows_used=None):
+    def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K, rows_used=None,
+                 workspace=True):
+        rows_total = M if fn_name.endswith("contiguous") else G * M
+        ws_bytes = _lib.lib().moe_gg_workspace_bytes(ctypes.c_int32(G), ctypes.c_int64(rows_total), ctypes.c_int32(N),
+                                                    ctypes.c_int32(K)) if workspace else 0
+        # scratch for the power-of-two-scale path, allocated once at bind time (set-up, untimed)
+        self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=d.device) if ws_bytes else None
         self._keep = (a, b, sfa, sfb, layout, d, rows_used)
         self._fn = getattr(_lib.lib(), fn_name)
         self._device = d.device
@@ -50,7 +56,8 @@ class _BoundGG:
             a=_ptr(a), b=_ptr(b), sfa=_ptr(sfa), sfa_stride_row=sfa_strides[0], sfa_stride_kblk=sfa_strides[1],
             sfb=_ptr(sfb), layout=_ptr(layout), d=_ptr(d), ldd=d.stride(-2), G=G, M=M, N=N, K=K,
             d_dtype=1 if d.dtype == torch.float32 else 0,
-            rows_used=_ptr(rows_used) if rows_used is not None else None)
+            rows_used=_ptr(rows_used) if rows_used is not None else None,
+            workspace=_ptr(self._ws) if self._ws is not None else None, workspace_bytes=ws_bytes)
         self._argp = ctypes.byref(self._args)
         self.out = d
 
@@ -61,7 +68,7 @@ class _BoundGG:
         return self.out
 
 
-def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None) -> _BoundGG:
+def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace=True) -> _BoundGG:
     """a fp8[M,K], sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128],
     d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row); rows_used: optional
     int32[1] device tensor with the number of leading rows in use."""
@@ -79,10 +86,11 @@ def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None) -> _Bound
         raise ValueError(f"grouped_layout must be contiguous int32 [{M}]")
     if rows_used is not None and (rows_used.dtype != torch.int32 or not rows_used.is_cuda):
         raise ValueError("rows_used must be an int32 CUDA tensor")
-    return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K, rows_used)
+    return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K, rows_used,
+                    workspace)
 
 
-def bind_masked(a, sfa, b, sfb, d, masked_m) -> _BoundGG:
+def bind_masked(a, sfa, b, sfb, d, masked_m, workspace=True) -> _BoundGG:
     """a fp8[G,max_m,K], sfa f32[G,max_m,K/128] (contiguous, or MN-major: a [G*max_m, K/128] view of any
     strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128], d bf16[G,max_m,N], masked_m int32[G]."""
     _check_fp8(a, "a"); _check_fp8(b, "b")
@@ -103,7 +111,7 @@ def bind_masked(a, sfa, b, sfb, d, masked_m) -> _BoundGG:
         raise ValueError(f"d must be contiguous bfloat16 (or float32) [{G}, {max_m}, {N}]")
     if masked_m.dtype != torch.int32 or masked_m.numel() != G or not masked_m.is_contiguous():
         raise ValueError(f"masked_m must be contiguous int32 [{G}]")
-    return _BoundGG("moe_gg_fp8_masked", a, b, sfa2, strides, sfb, masked_m, d, G, max_m, N, K)
+    return _BoundGG("moe_gg_fp8_masked", a, b, sfa2, strides, sfb, masked_m, d, G, max_m, N, K, None, workspace)
 
 
 def m_grouped_fp8_gemm_nt_contiguous(a, sfa, b, sfb, d, grouped_layout):
