@@ -182,6 +182,7 @@ typedef struct moe_layer_args {
     void* workspace;
     uint64_t workspace_bytes;
     int32_t T, H, I, E, E_global, e_lo, top_k, align, gate_first;
+    int32_t fuse_act;        /* != 0: SiLU*mul requant inside the gate_up GEMM (no gate_up matrix in memory) */
 } moe_layer_args;
 
 size_t moe_workspace_bytes(int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k, int32_t align);
@@ -254,6 +255,15 @@ int moe_ep_dispatch(const moe_ep_peers* peers, const void* x_q, const float* x_s
  * y buffers and accumulates w * row in fp32 (slot order), writing bf16. */
 int moe_ep_combine(const moe_ep_peers* peers, const int32_t* ids, const int32_t* pos, const float* w, void* out_bf16,
                    int32_t T, int32_t top_k, int32_t E_local, int32_t H, int32_t world, void* stream);
+
+/* gate_up grouped GEMM (contiguous layout, N = 2*inter) whose epilogue applies SiLU(gate)*up to the fp32
+ * accumulators and requantises to e4m3 with 1x128 scales, writing act_q [M, inter] and
+ * act_scales[(row)*ss_row + (block)*ss_blk]; the gate_up matrix is never stored (args->d is ignored).
+ * This is the "fused SiLU-mul-FP8 requant between the two GEMMs": same rule as moe_silu_mul_requant
+ * (alphamoe/definition.json `_reference_quantized`: gate_up and SwiGLU stay fp32 up to the requant),
+ * gate_first as there.  Requires N % 256 == 0. */
+int moe_gg_fp8_gate_up_act(const moe_gg_args* args, void* act_q, float* act_scales, int64_t ss_row, int64_t ss_blk,
+                           int32_t gate_first, void* stream);
 
 /* Reads (and clears) the device-side status word of the current device; synchronises the
  * stream first.  0 = no kernel reported a problem.  Non-zero: a bounded wait inside a kernel ran

@@ -145,7 +145,7 @@ def test_layer_stagewise_parity(ops):
     from tirx_harness_b200 import moe_layer
     T, H, I, E, top_k = 300, 512, 256, 8, 2
     dev, host = _make_layer(T, H, I, E, top_k, seed=21)
-    layer = moe_layer.setup(dev, T, top_k=top_k, gate_first=False)
+    layer = moe_layer.setup(dev, T, top_k=top_k, gate_first=False, fuse_act=False)
     dev["output"].fill_(float("nan"))
     layer()
     assert ops.status() == 0
@@ -190,15 +190,65 @@ def test_layer_with_given_routes_and_mn_major_input_scales(ops):
     from tirx_harness_b200 import moe_layer
     T, H, I, E, top_k = 130, 256, 128, 4, 2
     dev, host = _make_layer(T, H, I, E, top_k, seed=5)
-    rid, rw = orc.route_softmax_topk(host["routing_logits"].numpy(), top_k)
+    first = moe_layer.setup(dev, T, top_k=top_k)
+    first()
+    v = first.view()
+    rid, _ = orc.route_softmax_topk(host["routing_logits"].numpy(), top_k)
+    np.testing.assert_array_equal(v["ids"].cpu().numpy(), rid)
     dev2 = dict(dev)
     del dev2["routing_logits"]
-    dev2["topk_ids"] = torch.from_numpy(rid).cuda()
-    dev2["topk_weights"] = torch.from_numpy(rw).cuda()
+    dev2["topk_ids"] = v["ids"].clone()                 # the routes the first run chose, passed explicitly
+    dev2["topk_weights"] = v["weights"].clone()
     dev2["hidden_states_scale"] = dev["hidden_states_scale"].t().contiguous()      # [H/128, T]
     dev2["output"] = torch.zeros_like(dev["output"])
-    moe_layer.setup(dev, T, top_k=top_k)()
     moe_layer.setup(dev2, T, top_k=top_k)()
     assert ops.status() == 0
     assert torch.equal(dev["output"], dev2["output"])
     assert torch.isfinite(dev["output"]).all() and dev["output"].abs().max() > 0
+
+
+@pytest.mark.parametrize("gate_first", [False, True])
+def test_gate_up_gemm_with_fused_silu_requant(ops, gate_first):
+    """The gate_up GEMM whose epilogue does SiLU*mul + requant, against the oracle that keeps gate_up in fp32."""
+    from tirx_harness_b200 import grouped_gemm as gg
+    from tirx_harness_b200.workloads import make_contiguous_case
+    inter = 384
+    data = make_contiguous_case(3, [200, 128, 77], 2 * inter, 512, seed=41, law="uniform_exp", mn_major_sfa=True)
+    data["SFB"].mul_(0.05)
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in data.items()}
+    dev["SFA"] = data["SFA"].t().contiguous().cuda().t()
+    M = data["M"]
+    act_q = torch.zeros((M, inter), dtype=torch.float8_e4m3fn, device="cuda")
+    act_s = torch.zeros((inter // 128, M), dtype=torch.float32, device="cuda").t()
+    gg.bind_gate_up_act(dev["A"], dev["SFA"], dev["B"], dev["SFB"], act_q, act_s, dev["grouped_layout"], gate_first)()
+    assert ops.status() == 0
+    gl = data["grouped_layout"].numpy()
+    valid = gl >= 0
+    g32 = orc.gg_contiguous(u8(data["A"]), u8(data["B"]), npf(data["SFA"]), npf(data["SFB"]), gl,
+                            model=orc.BLOCK_PROMOTE, out_f32=True)
+    rq, rs = orc.silu_mul_requant(g32, gate_first=gate_first, row_valid=valid.astype(np.uint8))
+    np.testing.assert_allclose(npf(act_s)[valid], rs[valid], rtol=2e-5)
+    _codes_close(u8(act_q)[valid], rq[valid], max_mismatch=5e-3)
+    assert (u8(act_q)[~valid] == 0).all()                     # padding rows untouched
+
+
+def test_layer_fused_activation_matches_oracle(ops):
+    from tirx_harness_b200 import moe_layer
+    T, H, I, E, top_k = 300, 512, 256, 8, 2
+    dev, host = _make_layer(T, H, I, E, top_k, seed=22)
+    layer = moe_layer.setup(dev, T, top_k=top_k, gate_first=False, fuse_act=True)
+    dev["output"].fill_(float("nan"))
+    layer()
+    assert ops.status() == 0
+    xq, xs = u8(host["hidden_states"]), host["hidden_states_scale"].numpy()
+    full = orc.moe_layer(xq, xs, host["routing_logits"].numpy(), u8(host["gemm1_weights"]),
+                         host["gemm1_weights_scale"].numpy(), u8(host["gemm2_weights"]),
+                         host["gemm2_weights_scale"].numpy(), top_k=top_k, gate_first=False, fused_act=True)
+    v = layer.view()
+    n = full["a2"].shape[0]
+    valid = full["plan"]["grouped_layout"][:n] >= 0
+    np.testing.assert_allclose(npf(v["s2"])[:n][valid], full["s2"][valid], rtol=2e-5)
+    _codes_close(u8(v["a2"])[:n][valid], full["a2"][valid], max_mismatch=5e-3)
+    got, ref = dev["output"].float().cpu().numpy(), orc.bf16_to_f32(full["out"])
+    assert np.isfinite(got).all()
+    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean())

@@ -128,6 +128,8 @@ int device_info(DeviceInfo** out) {
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg2::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -217,6 +219,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.layout = a->layout;
     p.rows_used = MASKED ? nullptr : a->rows_used;
     p.mode_flag = nullptr;
+    p.act_q = nullptr; p.act_s = nullptr; p.act_ss_r = 0; p.act_ss_b = 0; p.inter = 0; p.gate_first = 0;
     p.d = a->d;
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
@@ -335,9 +338,61 @@ int check_plan_args(int64_t n_pairs, int32_t E_local, int32_t align, int64_t cap
     return MOE_OK;
 }
 
+
+// gate_up grouped GEMM with the SiLU*mul + 1x128 FP8 requantisation done in its epilogue.
+int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, int64_t ss_row, int64_t ss_blk,
+                        int32_t gate_first, void* stream) {
+    if (!a) return fail(MOE_ERR_INVALID, "args is NULL");
+    if (a->M == 0 && a->G > 0 && a->N > 0 && a->K > 0) return MOE_OK;
+    if (!a->a || !a->b || !a->sfa || !a->sfb || !a->layout || !act_q || !act_scales)
+        return fail(MOE_ERR_INVALID, "a, b, sfa, sfb, layout, act_q and act_scales must all be non-NULL");
+    if (a->G <= 0 || a->N <= 0 || a->K <= 0 || a->M < 0) return fail(MOE_ERR_INVALID, "G, N, K must be positive, M non-negative");
+    if (a->K % 128 != 0) return fail(MOE_ERR_INVALID, "K=%d must be a multiple of 128", a->K);
+    if (a->N % 256 != 0) return fail(MOE_ERR_INVALID, "N=%d (= 2 x intermediate) must be a multiple of 256", a->N);
+    if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->b) & 15) ||
+        (reinterpret_cast<uintptr_t>(act_q) & 15))
+        return fail(MOE_ERR_INVALID, "a, b and act_q must be 16-byte aligned");
+    if ((long long)a->G * a->N > 0x7FFFFFFFll) return fail(MOE_ERR_INVALID, "row counts exceed 2^31-1");
+    DeviceInfo* di = nullptr;
+    int rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
+    CUtensorMap tmap_a, tmap_b;
+    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)a->M, (uint64_t)a->K, gg::BM);
+    if (rc != MOE_OK) return rc;
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, 64);
+    if (rc != MOE_OK) return rc;
+    GGParams p = {};
+    p.sfa = a->sfa; p.sfa_sr = a->sfa_stride_row; p.sfa_sk = a->sfa_stride_kblk;
+    p.sfb = a->sfb; p.layout = a->layout; p.rows_used = a->rows_used; p.mode_flag = nullptr;
+    p.d = nullptr; p.ldd = 0; p.d_f32 = 0;
+    p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
+    p.rows_total = a->M;
+    p.inter = a->N / 2;
+    p.num_n_blocks = p.inter / 128;          // one tile = 128 activation columns = 256 GEMM columns
+    p.num_k_blocks = a->K / 128;
+    p.nb128 = a->N / 128;
+    p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
+    p.act_q = static_cast<uint8_t*>(act_q);
+    p.act_s = act_scales;
+    p.act_ss_r = ss_row; p.act_ss_b = ss_blk;
+    p.gate_first = gate_first ? 1 : 0;
+    long long max_tiles = (long long)p.num_m_blocks * p.num_n_blocks;
+    int grid = (int)(max_tiles < di->num_sms ? max_tiles : di->num_sms);
+    if (grid < 1) grid = 1;
+    gg_fp8_kernel<false, true><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        tmap_a, tmap_b, p, status_ptr());
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+int moe_gg_fp8_gate_up_act(const moe_gg_args* args, void* act_q, float* act_scales, int64_t ss_row, int64_t ss_blk,
+                           int32_t gate_first, void* stream) {
+    return launch_gg_fused_act(args, act_q, act_scales, ss_row, ss_blk, gate_first, stream);
+}
 
 size_t moe_gg_workspace_bytes(int32_t G, int64_t rows_total, int32_t N, int32_t K) {
     if (G <= 0 || rows_total < 0 || N <= 0 || K <= 0) return 0;
@@ -379,9 +434,8 @@ int moe_silu_mul_requant(const void* gate_up_bf16, void* q, float* scales, int64
     if (!gate_up_bf16 || !q || !scales) return fail(MOE_ERR_INVALID, "gate_up, q and scales must be non-NULL");
     if (rows < 0 || inter <= 0 || inter % 128) return fail(MOE_ERR_INVALID, "inter=%d must be a positive multiple of 128", inter);
     if (rows == 0) return MOE_OK;
-    const long long warps = (long long)rows * (inter / 128);
     const int wpb = 8;
-    silu_mul_requant_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+    silu_mul_requant_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(gate_up_bf16), static_cast<uint8_t*>(q), scales, ss_row, ss_blk, layout,
         rows, inter, gate_first);
     CUDA_TRY(cudaGetLastError());
@@ -505,10 +559,15 @@ int moe_layer_forward(const moe_layer_args* L, void* stream) {
     g1.sfb = L->w13_scale; g1.layout = w.layout; g1.d = w.g1; g1.ldd = 2 * (int64_t)L->I;
     g1.rows_used = w.offsets + L->E;
     g1.G = L->E; g1.M = cap; g1.N = 2 * L->I; g1.K = L->H; g1.d_dtype = MOE_DTYPE_BF16;
-    rc = moe_gg_fp8_contiguous(&g1, stream);
-    if (rc != MOE_OK) return rc;
-    rc = moe_silu_mul_requant(w.g1, w.a2, w.s2, 1, cap, w.layout, cap, L->I, L->gate_first, stream);
-    if (rc != MOE_OK) return rc;
+    if (L->fuse_act) {
+        rc = moe_gg_fp8_gate_up_act(&g1, w.a2, w.s2, 1, cap, L->gate_first, stream);
+        if (rc != MOE_OK) return rc;
+    } else {
+        rc = moe_gg_fp8_contiguous(&g1, stream);
+        if (rc != MOE_OK) return rc;
+        rc = moe_silu_mul_requant(w.g1, w.a2, w.s2, 1, cap, w.layout, cap, L->I, L->gate_first, stream);
+        if (rc != MOE_OK) return rc;
+    }
     moe_gg_args g2 = {};
     g2.a = w.a2; g2.b = L->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = cap;
     g2.sfb = L->w2_scale; g2.layout = w.layout; g2.d = w.y; g2.ldd = L->H;

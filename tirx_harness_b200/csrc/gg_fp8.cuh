@@ -17,6 +17,10 @@
 //                 acc += partial * (sfa * sfb) in registers, hand the TMEM buffer back, and after
 //                 the last K block convert to bf16 and store the valid rows
 // The MMA of K block i+1 runs while block i is being promoted (double-buffered TMEM).
+// FUSE_ACT (gate_up GEMM of a MoE layer): a tile's 256 columns are [up 64 | gate 64] for each of the two
+// warpgroups, so every epilogue thread ends up holding matching gate/up values; it forms silu(gate)*up
+// in fp32, the two warpgroups exchange their 64-column amax through shared memory, and the 128-wide block
+// is requantised to e4m3 with its scale and stored -- the gate_up matrix itself is never written.
 // Every wait is bounded (see mbar_wait_warp); on expiry the CTA unwinds and the host sees a status.
 #pragma once
 
@@ -25,6 +29,7 @@
 #include <limits.h>
 
 #include "ptx.cuh"
+#include "moe_ops.cuh"
 
 namespace b200 {
 
@@ -44,7 +49,8 @@ constexpr int SF_SLOTS = 8;                        // scale ring: per slot 128 r
 constexpr int SF_SLOT_FLOATS = 132;
 constexpr int OFF_BARS = SMEM_TILE_BYTES;          // mbarriers, TMEM base, abort flag
 constexpr int OFF_SF = OFF_BARS + 512;
-constexpr int OFF_PREFIX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;
+constexpr int OFF_AMAX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;     // fused activation: float [2 parity][2 half][128]
+constexpr int OFF_PREFIX = OFF_AMAX + 2 * 2 * 128 * 4;
 // + masked-layout prefix table + slack for 1024-byte alignment
 constexpr int SMEM_BYTES = OFF_PREFIX + (MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
 }  // namespace gg
@@ -56,6 +62,11 @@ struct GGParams {
     const int* layout;           // grouped_layout[M] or masked_m[G]
     const int* rows_used;        // contiguous, optional: device count of leading rows in use (<= M)
     const int* mode_flag;        // optional: this kernel runs only if *mode_flag != 0 (see gg_fp8_mx.cuh)
+    // fused SiLU*mul requant (FUSE_ACT kernels): N = 2*inter, outputs replace d
+    uint8_t* act_q;              // e4m3 [M, inter]
+    float* act_s;                // scale of (row r, 128-block b) at act_s[r*act_ss_r + b*act_ss_b]
+    long long act_ss_r, act_ss_b;
+    int inter, gate_first;
     void* d;                     // bf16 (or fp32 when d_f32 != 0)
     long long ldd;
     int d_f32;
@@ -154,10 +165,11 @@ struct Scheduler {
     }
 };
 
-template <bool MASKED>
+template <bool MASKED, bool FUSE_ACT = false>
 __global__ void __launch_bounds__(gg::THREADS, 1)
 gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const GGParams p, int* status) {
+    static_assert(!(MASKED && FUSE_ACT), "the fused activation epilogue exists for the contiguous layout only");
     using namespace gg;
     if (p.mode_flag != nullptr && *p.mode_flag == 0) return;   // the power-of-two-scale path took this call
     extern __shared__ uint8_t smem_raw[];
@@ -168,7 +180,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty,
     // then SF_SLOTS scale-full and SF_SLOTS scale-empty barriers
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     float* sf_ring = reinterpret_cast<float*>(smem + OFF_SF);
     int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
@@ -182,6 +194,8 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + ACC_STAGES);
     const uint32_t sffull_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES);
     const uint32_t sfempty_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES + SF_SLOTS);
+    const uint32_t amax_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
+    float* amax_x = reinterpret_cast<float*>(smem + OFF_AMAX);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -196,6 +210,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             mbar_init(sffull_bar + 8 * s, 32);    // every lane of the loader warp arrives
             mbar_init(sfempty_bar + 8 * s, 8);    // one arrival per epilogue warp
         }
+        mbar_init(amax_bar, 256);                 // every epilogue thread, once per tile
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
@@ -255,7 +270,18 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         const uint32_t fb = full_bar + 8 * stage;
                         mbar_arrive_expect_tx(fb, A_STAGE_BYTES + B_STAGE_BYTES);
                         tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tile.m0);
-                        tma_load_2d(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
+                        if (FUSE_ACT) {
+                            // tmap_b has a 64-row box here: [up 64 | gate 64] for each warpgroup
+                            const int up0 = tile.g * p.N + (p.gate_first ? p.inter : 0) + tile.n_blk * 128;
+                            const int gate0 = tile.g * p.N + (p.gate_first ? 0 : p.inter) + tile.n_blk * 128;
+                            const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
+                            tma_load_2d(sb, &tmap_b, fb, kb * BK, up0);
+                            tma_load_2d(sb + 64 * BK, &tmap_b, fb, kb * BK, gate0);
+                            tma_load_2d(sb + 128 * BK, &tmap_b, fb, kb * BK, up0 + 64);
+                            tma_load_2d(sb + 192 * BK, &tmap_b, fb, kb * BK, gate0 + 64);
+                        } else {
+                            tma_load_2d(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
+                        }
                     }
                     __syncwarp();
                     issued |= 1u << stage;
@@ -321,6 +347,8 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     rp[j] = p.sfa + (long long)r * p.sfa_sr;
                 }
                 int nb = ((tile.n_blk * BN) >> 7) + (lane & 1);
+                if (FUSE_ACT)      // slot word 128 = up block, 129 = gate block of this tile's 128 activation columns
+                    nb = tile.n_blk + ((((lane & 1) != 0) != (p.gate_first != 0)) ? (p.inter >> 7) : 0);
                 if (nb >= p.nb128) nb = p.nb128 - 1;
                 const float* bp = p.sfb + ((long long)tile.g * p.nb128 + nb) * KB;
                 for (int kb0 = 0; kb0 < KB && ok; kb0 += 4) {
@@ -360,7 +388,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         const int row_in_tile = quarter * 32 + lane;
         Scheduler<MASKED> sched(p, prefix, lane);
         Tile tile;
-        uint32_t acc = 0, acc_phase = 0, slot = 0, sphase = 0;
+        uint32_t acc = 0, acc_phase = 0, slot = 0, sphase = 0, act_phase = 0;
         bool ok = true;
         while (ok && sched.next(tile)) {
             const int n0 = tile.n_blk * BN + half * 128;
@@ -376,11 +404,14 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 ok = mbar_wait_warp(sffull_bar + 8 * slot, sphase, abort_flag, status, STATUS_TIMEOUT_SF_FULL);
                 if (!ok) break;
                 const float* sfp = sf_ring + slot * SF_SLOT_FLOATS;
-                const float s = sfp[row_in_tile] * sfp[128 + half];
+                const float sa_row = sfp[row_in_tile];
+                const float s = sa_row * sfp[128 + (FUSE_ACT ? 0 : half)];
+                const float sg = FUSE_ACT ? sa_row * sfp[129] : s;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sfempty_bar + 8 * slot);
                 if (++slot == SF_SLOTS) { slot = 0; sphase ^= 1; }
                 const unsigned long long s2 = pack_f32x2(s, s);
+                const unsigned long long s2g = pack_f32x2(sg, sg);     // columns 64..127 (gate) when fused
 
                 ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status,
                                     STATUS_TIMEOUT_TMEM_FULL);
@@ -397,7 +428,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     tmem_ld_32x32b_x16(taddr + (c + 1) * 16, v1);
 #pragma unroll
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[c * 8 + j], v0[2 * j], v0[2 * j + 1], s2);
+                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[c * 8 + j], v0[2 * j], v0[2 * j + 1], c < 4 ? s2 : s2g);
                     tmem_ld_wait(v1);
                     if (c + 2 < 8) {
                         tmem_ld_32x32b_x16(taddr + (c + 2) * 16, v0);
@@ -409,11 +440,49 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     }
 #pragma unroll
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[(c + 1) * 8 + j], v1[2 * j], v1[2 * j + 1], s2);
+                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[(c + 1) * 8 + j], v1[2 * j], v1[2 * j + 1], c + 1 < 4 ? s2 : s2g);
                 }
                 if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
             }
             if (!ok) break;
+            if (FUSE_ACT) {
+                // accr[0..32) = up columns, accr[32..64) = gate columns of this warpgroup's 64 activations
+                float amax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float u0, u1, g0, g1;
+                    unpack_f32x2(accr[j], u0, u1);
+                    unpack_f32x2(accr[32 + j], g0, g1);
+                    const float a0 = __fmul_rn(silu_f32(g0), u0), a1 = __fmul_rn(silu_f32(g1), u1);
+                    amax = fmaxf(amax, fmaxf(fabsf(a0), fabsf(a1)));
+                    accr[j] = pack_f32x2(a0, a1);
+                }
+                // the 128-wide quantisation block spans both warpgroups: swap the 64-column maxima
+                amax_x[(act_phase * 2 + half) * 128 + row_in_tile] = amax;
+                mbar_arrive(amax_bar);
+                ok = mbar_wait_warp(amax_bar, act_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+                if (!ok) break;
+                amax = fmaxf(amax, amax_x[(act_phase * 2 + (half ^ 1)) * 128 + row_in_tile]);
+                act_phase ^= 1;
+                const float sc = __fdiv_rn(fmaxf(amax, 1.0e-8f), 448.0f);
+                if (row_valid) {
+                    uint8_t* qrow = p.act_q + (long long)row * p.inter + tile.n_blk * 128 + half * 64;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float a0, a1, a2, a3;
+                            unpack_f32x2(accr[j + 2 * i], a0, a1);
+                            unpack_f32x2(accr[j + 2 * i + 1], a2, a3);
+                            w[i] = pack4_e4m3(clamp448(__fdiv_rn(a0, sc)), clamp448(__fdiv_rn(a1, sc)),
+                                              clamp448(__fdiv_rn(a2, sc)), clamp448(__fdiv_rn(a3, sc)));
+                        }
+                        *reinterpret_cast<uint4*>(qrow + j * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    if (half == 0) p.act_s[(long long)row * p.act_ss_r + (long long)tile.n_blk * p.act_ss_b] = sc;
+                }
+            } else
             if (row_valid && p.d_f32) {
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll

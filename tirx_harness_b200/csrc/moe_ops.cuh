@@ -69,27 +69,43 @@ __device__ __forceinline__ float silu_f32(float x) {
 
 // gate_up bf16 [rows, 2I] -> act = silu(gate) * up (fp32) -> 1x128 requant: q e4m3 [rows, I],
 // scales at [r*ss_r + b*ss_b].  gate_first: gate = columns [0, I), else gate = [I, 2I).
-// Rows whose layout entry is negative (padding) are skipped.  One warp per (row, 128-block).
+// Rows whose layout entry is negative (padding) are skipped.  One warp per row: all loads of up to four
+// 128-blocks are issued before the first is consumed, so each lane keeps 64 bytes in flight.
 __global__ void silu_mul_requant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ q,
                                         float* __restrict__ scales, long long ss_r, long long ss_b,
                                         const int* __restrict__ layout, int rows, int inter,
                                         int gate_first) {
     const int nb = inter >> 7;
-    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    if (w >= (long long)rows * nb) return;
-    const int r = (int)(w / nb), b = (int)(w % nb);
+    if (r >= rows) return;
     if (layout != nullptr && __ldg(layout + r) < 0) return;
-    const long long base = (long long)r * 2 * inter + b * 128 + lane * 4;
-    float g[4], u[4], a[4];
-    bf16x4_to_float(__ldg(reinterpret_cast<const uint2*>(gu + base + (gate_first ? 0 : inter))), g);
-    bf16x4_to_float(__ldg(reinterpret_cast<const uint2*>(gu + base + (gate_first ? inter : 0))), u);
+    const __nv_bfloat16* grow = gu + (long long)r * 2 * inter + (gate_first ? 0 : inter) + lane * 4;
+    const __nv_bfloat16* urow = gu + (long long)r * 2 * inter + (gate_first ? inter : 0) + lane * 4;
+    for (int b0 = 0; b0 < nb; b0 += 4) {
+        uint2 graw[4], uraw[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) a[j] = __fmul_rn(silu_f32(g[j]), u[j]);
-    float s;
-    const uint32_t packed = quant_block_4(a, &s);
-    *reinterpret_cast<uint32_t*>(q + (long long)r * inter + b * 128 + lane * 4) = packed;
-    if (lane == 0) scales[r * ss_r + b * ss_b] = s;
+        for (int i = 0; i < 4; ++i) {
+            if (b0 + i < nb) {
+                graw[i] = __ldcs(reinterpret_cast<const uint2*>(grow + (b0 + i) * 128));
+                uraw[i] = __ldcs(reinterpret_cast<const uint2*>(urow + (b0 + i) * 128));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (b0 + i < nb) {
+                float g[4], u[4], a[4];
+                bf16x4_to_float(graw[i], g);
+                bf16x4_to_float(uraw[i], u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) a[j] = __fmul_rn(silu_f32(g[j]), u[j]);
+                float s;
+                const uint32_t packed = quant_block_4(a, &s);
+                *reinterpret_cast<uint32_t*>(q + (long long)r * inter + (b0 + i) * 128 + lane * 4) = packed;
+                if (lane == 0) scales[r * ss_r + (long long)(b0 + i) * ss_b] = s;
+            }
+        }
+    }
 }
 
 // Softmax over E logits + top-k (ties -> lowest expert index), weights renormalised over the

@@ -71,7 +71,7 @@ class SymmetricBuffer:
 
 class EpMoeLayer:
     def __init__(self, data: dict, T_local: int, top_k: int = 8, align: int = 128, gate_first: bool = False,
-                 group=None):
+                 group=None, fuse_act: bool = False):
         import torch.distributed as dist
         self.L = _lib.lib()
         x_q, xs = data["hidden_states"], data["hidden_states_scale"]
@@ -95,7 +95,7 @@ class EpMoeLayer:
             xs = xs.t()
         if tuple(x_q.shape) != (T_local, H) or tuple(xs.shape) != (T_local, H // 128):
             raise ValueError("hidden_states must be [T_local, H] with scales [T_local, H/128]")
-        self.x_q, self.xs, self.gate_first = x_q, xs, gate_first
+        self.x_q, self.xs, self.gate_first, self.fuse_act = x_q, xs, gate_first, fuse_act
         self.T, self.H, self.I, self.E_local, self.E_total, self.top_k, self.align = T_local, H, inter, E_local, E_total, top_k, align
         n_pairs = T_local * top_k
         self.n_pairs = n_pairs
@@ -128,7 +128,7 @@ class EpMoeLayer:
         self.layout = torch.full((cap,), -1, **i32)
         self.ws_bytes = self.L.moe_ep_workspace_bytes(_i64(n_pairs), _i32(E_total))
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
-        self.g1 = torch.empty((cap, two_i), dtype=torch.bfloat16, device=dev)
+        self.g1 = torch.empty((cap if not fuse_act else 1, two_i), dtype=torch.bfloat16, device=dev)
         self.a2 = torch.empty((cap, inter), dtype=torch.float8_e4m3fn, device=dev)
         self.s2 = torch.empty((inter // 128, cap), dtype=torch.float32, device=dev)
         self._keep = (w13, s13, w2, s2)
@@ -137,8 +137,14 @@ class EpMoeLayer:
         self.s1_t = self._wrap(self._local["sa"], (H // 128, cap), torch.float32).t()
         self.y_t = self._wrap(self._local["y"], (cap, H), torch.bfloat16)
         rows_used = self.offsets[E_local:E_local + 1]
-        self.gemm1 = grouped_gemm.bind_contiguous(self.a1_t, self.s1_t, w13, s13, self.g1, self.layout, rows_used)
-        self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used)
+        if fuse_act:
+            self.gemm1 = grouped_gemm.bind_gate_up_act(self.a1_t, self.s1_t, w13, s13, self.a2, self.s2.t(), self.layout,
+                                                       gate_first, rows_used)
+        else:
+            self.gemm1 = grouped_gemm.bind_contiguous(self.a1_t, self.s1_t, w13, s13, self.g1, self.layout, rows_used,
+                                                      workspace=False)
+        self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used,
+                                                  workspace=False)    # activation scales are amax/448, never 2^e
         self.epoch = 0
         if self.world > 1:
             dist.barrier(group)
@@ -192,10 +198,11 @@ class EpMoeLayer:
             mark("dispatch+barrier")
             self.gemm1()
             mark("gate_up_gemm")
-            _lib.check(L.moe_silu_mul_requant(_vp(self.g1.data_ptr()), _vp(self.a2.data_ptr()), _vp(self.s2.data_ptr()),
-                                              _i64(1), _i64(self.cap), _vp(self.layout.data_ptr()), _i32(self.cap),
-                                              _i32(self.I), _i32(1 if self.gate_first else 0), st))
-            mark("silu_mul_requant")
+            if not self.fuse_act:
+                _lib.check(L.moe_silu_mul_requant(_vp(self.g1.data_ptr()), _vp(self.a2.data_ptr()), _vp(self.s2.data_ptr()),
+                                                  _i64(1), _i64(self.cap), _vp(self.layout.data_ptr()), _i32(self.cap),
+                                                  _i32(self.I), _i32(1 if self.gate_first else 0), st))
+                mark("silu_mul_requant")
             self.gemm2()
             mark("down_gemm")
             self._barrier(st)

@@ -114,6 +114,44 @@ def bind_masked(a, sfa, b, sfb, d, masked_m, workspace=True) -> _BoundGG:
     return _BoundGG("moe_gg_fp8_masked", a, b, sfa2, strides, sfb, masked_m, d, G, max_m, N, K, None, workspace)
 
 
+class _BoundGateUpAct:
+    """gate_up grouped GEMM with SiLU*mul + 1x128 FP8 requant in the epilogue; ``__call__`` launches."""
+
+    def __init__(self, a, sfa, sfa_strides, b, sfb, act_q, act_s, layout, gate_first, rows_used, G, M, N, K):
+        self._keep = (a, sfa, b, sfb, act_q, act_s, layout, rows_used)
+        self._device = a.device
+        self._args = _lib.GGArgs(a=_ptr(a), b=_ptr(b), sfa=_ptr(sfa), sfa_stride_row=sfa_strides[0],
+                                 sfa_stride_kblk=sfa_strides[1], sfb=_ptr(sfb), layout=_ptr(layout), d=None, ldd=0,
+                                 G=G, M=M, N=N, K=K, d_dtype=0,
+                                 rows_used=_ptr(rows_used) if rows_used is not None else None, workspace=None,
+                                 workspace_bytes=0)
+        self._act = (ctypes.c_void_p(_ptr(act_q)), ctypes.c_void_p(_ptr(act_s)), ctypes.c_int64(act_s.stride(0)),
+                     ctypes.c_int64(act_s.stride(1)), ctypes.c_int32(1 if gate_first else 0))
+        self.out = (act_q, act_s)
+
+    def __call__(self):
+        with torch.cuda.device(self._device):
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(_lib.lib().moe_gg_fp8_gate_up_act(ctypes.byref(self._args), *self._act, ctypes.c_void_p(stream)))
+        return self.out
+
+
+def bind_gate_up_act(a, sfa, b, sfb, act_q, act_s, grouped_layout, gate_first=False, rows_used=None):
+    """a fp8[M,K], sfa f32[M,K/128], b fp8[G,2I,K], sfb f32[G,2I/128,K/128] -> act_q fp8[M,I], act_s f32[M,I/128]
+    (any strides) = 1x128 requant of silu(gate)*up, computed from the fp32 accumulators inside the GEMM."""
+    _check_fp8(a, "a"); _check_fp8(b, "b"); _check_fp8(act_q, "act_q")
+    M, K = a.shape
+    G, N, Kb = b.shape
+    if Kb != K or K % 128 or N % 256:
+        raise ValueError("K must match and be a multiple of 128; N = 2*I must be a multiple of 256")
+    strides = _scale_strides(sfa, M, K // 128, "sfa")
+    if sfb.dtype != torch.float32 or tuple(sfb.shape) != (G, N // 128, K // 128) or not sfb.is_contiguous():
+        raise ValueError(f"sfb must be contiguous float32 [{G}, {N // 128}, {K // 128}]")
+    if tuple(act_q.shape) != (M, N // 2) or tuple(act_s.shape) != (M, N // 256) or act_s.dtype != torch.float32:
+        raise ValueError("act_q must be [M, I] and act_s float32 [M, I/128]")
+    return _BoundGateUpAct(a, sfa, strides, b, sfb, act_q, act_s, grouped_layout, gate_first, rows_used, G, M, N, K)
+
+
 def m_grouped_fp8_gemm_nt_contiguous(a, sfa, b, sfb, d, grouped_layout):
     """One-shot form (argument order of the kernel the reference baselines against: (a, sfa), (b, sfb), d, layout)."""
     return bind_contiguous(a, sfa, b, sfb, d, grouped_layout)()

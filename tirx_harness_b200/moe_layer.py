@@ -27,7 +27,7 @@ class MoeLayer:
     """Binds one layer's tensors and workspace; ``__call__`` launches the whole pipeline."""
 
     def __init__(self, data: dict, T: int, top_k: int = 8, e_lo: int = 0, align: int = 128,
-                 gate_first: bool = False):
+                 gate_first: bool = False, fuse_act: bool = False):
         x_q, xs = data["hidden_states"], data["hidden_states_scale"]
         w13, s13 = data["gemm1_weights"], data["gemm1_weights_scale"]
         w2, s2 = data["gemm2_weights"], data["gemm2_weights_scale"]
@@ -62,7 +62,7 @@ class MoeLayer:
             logits=_p(logits), topk_ids=_p(ids), topk_weights=_p(wts), w13=_p(w13), w13_scale=_p(s13.contiguous()),
             w2=_p(w2), w2_scale=_p(s2.contiguous()), out=_p(out), workspace=_p(self.workspace),
             workspace_bytes=self.ws_bytes, T=T, H=H, I=inter, E=E, E_global=e_global, e_lo=e_lo, top_k=top_k,
-            align=align, gate_first=1 if gate_first else 0)
+            align=align, gate_first=1 if gate_first else 0, fuse_act=1 if fuse_act else 0)
         self.out = out
 
     def __call__(self):
