@@ -32,10 +32,18 @@ DATASHEET_HBM_GBS = 8000.0
 NCU_TRAFFIC_BYTES = {"gemm": None}
 
 WORKLOADS = {
-    # name: (G, rows per group, N, K)
+    # contiguous layout: G groups of m rows (or `sizes` rows each, padded to 128)
     "gemm": dict(G=8, m=4096, N=4096, K=7168,
                  desc="m-grouped contiguous FP8 GEMM, DeepSeek-V3 gate_up: G=8 x 4096 rows (M=32768), N=4096, K=7168"),
     "tiny": dict(G=2, m=128, N=512, K=512, desc="tiny contiguous FP8 GEMM G=2 x 128 rows, N=512, K=512"),
+    "zipf": dict(G=64, zipf_rows=65536, N=7168, K=2048,
+                 desc="load-imbalance stress, contiguous layout: G=64 experts, Zipf(s=1.2) token counts over 65536 "
+                      "routed rows, each padded to a multiple of 128; N=7168, K=2048"),
+    # masked layout (decode): G groups of max_m rows, masked_m ~ U{0..max_m}
+    "masked_gate_up": dict(G=32, max_m=256, N=4096, K=7168, masked=True,
+                           desc="masked-layout FP8 grouped GEMM (decode): G=32, max_m=256, masked_m~U[0,256], N=4096, K=7168"),
+    "masked_down": dict(G=32, max_m=256, N=7168, K=2048, masked=True,
+                        desc="masked-layout FP8 grouped GEMM (decode): G=32, max_m=256, masked_m~U[0,256], N=7168, K=2048"),
 }
 
 
@@ -107,11 +115,29 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def _group_sizes(cfg, seed=0):
+    """Valid rows per group."""
+    if cfg.get("masked"):
+        import torch
+        g = torch.Generator().manual_seed(seed)
+        return torch.randint(0, cfg["max_m"] + 1, (cfg["G"],), generator=g).tolist()
+    if "zipf_rows" in cfg:
+        from tirx_harness_b200.workloads import zipf_group_sizes
+        return zipf_group_sizes(cfg["G"], cfg["zipf_rows"], 1.2)
+    return [cfg["m"]] * cfg["G"]
+
+
 def _device_case(cfg, seed, device):
     """Seeded synthetic operands generated on the device (same law as workloads.make_contiguous_case)."""
     import torch
-    G, m, N, K = cfg["G"], cfg["m"], cfg["N"], cfg["K"]
-    M = G * m
+    G, N, K = cfg["G"], cfg["N"], cfg["K"]
+    sizes = _group_sizes(cfg, 0)
+    masked = bool(cfg.get("masked"))
+    if masked:
+        rows_per = [cfg["max_m"]] * G
+    else:
+        rows_per = [(m + 127) // 128 * 128 for m in sizes]
+    M = sum(rows_per)
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     sfa = torch.exp2(torch.randint(-4, 1, (M, K // 128), generator=gen, device=device).float())
@@ -127,16 +153,34 @@ def _device_case(cfg, seed, device):
         x = torch.randn((N, K), generator=gen, device=device)
         full = sfb[g].repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)
         B[g] = (x / full).clamp_(-448, 448).to(torch.float8_e4m3fn)
-    gl = (torch.arange(M, device=device) // m).to(torch.int32)
     D = torch.zeros((M, N), dtype=torch.bfloat16, device=device)
-    return dict(A=A, B=B, SFA=sfa, SFB=sfb, D=D, grouped_layout=gl, G=G, M=M, N=N, K=K)
+    data = dict(A=A, B=B, SFA=sfa, SFB=sfb, D=D, G=G, M=M, N=N, K=K, sizes=sizes)
+    if masked:
+        data["masked_m"] = torch.tensor(sizes, dtype=torch.int32, device=device)
+    else:
+        gl = torch.full((M,), -1, dtype=torch.int32)
+        r = 0
+        for g, (m, mp) in enumerate(zip(sizes, rows_per)):
+            gl[r:r + m] = g
+            r += mp
+        data["grouped_layout"] = gl.to(device)
+    return data
+
+
+def _bind(gg, cfg, data):
+    if cfg.get("masked"):
+        G, mm, N, K = cfg["G"], cfg["max_m"], cfg["N"], cfg["K"]
+        return gg.bind_masked(data["A"].view(G, mm, K), data["SFA"].view(G, mm, K // 128), data["B"], data["SFB"],
+                              data["D"].view(G, mm, N), data["masked_m"])
+    return gg.setup(data, data["G"], data["M"], data["N"], data["K"])
 
 
 def _algorithmic(cfg):
-    G, m, N, K = cfg["G"], cfg["m"], cfg["N"], cfg["K"]
-    M = G * m
-    flops = 2.0 * M * N * K
-    bytes_ = M * K + G * N * K + M * N * 2 + M * (K // 128) * 4 + G * ((N + 127) // 128) * (K // 128) * 4
+    """FLOPs and bytes over VALID rows only."""
+    G, N, K = cfg["G"], cfg["N"], cfg["K"]
+    rows = sum(_group_sizes(cfg, 0))
+    flops = 2.0 * rows * N * K
+    bytes_ = rows * K + G * N * K + rows * N * 2 + rows * (K // 128) * 4 + G * ((N + 127) // 128) * (K // 128) * 4
     return flops, float(bytes_)
 
 
@@ -144,8 +188,8 @@ def cpu_baseline(cfg, seed=0, rows_per_group=1024):
     """Times the CPU oracle (simulator-order FMA chain) on a bounded row sample of the workload."""
     import numpy as np
     from oracle import oracle as orc
-    G, m, N, K = cfg["G"], cfg["m"], cfg["N"], cfg["K"]
-    rows_per_group = min(rows_per_group, m)
+    G, N, K = cfg["G"], cfg["N"], cfg["K"]
+    rows_per_group = max(1, min(rows_per_group, max(_group_sizes(cfg, 0)), 8192 // G))
     rng = np.random.default_rng(seed)
     M = G * rows_per_group
     A = rng.integers(0, 0x7F, size=(M, K), dtype=np.uint8)
@@ -334,8 +378,9 @@ def run_ours(args):
 
     cfg = WORKLOADS[args.workload]
     data = _device_case(cfg, seed=rank, device=device)
-    launch = gg.setup(data, data["G"], data["M"], data["N"], data["K"])
+    launch = _bind(gg, cfg, data)
     flops, alg_bytes = _algorithmic(cfg)
+    layout_key = "masked_m" if cfg.get("masked") else "grouped_layout"
 
     for _ in range(max(args.warmup, 3)):
         launch()
@@ -368,14 +413,14 @@ def run_ours(args):
         e2e_steps = max(3, min(args.steps, 10))
         hA = data["A"].view(torch.uint8).cpu().pin_memory()
         hS = data["SFA"].cpu().pin_memory()
-        hL = data["grouped_layout"].cpu().pin_memory()
+        hL = data[layout_key].cpu().pin_memory()
         hD = torch.empty(data["D"].shape, dtype=torch.bfloat16).pin_memory()
         dA8 = data["A"].view(torch.uint8)
 
         def e2e_step():
             dA8.copy_(hA, non_blocking=True)
             data["SFA"].copy_(hS, non_blocking=True)
-            data["grouped_layout"].copy_(hL, non_blocking=True)
+            data[layout_key].copy_(hL, non_blocking=True)
             launch()
             hD.copy_(data["D"], non_blocking=True)
 
@@ -402,18 +447,24 @@ def run_ours(args):
         fp8_peak = 2.0 * (peaks["bf16_sustained"] or peaks["bf16_burst"])
         per_gpu = value / world
         traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+        ridge = fp8_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
+        hbm_bound = flops / alg_bytes < ridge
         line = {
             "metric": "grouped_gemm_fp8_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": cfg["desc"] + (f"; per GPU, {world} GPUs each own 8 experts" if world > 1 else ""),
+            "config": {"workload": cfg["desc"] + (f"; per GPU, {world} GPUs each own {cfg['G']} experts" if world > 1 else ""),
                        "scales": "fp32, A 1x128 per row, B 128x128, 2^{-4..0}", "accumulate": "fp32", "out": "bf16",
-                       "l2": "inputs (746 MB per launch) larger than L2, no flush", "seed": 0,
+                       "l2": f"inputs ({alg_bytes / 1e6:.0f} MB per launch) larger than L2, no flush", "seed": 0,
                        "timing": "CUDA events around K back-to-back launches, max over ranks"},
             "clocks": clocks.summary(),
             "e2e": e2e,
             "gpu_launches": args.steps * 3,      # per step: scale check+pack, block-scaled GEMM, promotion GEMM (exits at once when not needed)
-            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
+            "roofline": {"bound": "hbm", "achieved": alg_bytes / (ms_step * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": alg_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                         "traffic": traffic, "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
+                         "tflops": per_gpu} if hbm_bound else
+                        {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": per_gpu / fp8_peak, "traffic": traffic,
                          "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
                                         "fp8 tensor rate is twice bf16",
@@ -446,8 +497,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["layer"], default="gemm")
-    ap.add_argument("--with-layer", action="store_true",
-                    help="after the grouped-GEMM measurement also time the expert-parallel MoE layer (extra object)")
+    ap.add_argument("--no-layer", dest="with_layer", action="store_false",
+                    help="skip the expert-parallel MoE layer measurement that follows the grouped-GEMM one "
+                         "(it is reported as the extra object `moe_layer` of the same JSON line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()

@@ -85,24 +85,12 @@ struct Tile {
     int rows;        // masked: number of valid rows in this tile (<= BM); contiguous: BM
 };
 
-// Smallest group id > prev among grouped_layout[m0 .. m0+127] (INT_MAX if none).  Warp-collective.
-__device__ __forceinline__ int next_group_in_block(const int* __restrict__ layout, int m0, int M,
-                                                   int prev, int lane) {
-    int best = INT_MAX;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        int r = m0 + lane * 4 + j;
-        if (r < M) {
-            int v = __ldg(layout + r);
-            if (v > prev && v < best) best = v;
-        }
-    }
-    return __reduce_min_sync(0xffffffffu, best);
-}
-
 // Static persistent schedule.  All warps of a CTA walk the same sequence.
 //  contiguous: tile index t -> (128-row block, column block); a row block is visited once per
-//              distinct non-negative group id found in it (one when groups are 128-aligned).
+//              distinct non-negative group id found in it (one when groups are 128-aligned).  The
+//              block's 128 layout entries (4 per lane) are fetched one tile AHEAD: as soon as a tile has
+//              been handed out and its block holds no further group, the loads for the next candidate
+//              are issued, so their latency is hidden behind the tile's K loop.
 //  masked:     compact enumeration of (group, row block < ceil(masked_m/128), column block)
 //              through a prefix table in shared memory.
 template <bool MASKED>
@@ -110,6 +98,26 @@ struct Scheduler {
     const GGParams& p;
     const int* prefix;   // masked: smem prefix of row blocks per group, [G+1]
     int t, lane, prev_g, total;
+    int vals[4];         // contiguous: layout entries of the row block of tile t held by this lane
+
+    __device__ __forceinline__ void fetch() {
+        if (t < total) {
+            const int m0 = (t / p.num_n_blocks) * gg::BM;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = m0 + lane * 4 + j;
+                vals[j] = r < p.M ? __ldg(p.layout + r) : -1;
+            }
+        }
+    }
+    // smallest group id > after in the fetched block, INT_MAX if none.  Warp-collective.
+    __device__ __forceinline__ int next_group(int after) const {
+        int best = INT_MAX;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (vals[j] > after && vals[j] < p.G && vals[j] < best) best = vals[j];
+        return __reduce_min_sync(0xffffffffu, best);
+    }
 
     __device__ __forceinline__ Scheduler(const GGParams& p_, const int* prefix_, int lane_)
         : p(p_), prefix(prefix_), t(blockIdx.x), lane(lane_), prev_g(-1) {
@@ -123,6 +131,7 @@ struct Scheduler {
                 m_blocks = (used + gg::BM - 1) / gg::BM;
             }
             total = m_blocks * p_.num_n_blocks;
+            fetch();
         }
     }
 
@@ -146,18 +155,23 @@ struct Scheduler {
             return true;
         } else {
             while (t < total) {
-                int m_blk = t / p.num_n_blocks;
-                int g = next_group_in_block(p.layout, m_blk * gg::BM, p.M, prev_g, lane);
-                if (g == INT_MAX || g >= p.G) {
+                const int g = next_group(prev_g);
+                if (g == INT_MAX) {             // block exhausted (or all padding): next candidate
                     t += gridDim.x;
                     prev_g = -1;
+                    fetch();
                     continue;
                 }
-                prev_g = g;
-                tile.m0 = m_blk * gg::BM;
+                tile.m0 = (t / p.num_n_blocks) * gg::BM;
                 tile.n_blk = t % p.num_n_blocks;
                 tile.g = g;
                 tile.rows = gg::BM;
+                prev_g = g;
+                if (next_group(g) == INT_MAX) { // nothing else in this block: start fetching the next one now
+                    t += gridDim.x;
+                    prev_g = -1;
+                    fetch();
+                }
                 return true;
             }
             return false;

@@ -94,28 +94,33 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t mask) {
         ::"r"(bar), "h"(mask) : "memory");
 }
 
-// Smallest group id > prev among grouped_layout[m0 .. m0+255] (INT_MAX if none).  Warp-collective.
-__device__ __forceinline__ int next_group_in_block256(const int* __restrict__ layout, int m0, int M,
-                                                      int prev, int lane) {
-    int best = INT_MAX;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        int r = m0 + lane * 8 + j;
-        if (r < M) {
-            int v = __ldg(layout + r);
-            if (v > prev && v < best) best = v;
-        }
-    }
-    return __reduce_min_sync(0xffffffffu, best);
-}
-
 // Static persistent schedule over CLUSTERS.  Both CTAs of a pair and all their warps walk the same
-// sequence.  A tile = (256-row block, column block, group); tile.m0 is THIS CTA's first row.
+// sequence.  A tile = (256-row block, column block, group); tile.m0 is THIS CTA's first row.  In the
+// contiguous layout the block's 256 layout entries (8 per lane) are fetched one tile ahead.
 template <bool MASKED>
 struct PairScheduler {
     const GGParams& p;
     const int* prefix;   // masked: prefix of 256-row blocks per group
     int t, lane, prev_g, total, stride, rank;
+    int vals[8];
+
+    __device__ __forceinline__ void fetch() {
+        if (t < total) {
+            const int m0 = (t / p.num_n_blocks) * 256;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r = m0 + lane * 8 + j;
+                vals[j] = r < p.M ? __ldg(p.layout + r) : -1;
+            }
+        }
+    }
+    __device__ __forceinline__ int next_group(int after) const {
+        int best = INT_MAX;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (vals[j] > after && vals[j] < p.G && vals[j] < best) best = vals[j];
+        return __reduce_min_sync(0xffffffffu, best);
+    }
 
     __device__ __forceinline__ PairScheduler(const GGParams& p_, const int* prefix_, int lane_, int rank_)
         : p(p_), prefix(prefix_), t(blockIdx.x >> 1), lane(lane_), prev_g(-1), stride(gridDim.x >> 1), rank(rank_) {
@@ -128,6 +133,7 @@ struct PairScheduler {
                 rows = used < 0 ? 0 : (used > p_.M ? p_.M : used);
             }
             total = ((rows + 255) / 256) * p_.num_n_blocks;
+            fetch();
         }
     }
 
@@ -153,18 +159,23 @@ struct PairScheduler {
             return true;
         } else {
             while (t < total) {
-                int m_blk = t / p.num_n_blocks;
-                int g = next_group_in_block256(p.layout, m_blk * 256, p.M, prev_g, lane);
-                if (g == INT_MAX || g >= p.G) {
+                const int g = next_group(prev_g);
+                if (g == INT_MAX) {
                     t += stride;
                     prev_g = -1;
+                    fetch();
                     continue;
                 }
-                prev_g = g;
-                tile.m0 = m_blk * 256 + rank * gg2::BM;
+                tile.m0 = (t / p.num_n_blocks) * 256 + rank * gg2::BM;
                 tile.n_blk = t % p.num_n_blocks;
                 tile.g = g;
                 tile.rows = gg2::BM;
+                prev_g = g;
+                if (next_group(g) == INT_MAX) {
+                    t += stride;
+                    prev_g = -1;
+                    fetch();
+                }
                 return true;
             }
             return false;
