@@ -242,6 +242,10 @@ LAYER = dict(T=16384, H=7168, I=2048, E=256, top_k=8,
                   "softmax top-8; dispatch -> gate_up grouped GEMM -> SiLU*mul FP8 requant -> down grouped GEMM -> combine")
 
 
+LAYER_SMALL = dict(LAYER, T=2048, E=32,
+                   desc="one rank's share of the 8-GPU MoE layer run alone: 2048 tokens, 32 experts (small case for ncu)")
+
+
 def _layer_case(world, rank, device, cfg=LAYER, seed=0):
     """This rank's token slice and experts (synthetic, generated on the device)."""
     import torch
@@ -275,8 +279,8 @@ def run_layer(args, world, rank, device, barrier, steps, warmup):
     import torch.distributed as dist
     from tirx_harness_b200 import ep_layer
     from tirx_harness_b200 import grouped_gemm as gg
-    cfg = LAYER
-    data = _layer_case(world, rank, device)
+    cfg = LAYER_SMALL if getattr(args, "layer_small", False) else LAYER
+    data = _layer_case(world, rank, device, cfg)
     Tl = cfg["T"] // world
     layer = ep_layer.setup(data, Tl, top_k=cfg["top_k"])
     for _ in range(max(warmup, 3)):
@@ -501,6 +505,7 @@ def main():
                     help="skip the expert-parallel MoE layer measurement that follows the grouped-GEMM one "
                          "(it is reported as the extra object `moe_layer` of the same JSON line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer-small", action="store_true", help="layer workload at 2048 tokens / 32 experts (profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

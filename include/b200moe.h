@@ -54,6 +54,10 @@ extern "C" {
  *           promotion -- same exact products, fp32 accumulation, about 1.5x faster.  Otherwise, and
  *           always without workspace, the promotion kernel runs.  The decision is taken per call on
  *           the device from the current scale values; nothing is cached between calls.
+ *   scatter_meta  contiguous layout, bf16 output only, may be NULL.  If given (int32 [M]), valid row r is not
+ *           stored at d + r*ldd but at scatter_base[meta >> 24] + (meta & 0xFFFFFF)*ldd, meta = scatter_meta[r]:
+ *           the expert-parallel down GEMM uses it to store every output row directly into the slot of the
+ *           rank that owns the token (bases may be peer-mapped memory of other GPUs; plain stores).
  * Requirements: K % 128 == 0, N % 8 == 0, a/b 16-byte aligned, d 16-byte aligned, ldd % 8 == 0.
  */
 typedef struct moe_gg_args {
@@ -71,6 +75,8 @@ typedef struct moe_gg_args {
     const int32_t* rows_used;
     void* workspace;
     uint64_t workspace_bytes;
+    const int32_t* scatter_meta;
+    void* scatter_base[8];
 } moe_gg_args;
 
 /* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With
@@ -216,13 +222,15 @@ int moe_ipc_close(void* ptr);
  *   sa     f32  [H/128, cap_rows]   its row scales, MN-major
  *   y      bf16 [cap_rows, H]       down-GEMM output rows
  *   counts int32 [world, E_total]   row s = number of pairs rank s routes to each expert
- *   flags  int32 [world]            barrier epochs                                                */
+ *   flags  int32 [world]            barrier epochs
+ *   meta   int32 [cap_rows]         (source rank << 24) | source pair index of each received row           */
 typedef struct moe_ep_peers {
     void* a[8];
     float* sa[8];
     const void* y[8];
     int32_t* counts[8];
     int32_t* flags[8];
+    int32_t* meta[8];
 } moe_ep_peers;
 
 /* Cross-GPU barrier on `stream`: publishes `epoch` (strictly increasing per call) to every peer and
@@ -246,10 +254,10 @@ int moe_ep_plan(const moe_ep_peers* peers, const int32_t* ids, int64_t n_pairs, 
                 size_t workspace_bytes, void* stream);
 
 /* Dispatch all-to-all fused with the permutation: every pair's e4m3 row and scales are stored directly
- * into the owner rank's grouped-layout buffers. */
+ * into the owner rank's grouped-layout buffers, together with the row's return address (meta). */
 int moe_ep_dispatch(const moe_ep_peers* peers, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
                     const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
-                    int32_t cap_rows, int32_t world, void* stream);
+                    int32_t cap_rows, int32_t rank, int32_t world, void* stream);
 
 /* Combine all-to-all fused with the weighted sum: each token loads its top_k expert rows from the owners'
  * y buffers and accumulates w * row in fp32 (slot order), writing bf16. */

@@ -36,7 +36,7 @@ def test_struct_layouts_match_header_field_order():
     from tirx_harness_b200 import _lib
     text = open(os.path.join(ROOT, "include", "b200moe.h")).read()
     for cname, pystruct in (("moe_gg_args", _lib.GGArgs), ("moe_layer_args", _lib.LayerArgs),
-                            ("moe_layer_view", _lib.LayerView)):
+                            ("moe_layer_view", _lib.LayerView), ("moe_ep_peers", _lib.EpPeers)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -45,7 +45,7 @@ def test_struct_layouts_match_header_field_order():
             if not decl:
                 continue
             names = decl.split(None, 1)[1] if not decl.startswith("const") else decl.split(None, 2)[2]
-            fields += [n.strip().lstrip("*").strip() for n in names.split(",")]
+            fields += [re.sub(r"\[\d+\]$", "", n.strip().lstrip("*").strip()) for n in names.split(",")]
         assert fields == [f[0] for f in pystruct._fields_], cname
 
 

@@ -23,6 +23,7 @@ class GGArgs(_c.Structure):
         ("G", _c.c_int32), ("M", _c.c_int32), ("N", _c.c_int32), ("K", _c.c_int32),
         ("d_dtype", _c.c_int32), ("rows_used", _c.c_void_p),
         ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
+        ("scatter_meta", _c.c_void_p), ("scatter_base", _c.c_void_p * 8),
     ]
 
 
@@ -48,7 +49,7 @@ class LayerView(_c.Structure):
 class EpPeers(_c.Structure):
     """``moe_ep_peers`` of include/b200moe.h."""
     _fields_ = [("a", _c.c_void_p * 8), ("sa", _c.c_void_p * 8), ("y", _c.c_void_p * 8),
-                ("counts", _c.c_void_p * 8), ("flags", _c.c_void_p * 8)]
+                ("counts", _c.c_void_p * 8), ("flags", _c.c_void_p * 8), ("meta", _c.c_void_p * 8)]
 
 
 class B200MoeError(RuntimeError):

@@ -175,7 +175,7 @@ template <bool MASKED>
 int launch_gg(const moe_gg_args* a, void* stream) {
     if (!a) return fail(MOE_ERR_INVALID, "args is NULL");
     if (a->M == 0 && a->G > 0 && a->N > 0 && a->K > 0) return MOE_OK;      // nothing to compute
-    if (!a->a || !a->b || !a->sfa || !a->sfb || !a->layout || !a->d)
+    if (!a->a || !a->b || !a->sfa || !a->sfb || !a->layout || (!a->d && !a->scatter_meta))
         return fail(MOE_ERR_INVALID, "a, b, sfa, sfb, layout and d must all be non-NULL");
     if (a->G <= 0 || a->N <= 0 || a->K <= 0 || a->M < 0)
         return fail(MOE_ERR_INVALID, "G, N, K must be positive and M non-negative (G=%d M=%d N=%d K=%d)", a->G,
@@ -220,6 +220,10 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.rows_used = MASKED ? nullptr : a->rows_used;
     p.mode_flag = nullptr;
     p.act_q = nullptr; p.act_s = nullptr; p.act_ss_r = 0; p.act_ss_b = 0; p.inter = 0; p.gate_first = 0;
+    p.scatter_meta = MASKED ? nullptr : a->scatter_meta;
+    for (int i = 0; i < 8; ++i) p.scatter_base[i] = static_cast<__nv_bfloat16*>(a->scatter_base[i]);
+    if (p.scatter_meta != nullptr && a->d_dtype != MOE_DTYPE_BF16)
+        return fail(MOE_ERR_INVALID, "scattered output is bf16 only");
     p.d = a->d;
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
@@ -231,7 +235,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
 
     // ---- power-of-two-scale path: needs caller workspace; stands down on the device if a scale is not 2^e
-    if (allow_mx && a->workspace != nullptr && (!MASKED || a->M % 128 == 0)) {
+    if (allow_mx && a->workspace != nullptr && (!MASKED || a->M % 128 == 0) && p.scatter_meta == nullptr) {
         const MxLayout ml = mx_layout(a->G, rows_total, a->N, a->K);
         if (a->workspace_bytes < ml.bytes)
             return fail(MOE_ERR_INVALID, "workspace too small: %llu < %zu bytes (moe_gg_workspace_bytes)",
@@ -266,7 +270,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         CUDA_TRY(cudaGetLastError());
         p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
     }
-    if (use_pair_kernel) {
+    if (use_pair_kernel && p.scatter_meta == nullptr) {
         const long long row_blocks = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
         const long long tiles = row_blocks * p.num_n_blocks;
         int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
@@ -626,7 +630,7 @@ static int ep_check(const moe_ep_peers* P, int rank, int world) {
     if (world < 1 || world > EP_MAX_WORLD || rank < 0 || rank >= world)
         return fail(MOE_ERR_INVALID, "world=%d must be in [1, %d] and rank=%d inside it", world, EP_MAX_WORLD, rank);
     for (int i = 0; i < world; ++i)
-        if (!P->a[i] || !P->sa[i] || !P->y[i] || !P->counts[i] || !P->flags[i])
+        if (!P->a[i] || !P->sa[i] || !P->y[i] || !P->counts[i] || !P->flags[i] || !P->meta[i])
             return fail(MOE_ERR_INVALID, "peer table entry %d has a NULL pointer", i);
     return MOE_OK;
 }
@@ -638,6 +642,7 @@ static EpPeers ep_convert(const moe_ep_peers* P) {
         d.y[i] = static_cast<const __nv_bfloat16*>(P->y[i]);
         d.counts[i] = P->counts[i];
         d.flags[i] = P->flags[i];
+        d.meta[i] = P->meta[i];
     }
     return d;
 }
@@ -708,8 +713,8 @@ int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int3
 
 int moe_ep_dispatch(const moe_ep_peers* P, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
                     const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
-                    int32_t cap_rows, int32_t world, void* stream) {
-    int rc = ep_check(P, 0, world);
+                    int32_t cap_rows, int32_t rank, int32_t world, void* stream) {
+    int rc = ep_check(P, rank, world);
     if (rc != MOE_OK) return rc;
     if (!x_q || !x_scale || !ids || !pos) return fail(MOE_ERR_INVALID, "dispatch pointers must be non-NULL");
     if (H <= 0 || H % 128 || top_k <= 0 || E_local <= 0) return fail(MOE_ERR_INVALID, "H must be a multiple of 128; top_k, E_local positive");
@@ -717,7 +722,7 @@ int moe_ep_dispatch(const moe_ep_peers* P, const void* x_q, const float* x_scale
     const int wpb = 8;
     ep_dispatch_kernel<<<(unsigned)((n_pairs + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         ep_convert(P), static_cast<const uint8_t*>(x_q), x_scale, xs_row, xs_blk, ids, pos, n_pairs, top_k, E_local, H,
-        cap_rows);
+        cap_rows, rank);
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }

@@ -62,6 +62,10 @@ struct GGParams {
     const int* layout;           // grouped_layout[M] or masked_m[G]
     const int* rows_used;        // contiguous, optional: device count of leading rows in use (<= M)
     const int* mode_flag;        // optional: this kernel runs only if *mode_flag != 0 (see gg_fp8_mx.cuh)
+    // scattered output (expert-parallel down GEMM): row r is stored at scatter_base[meta >> 24] + (meta & 0xFFFFFF) * ldd
+    // with meta = scatter_meta[r]; the bases may be other GPUs' memory (plain stores only)
+    const int* scatter_meta;
+    __nv_bfloat16* scatter_base[8];
     // fused SiLU*mul requant (FUSE_ACT kernels): N = 2*inter, outputs replace d
     uint8_t* act_q;              // e4m3 [M, inter]
     float* act_s;                // scale of (row r, 128-block b) at act_s[r*act_ss_r + b*act_ss_b]
@@ -509,7 +513,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     }
                 }
             } else if (row_valid) {
-                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+                __nv_bfloat16* drow;
+                if (p.scatter_meta != nullptr) {
+                    const int meta = __ldg(p.scatter_meta + row);
+                    drow = p.scatter_base[(meta >> 24) & 7] + (long long)(meta & 0xFFFFFF) * p.ldd + n0;
+                } else {
+                    drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+                }
 #pragma unroll
                 for (int j = 0; j < 128; j += 8) {
                     if (n0 + j + 8 <= p.N) {

@@ -351,6 +351,7 @@ struct EpPeers {
     const __nv_bfloat16* y[EP_MAX_WORLD];// bf16 [cap_rows, H] expert outputs of each rank
     int* counts[EP_MAX_WORLD];           // int32 [world, E_total]: row s = pairs rank s routes to each expert
     int* flags[EP_MAX_WORLD];            // int32 [world]: barrier epochs written by each peer
+    int* meta[EP_MAX_WORLD];             // int32 [cap_rows]: (source rank << 24) | source pair index of each row
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
@@ -452,7 +453,7 @@ __global__ void ep_layout_kernel(const int* __restrict__ offsets, const int* __r
 __global__ void ep_dispatch_kernel(EpPeers peers, const uint8_t* __restrict__ x, const float* __restrict__ xs,
                                    long long xs_r, long long xs_b, const int* __restrict__ ids,
                                    const int* __restrict__ pos, long long n_pairs, int top_k, int E_local,
-                                   int H, int cap_rows) {
+                                   int H, int cap_rows, int rank) {
     const long long p = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (p >= n_pairs) return;
@@ -465,6 +466,8 @@ __global__ void ep_dispatch_kernel(EpPeers peers, const uint8_t* __restrict__ x,
     for (int i = lane; i < (H >> 4); i += 32) dst[i] = __ldg(src + i);
     float* sdst = peers.sa[d];
     for (int b = lane; b < (H >> 7); b += 32) sdst[(long long)b * cap_rows + row] = __ldg(xs + t * xs_r + b * xs_b);
+    // where this row's result has to go back to: lets the owner's down GEMM store it straight into our slot
+    if (lane == 0) peers.meta[d][row] = (rank << 24) | (int)p;
 }
 
 // Combine: out[t,:] = bf16( sum_j w[t,j] * Y_owner(ids[t,j])[pos[t,j], :] ), rows fetched from the
@@ -487,16 +490,25 @@ __global__ void ep_combine_kernel(EpPeers peers, const int* __restrict__ ids, co
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-        for (int j = 0; j < top_k; ++j) {
-            const __nv_bfloat16* rp = s_row[j];
-            if (rp == nullptr) continue;
-            const float wj = s_w[j];
-            const uint4 raw = *(reinterpret_cast<const uint4*>(rp) + c);
-            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+        // peer loads take microseconds: issue a batch of eight before the first is consumed
+        for (int j0 = 0; j0 < top_k; j0 += 8) {
+            uint4 raw[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(wj, __uint_as_float(u[i] << 16)));
-                acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(wj, __uint_as_float(u[i] & 0xFFFF0000u)));
+            for (int jj = 0; jj < 8; ++jj) {
+                const __nv_bfloat16* rp = (j0 + jj < top_k) ? s_row[j0 + jj] : nullptr;
+                raw[jj] = rp != nullptr ? *(reinterpret_cast<const uint4*>(rp) + c) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                if (j0 + jj < top_k && s_row[j0 + jj] != nullptr) {
+                    const float wj = s_w[j0 + jj];
+                    const uint32_t u[4] = {raw[jj].x, raw[jj].y, raw[jj].z, raw[jj].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(wj, __uint_as_float(u[i] << 16)));
+                        acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(wj, __uint_as_float(u[i] & 0xFFFF0000u)));
+                    }
+                }
             }
         }
         uint4 o;

@@ -5,9 +5,12 @@
 
 Rank r owns experts [r*E_local, (r+1)*E_local) with their weights resident and T_local tokens.
 Per forward: route -> publish per-expert counts to all peers -> barrier -> plan -> dispatch (rows are
-stored straight into the owner's grouped-layout buffer over NVLink) -> barrier -> gate_up grouped GEMM
--> SiLU*mul requant -> down grouped GEMM -> barrier -> combine (each token loads its expert rows from
-the owners' buffers and forms the weighted sum).  The reference emulates this sharding on one GPU
+stored straight into the owner's grouped-layout buffer over NVLink, with their return address) -> barrier
+-> gate_up grouped GEMM -> SiLU*mul requant -> down grouped GEMM -> barrier -> combine (each token loads
+its expert rows from the owners' buffers with 16-byte peer loads and forms the weighted sum).
+``combine="push"`` instead lets the down GEMM's epilogue store every output row directly into the slot of
+the rank that owns the token, followed by a local weighted sum; it is correct but slower at present
+(its 16-byte scattered stores use NVLink poorly: measured 3.6 ms vs 1.6 ms for the down GEMM on 2 GPUs).  The reference emulates this sharding on one GPU
 with ``local_expert_offset`` (mlc-ai/TIRx-harness: evolution/benchmark/flashinfer_bench_evolve/tasks/
 moe/definition.json); with world size 1 this class computes exactly what ``moe_layer.MoeLayer`` does.
 
@@ -71,7 +74,7 @@ class SymmetricBuffer:
 
 class EpMoeLayer:
     def __init__(self, data: dict, T_local: int, top_k: int = 8, align: int = 128, gate_first: bool = False,
-                 group=None, fuse_act: bool = False):
+                 group=None, fuse_act: bool = False, combine: str = "pull"):
         import torch.distributed as dist
         self.L = _lib.lib()
         x_q, xs = data["hidden_states"], data["hidden_states_scale"]
@@ -102,8 +105,13 @@ class EpMoeLayer:
         # worst case: every pair of every rank lands on this rank
         cap = (n_pairs * self.world + align - 1) // align * align + E_local * align
         self.cap = cap
-        # ---- symmetric region: a | sa | y | counts | flags
-        sizes = [cap * H, (H // 128) * cap * 4, cap * H * 2, self.world * E_total * 4, 256]
+        if combine not in ("push", "pull"):
+            raise ValueError("combine must be 'push' or 'pull'")
+        self.combine = combine
+        # ---- symmetric region: a | sa | y (pull: [cap,H] expert outputs; push: [T_local*top_k,H] return slots)
+        #      | counts | flags | meta
+        y_rows = cap if combine == "pull" else n_pairs
+        sizes = [cap * H, (H // 128) * cap * 4, y_rows * H * 2, self.world * E_total * 4, 256, cap * 4]
         offs, o = [], 0
         for s in sizes:
             offs.append(o)
@@ -115,6 +123,7 @@ class EpMoeLayer:
             base = self.symm.ptrs[r]
             self.peers.a[r], self.peers.sa[r], self.peers.y[r] = base + offs[0], base + offs[1], base + offs[2]
             self.peers.counts[r], self.peers.flags[r] = base + offs[3], base + offs[4]
+            self.peers.meta[r] = base + offs[5]
         self._local = dict(a=self.symm.local + offs[0], sa=self.symm.local + offs[1], y=self.symm.local + offs[2])
         # ---- private scratch
         i32 = dict(dtype=torch.int32, device=dev)
@@ -135,7 +144,8 @@ class EpMoeLayer:
         # the grouped GEMMs see the symmetric buffers as ordinary tensors of this process
         self.a1_t = self._wrap(self._local["a"], (cap, H), torch.uint8).view(torch.float8_e4m3fn)
         self.s1_t = self._wrap(self._local["sa"], (H // 128, cap), torch.float32).t()
-        self.y_t = self._wrap(self._local["y"], (cap, H), torch.bfloat16)
+        self.y_t = self._wrap(self._local["y"], (y_rows, H), torch.bfloat16)
+        self.meta_t = self._wrap(self.symm.local + offs[5], (cap,), torch.int32)
         rows_used = self.offsets[E_local:E_local + 1]
         if fuse_act:
             self.gemm1 = grouped_gemm.bind_gate_up_act(self.a1_t, self.s1_t, w13, s13, self.a2, self.s2.t(), self.layout,
@@ -143,8 +153,14 @@ class EpMoeLayer:
         else:
             self.gemm1 = grouped_gemm.bind_contiguous(self.a1_t, self.s1_t, w13, s13, self.g1, self.layout, rows_used,
                                                       workspace=False)
-        self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used,
-                                                  workspace=False)    # activation scales are amax/448, never 2^e
+        if combine == "push":
+            bases = [self.peers.y[r] for r in range(self.world)]
+            self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used,
+                                                      workspace=False, scatter=(self.meta_t, bases))
+            self.slot_pos = torch.arange(n_pairs, dtype=torch.int32, device=dev).view(T_local, top_k)
+        else:
+            self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used,
+                                                      workspace=False)    # activation scales are amax/448, never 2^e
         self.epoch = 0
         if self.world > 1:
             dist.barrier(group)
@@ -193,7 +209,8 @@ class EpMoeLayer:
             mark("plan")
             _lib.check(L.moe_ep_dispatch(P, _vp(self.x_q.data_ptr()), _vp(self.xs.data_ptr()), _i64(self.xs.stride(0)),
                                          _i64(self.xs.stride(1)), _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
-                                         _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap, self.world, st))
+                                         _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap, self.rank,
+                                         self.world, st))
             self._barrier(st)
             mark("dispatch+barrier")
             self.gemm1()
@@ -206,8 +223,14 @@ class EpMoeLayer:
             self.gemm2()
             mark("down_gemm")
             self._barrier(st)
-            _lib.check(L.moe_ep_combine(P, _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()), _vp(self.weights.data_ptr()),
-                                        _vp(self.out.data_ptr()), self.T, self.top_k, self.E_local, self.H, self.world, st))
+            if self.combine == "push":
+                _lib.check(L.moe_combine(_vp(self.y_t.data_ptr()), _vp(self.slot_pos.data_ptr()),
+                                         _vp(self.weights.data_ptr()), _vp(self.out.data_ptr()), _i32(self.T),
+                                         _i32(self.top_k), _i32(self.H), st))
+            else:
+                _lib.check(L.moe_ep_combine(P, _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
+                                            _vp(self.weights.data_ptr()), _vp(self.out.data_ptr()), self.T, self.top_k,
+                                            self.E_local, self.H, self.world, st))
             mark("barrier+combine")
         return self.out
 

@@ -43,7 +43,7 @@ class _BoundGG:
     """A validated argument block; ``__call__`` launches on the current stream of the tensors' device."""
 
     def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K, rows_used=None,
-                 workspace=True):
+                 workspace=True, scatter=None):
         rows_total = M if fn_name.endswith("contiguous") else G * M
         ws_bytes = _lib.lib().moe_gg_workspace_bytes(ctypes.c_int32(G), ctypes.c_int64(rows_total), ctypes.c_int32(N),
                                                     ctypes.c_int32(K)) if workspace else 0
@@ -58,6 +58,12 @@ class _BoundGG:
             d_dtype=1 if d.dtype == torch.float32 else 0,
             rows_used=_ptr(rows_used) if rows_used is not None else None,
             workspace=_ptr(self._ws) if self._ws is not None else None, workspace_bytes=ws_bytes)
+        if scatter is not None:          # (meta int32[M] tensor, list of up to 8 base addresses)
+            meta, bases = scatter
+            self._keep = self._keep + (meta,)
+            self._args.scatter_meta = _ptr(meta)
+            for i, b_ in enumerate(bases):
+                self._args.scatter_base[i] = b_
         self._argp = ctypes.byref(self._args)
         self.out = d
 
@@ -68,7 +74,7 @@ class _BoundGG:
         return self.out
 
 
-def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace=True) -> _BoundGG:
+def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace=True, scatter=None) -> _BoundGG:
     """a fp8[M,K], sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128],
     d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row); rows_used: optional
     int32[1] device tensor with the number of leading rows in use."""
@@ -80,14 +86,17 @@ def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace
     strides = _scale_strides(sfa, M, K // 128, "sfa")
     if sfb.dtype != torch.float32 or tuple(sfb.shape) != (G, (N + 127) // 128, K // 128) or not sfb.is_contiguous():
         raise ValueError(f"sfb must be contiguous float32 [{G}, {(N + 127) // 128}, {K // 128}]")
-    if d.dtype not in (torch.bfloat16, torch.float32) or tuple(d.shape) != (M, N) or d.stride(1) != 1:
+    if scatter is not None:
+        if d.dtype != torch.bfloat16 or d.shape[1] != N or d.stride(1) != 1:
+            raise ValueError("with scatter, d only supplies dtype (bf16) and row stride: shape [*, N]")
+    elif d.dtype not in (torch.bfloat16, torch.float32) or tuple(d.shape) != (M, N) or d.stride(1) != 1:
         raise ValueError(f"d must be bfloat16 (or float32) [{M}, {N}] with unit column stride")
     if grouped_layout.dtype != torch.int32 or grouped_layout.numel() != M or not grouped_layout.is_contiguous():
         raise ValueError(f"grouped_layout must be contiguous int32 [{M}]")
     if rows_used is not None and (rows_used.dtype != torch.int32 or not rows_used.is_cuda):
         raise ValueError("rows_used must be an int32 CUDA tensor")
     return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K, rows_used,
-                    workspace)
+                    workspace and scatter is None, scatter)
 
 
 def bind_masked(a, sfa, b, sfb, d, masked_m, workspace=True) -> _BoundGG:
