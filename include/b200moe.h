@@ -32,6 +32,9 @@ extern "C" {
 #define MOE_DTYPE_BF16 0
 #define MOE_DTYPE_F32 1
 
+#define MOE_SF_F32 0            /* block scales as fp32 values */
+#define MOE_SF_UE8M0_PACKED 1   /* block scales as UE8M0 bytes, four consecutive 128-K blocks per int32 */
+
 /* Arguments of the m-grouped FP8 block-scaled GEMM  D_g = deq(A_g) * deq(B_g)^T.
  *   a       e4m3, K-major.  contiguous: [M, K];  masked: [G, M, K] with M = max rows per group
  *   b       e4m3 [G, N, K], K-major
@@ -54,6 +57,13 @@ extern "C" {
  *           promotion -- same exact products, fp32 accumulation, about 1.5x faster.  Otherwise, and
  *           always without workspace, the promotion kernel runs.  The decision is taken per call on
  *           the device from the current scale values; nothing is cached between calls.
+ *   sf_format  MOE_SF_F32 (default, 0) or MOE_SF_UE8M0_PACKED: the scale format of the registered
+ *           grouped_gemm/fp8 workload (evolution/tasks/grouped_gemm_fp8.yaml:16-19; packing as in
+ *           tools/tests/numsim/corpus/kernels/gemm.py:252-263: byte j of a word = K block 4*word+j).
+ *           Then sfa / sfb point to int32 words: word (row r, q) of A at sfa[r*sfa_stride_row + q*sfa_stride_kblk],
+ *           word (group g, column n, q) of B at sfb[g*sfb_stride[0] + n*sfb_stride[1] + q*sfb_stride[2]]
+ *           (B scales per column, as that format stores them).  Needs workspace; always takes the
+ *           block-scaled-MMA path.
  *   scatter_meta  contiguous layout, bf16 output only, may be NULL.  If given (int32 [M]), valid row r is not
  *           stored at d + r*ldd but at scatter_base[meta >> 24] + (meta & 0xFFFFFF)*ldd, meta = scatter_meta[r]:
  *           the expert-parallel down GEMM uses it to store every output row directly into the slot of the
@@ -77,6 +87,8 @@ typedef struct moe_gg_args {
     uint64_t workspace_bytes;
     const int32_t* scatter_meta;
     void* scatter_base[8];
+    int32_t sf_format;
+    int64_t sfb_stride[3];
 } moe_gg_args;
 
 /* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With

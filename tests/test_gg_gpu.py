@@ -276,3 +276,33 @@ def test_masked_power_of_two_path(gg):
     from tirx_harness_b200.workloads import make_masked_case
     _check_masked(gg, make_masked_case(5, 256, 512, 1024, seed=31, law="pow2", masked_m=[256, 0, 129, 77, 255]))
     _check_masked(gg, make_masked_case(3, 384, 384, 512, seed=32, law="pow2", masked_m=[384, 100, 257]))
+
+
+def test_registered_contract_packed_ue8m0_scales_alignment_224(gg):
+    """The registered grouped_gemm/fp8 layout: UE8M0 scales packed four per int32, stored MN-major
+    (tools/tests/numsim/corpus/kernels/gemm.py:252-263 pins the packing), B scales per column, groups padded
+    to 224 rows with -1 in grouped_layout."""
+    from tirx_harness_b200.workloads import make_contiguous_case
+    data = make_contiguous_case(3, [224, 300, 17], 512, 1024, seed=51, law="pow2", alignment=224)
+    M, N, K, G = data["M"], data["N"], data["K"], data["G"]
+    codes_a = (np.log2(data["SFA"].numpy()).astype(np.int32) + 127).astype(np.uint8)             # [M, K/128]
+    sfa_words = orc.ue8m0_pack(codes_a)                                                            # [K/512, M]
+    sfb_col = np.repeat(data["SFB"].numpy(), 128, axis=1)[:, :N]                                   # per column
+    codes_b = (np.log2(sfb_col).astype(np.int32) + 127).astype(np.uint8)                           # [G, N, K/128]
+    sfb_words = np.stack([orc.ue8m0_pack(codes_b[g]) for g in range(G)])                           # [G, K/512, N]
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in data.items()}
+    dev["SFA"] = torch.from_numpy(sfa_words.view(np.int32)).cuda().t()                             # [M, K/512] MN-major
+    dev["SFB"] = torch.from_numpy(sfb_words.view(np.int32)).cuda().permute(0, 2, 1)               # [G, N, K/512]
+    dev["D"].fill_(float("nan"))
+    gg.setup(dev, G, M, N, K)()
+    assert gg.device_status() == 0
+    gl = data["grouped_layout"].numpy()
+    valid = gl >= 0
+    got = bf16_bits(dev["D"])
+    ref = _oracle_contig(data)
+    assert np.isnan(orc.bf16_to_f32(got[~valid])).all()
+    assert_bf16_close(got[valid], ref[valid])
+    # identical to the fp32-scale entry on the same values
+    d2 = torch.full_like(dev["D"], float("nan"))
+    gg.bind_contiguous(dev["A"], data["SFA"].cuda(), dev["B"], data["SFB"].cuda(), d2, dev["grouped_layout"])()
+    assert torch.equal(d2[dev["grouped_layout"] >= 0], dev["D"][dev["grouped_layout"] >= 0])

@@ -175,6 +175,13 @@ template <bool MASKED>
 int launch_gg(const moe_gg_args* a, void* stream) {
     if (!a) return fail(MOE_ERR_INVALID, "args is NULL");
     if (a->M == 0 && a->G > 0 && a->N > 0 && a->K > 0) return MOE_OK;      // nothing to compute
+    const bool packed_sf = a->sf_format == MOE_SF_UE8M0_PACKED;
+    if (a->sf_format != MOE_SF_F32 && !packed_sf) return fail(MOE_ERR_INVALID, "sf_format must be MOE_SF_F32 or MOE_SF_UE8M0_PACKED");
+    if (packed_sf) {
+        if (!a->workspace) return fail(MOE_ERR_INVALID, "packed UE8M0 scales need workspace (moe_gg_workspace_bytes)");
+        if (MASKED && a->M % 128 != 0) return fail(MOE_ERR_UNSUPPORTED, "packed UE8M0 scales with the masked layout need max_m %% 128 == 0");
+        if (a->scatter_meta) return fail(MOE_ERR_UNSUPPORTED, "packed UE8M0 scales cannot be combined with scattered output");
+    }
     if (!a->a || !a->b || !a->sfa || !a->sfb || !a->layout || (!a->d && !a->scatter_meta))
         return fail(MOE_ERR_INVALID, "a, b, sfa, sfb, layout and d must all be non-NULL");
     if (a->G <= 0 || a->N <= 0 || a->K <= 0 || a->M < 0)
@@ -235,7 +242,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
 
     // ---- power-of-two-scale path: needs caller workspace; stands down on the device if a scale is not 2^e
-    if (allow_mx && a->workspace != nullptr && (!MASKED || a->M % 128 == 0) && p.scatter_meta == nullptr) {
+    if ((allow_mx || packed_sf) && a->workspace != nullptr && (!MASKED || a->M % 128 == 0) && p.scatter_meta == nullptr) {
         const MxLayout ml = mx_layout(a->G, rows_total, a->N, a->K);
         if (a->workspace_bytes < ml.bytes)
             return fail(MOE_ERR_INVALID, "workspace too small: %llu < %zu bytes (moe_gg_workspace_bytes)",
@@ -251,8 +258,14 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         CUDA_TRY(cudaMemsetAsync(ws.flag, 0, sizeof(int), st));
         dim3 pgrid(ml.row_blocks + a->G * p.nb128, ml.quads, 1);
-        mx_prep_kernel<<<pgrid, 128, 0, st>>>(a->sfa, a->sfa_stride_row, a->sfa_stride_kblk, a->sfb, (int)rows_total,
-                                              p.num_k_blocks, a->G, p.nb128, ws);
+        if (packed_sf)
+            mx_prep_packed_kernel<<<pgrid, 128, 0, st>>>(
+                reinterpret_cast<const uint32_t*>(a->sfa), a->sfa_stride_row, a->sfa_stride_kblk,
+                reinterpret_cast<const uint32_t*>(a->sfb), a->sfb_stride[0], a->sfb_stride[1], a->sfb_stride[2],
+                (int)rows_total, a->N, a->G, p.nb128, ws);
+        else
+            mx_prep_kernel<<<pgrid, 128, 0, st>>>(a->sfa, a->sfa_stride_row, a->sfa_stride_kblk, a->sfb, (int)rows_total,
+                                                  p.num_k_blocks, a->G, p.nb128, ws);
         CUDA_TRY(cudaGetLastError());
         CUtensorMap tmap_b2, tmap_sfa, tmap_sfb;
         rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx::BN / 2);
@@ -269,6 +282,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
                                                                                ws.flag, ml.quads, status_ptr());
         CUDA_TRY(cudaGetLastError());
         p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
+        if (packed_sf) return MOE_OK;    // UE8M0 bytes are powers of two by construction: nothing else to run
     }
     if (use_pair_kernel && p.scatter_meta == nullptr) {
         const long long row_blocks = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;

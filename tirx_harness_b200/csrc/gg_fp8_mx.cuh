@@ -91,6 +91,27 @@ __global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, 
     if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(ws.flag, 1);
 }
 
+// Same outputs from scales that already ARE UE8M0 bytes packed four to an int32 (the registered
+// grouped_gemm/fp8 contract): word (row m, word q) of A at sfa[m*a_sr + q*a_sq]; word (g, column n, q) of B
+// at sfb[g*b_sg + n*b_sn + q*b_sq] -- B scales are per column here.  Nothing to check: every byte is 2^e.
+__global__ void mx_prep_packed_kernel(const uint32_t* __restrict__ sfa, long long a_sr, long long a_sq,
+                                      const uint32_t* __restrict__ sfb, long long b_sg, long long b_sn, long long b_sq,
+                                      int rows_total, int N, int G, int nb128, MxWorkspace ws) {
+    const int q = blockIdx.y;
+    if ((int)blockIdx.x < ws.row_blocks) {
+        const int r = blockIdx.x * 128 + threadIdx.x;
+        const uint32_t word = r < rows_total ? __ldg(sfa + (long long)r * a_sr + (long long)q * a_sq) : 0x7F7F7F7Fu;
+        ws.sfa_packed[((long long)blockIdx.x * ws.quads + q) * 128 + sf_tile_index(threadIdx.x)] = word;
+    } else {
+        const int idx = blockIdx.x - ws.row_blocks;       // (g, nb)
+        if (idx < G * nb128) {
+            const int g = idx / nb128, n = (idx % nb128) * 128 + threadIdx.x;
+            const uint32_t word = n < N ? __ldg(sfb + (long long)g * b_sg + (long long)n * b_sn + (long long)q * b_sq) : 0x7F7F7F7Fu;
+            ws.sfb_packed[((long long)idx * ws.quads + q) * 128 + sf_tile_index(threadIdx.x)] = word;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ PTX for this path
 __device__ __forceinline__ void tma_load_1d_pair(uint32_t smem_dst, const void* tmap, uint32_t cluster_bar, int32_t c0) {
     asm volatile(
@@ -246,44 +267,53 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
         } else if (warp == 1 && rank == 0) {
             // ------------------------------------------------ MMA issuer (leader)
+            // The tile sequence is computed by the whole warp; a tile's K loop is run by lane 0 alone with
+            // single-thread waits and incrementally updated descriptors.  The tensor pipe only queues a
+            // couple of MMAs, so every instruction this thread spends between two K blocks is a bubble.
             PairScheduler<MASKED> sched(p, prefix, lane, rank);
             Tile tile;
             uint32_t stage = 0, phase = 0, tile_phase = 0, qcount = 0;
             bool ok = true;
+            const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem_a));
+            const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
+            const uint32_t idesc0 = make_idesc_mxf8(2 * BM, BN, 0);
             while (ok && sched.next(tile)) {
-                // the single accumulator must have been drained by both CTAs' epilogues
-                ok = mbar_wait_warp(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
-                if (!ok) break;
-                for (int kb = 0; kb < KB; ++kb) {
-                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (lane == 0) {
-                        if ((kb & 3) == 0) {
+                if (lane == 0) {
+                    // the single accumulator must have been drained by both CTAs' epilogues
+                    ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                    for (int kb = 0; ok && kb < KB; ++kb) {
+                        ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t sub = kb & 3;
+                        if (sub == 0) {
                             const uint32_t src = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
                             const uint32_t tsf = tmem_base + TMEM_SF_BASE + (qcount & 1) * TMEM_SF_STRIDE;
                             tmem_cp_sf_pair(tsf, make_sf_desc(src));
                             tmem_cp_sf_pair(tsf + 4, make_sf_desc(src + 512));
                             tmem_cp_sf_pair(tsf + 8, make_sf_desc(src + 1024));
+                            ++qcount;
                         }
-                        const uint32_t buf = ((kb & 3) == 0 ? qcount : qcount - 1) & 1;
-                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + buf * TMEM_SF_STRIDE;
+                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + ((qcount - 1) & 1) * TMEM_SF_STRIDE;
                         const uint32_t tsfb = tsfa + 4;
-                        const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, kb & 3);
-                        const uint64_t adesc = make_smem_desc_sw128(smem_u32(smem_a + stage * A_STAGE_BYTES));
-                        const uint64_t bdesc = make_smem_desc_sw128(smem_u32(smem_b + stage * B_STAGE_BYTES));
-#pragma unroll
-                        for (int k = 0; k < BK / 32; ++k)
-                            umma_mxf8_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, tsfa, tsfb,
-                                           (kb > 0 || k > 0) ? 1u : 0u);
+                        const uint32_t idesc = idesc0 | (sub << 4) | (sub << 29);
+                        const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
+                        const uint64_t bdesc = bdesc0 + stage * (B_STAGE_BYTES >> 4);
+                        umma_mxf8_pair(tmem_base, adesc, bdesc, idesc, tsfa, tsfb, kb > 0 ? 1u : 0u);
+                        umma_mxf8_pair(tmem_base, adesc + 2, bdesc + 2, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_base, adesc + 4, bdesc + 4, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_base, adesc + 6, bdesc + 6, idesc, tsfa, tsfb, 1u);
                         umma_commit_pair(empty_bar + 8 * stage, 3);
                         if (kb == KB - 1) umma_commit_pair(tfull_bar, 3);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
-                    __syncwarp();
-                    if ((kb & 3) == 0) ++qcount;
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    tile_phase ^= 1;
                 }
-                tile_phase ^= 1;
+                ok = __all_sync(0xffffffffu, ok);
+                stage = __shfl_sync(0xffffffffu, stage, 0);
+                phase = __shfl_sync(0xffffffffu, phase, 0);
+                tile_phase = __shfl_sync(0xffffffffu, tile_phase, 0);
+                qcount = __shfl_sync(0xffffffffu, qcount, 0);
             }
         }
     } else {

@@ -90,6 +90,28 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, ok);
 }
 
+// Single-thread form of the bounded wait (no warp vote): used by the one thread that issues MMAs, where
+// every instruction between "operands ready" and "MMA issued" is on the critical path.
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 1023u) == 0) {
+            if (*abort_flag) return false;
+            uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicOr(status, code);
+                return false;
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ TMA
 // 2-D tiled load global -> shared, completion on an mbarrier (no multicast).
 // c0 = innermost coordinate (elements), c1 = row.  c0 * element size must be a multiple of 16 B.

@@ -161,6 +161,28 @@ def bind_gate_up_act(a, sfa, b, sfb, act_q, act_s, grouped_layout, gate_first=Fa
     return _BoundGateUpAct(a, sfa, strides, b, sfb, act_q, act_s, grouped_layout, gate_first, rows_used, G, M, N, K)
 
 
+def bind_contiguous_packed(a, sfa_words, b, sfb_words, d, grouped_layout) -> _BoundGG:
+    """The registered workload's own scale format: UE8M0 bytes packed four per int32.
+    sfa_words int32 [M, ceil(K/512)] (any strides; DeepGEMM stores it MN-major), sfb_words int32
+    [G, N, ceil(K/512)] (any strides).  Always runs the block-scaled-MMA kernel."""
+    _check_fp8(a, "a"); _check_fp8(b, "b")
+    M, K = a.shape
+    G, N, _ = b.shape
+    kq = (K // 128 + 3) // 4
+    if sfa_words.dtype != torch.int32 or tuple(sfa_words.shape) != (M, kq):
+        raise ValueError(f"packed SFA must be int32 [{M}, {kq}]")
+    if sfb_words.dtype != torch.int32 or tuple(sfb_words.shape) != (G, N, kq):
+        raise ValueError(f"packed SFB must be int32 [{G}, {N}, {kq}]")
+    if d.dtype != torch.bfloat16 and d.dtype != torch.float32 or tuple(d.shape) != (M, N):
+        raise ValueError(f"d must be [{M}, {N}] bf16 or f32")
+    bound = _BoundGG("moe_gg_fp8_contiguous", a, b, sfa_words, (sfa_words.stride(0), sfa_words.stride(1)), sfb_words,
+                     grouped_layout, d, G, M, N, K, None, True)
+    bound._args.sf_format = 1
+    for i in range(3):
+        bound._args.sfb_stride[i] = sfb_words.stride(i)
+    return bound
+
+
 def m_grouped_fp8_gemm_nt_contiguous(a, sfa, b, sfb, d, grouped_layout):
     """One-shot form (argument order of the kernel the reference baselines against: (a, sfa), (b, sfb), d, layout)."""
     return bind_contiguous(a, sfa, b, sfb, d, grouped_layout)()
@@ -174,12 +196,16 @@ def setup(data: dict, G: int, M: int, N: int, K: int):
     """Candidate entry of the registered workload: returns the zero-argument timed callable.
 
     ``data`` holds ``A`` fp8[M,K], ``B`` fp8[G,N,K], ``SFA`` f32[M,K/128] (any strides), ``SFB``
-    f32[G,N/128,K/128], ``D`` bf16[M,N] (written in place) and ``grouped_layout`` int32[M];
+    f32[G,N/128,K/128] -- or the workload's packed UE8M0 form, ``SFA`` int32[M,K/512] and ``SFB``
+    int32[G,N,K/512] with whatever strides they come with --, ``D`` bf16[M,N] (written in place) and
+    ``grouped_layout`` int32[M];
     ``actual_ms`` / ``aligned_ms`` / ``alignment`` are accepted and not needed.
     """
     a, b, d = data["A"], data["B"], data["D"]
     if tuple(a.shape) != (M, K) or tuple(b.shape) != (G, N, K):
         raise ValueError(f"A/B shapes {tuple(a.shape)}/{tuple(b.shape)} do not match G={G} M={M} N={N} K={K}")
+    if data["SFA"].dtype == torch.int32:          # the registered workload's packed UE8M0 scales
+        return bind_contiguous_packed(a, data["SFA"], b, data["SFB"], d, data["grouped_layout"])
     bound = bind_contiguous(a, data["SFA"], b, data["SFB"], d, data["grouped_layout"])
     return bound
 
