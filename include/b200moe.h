@@ -129,6 +129,16 @@ int moe_silu_mul_requant(const void* gate_up_bf16, void* q, float* scales, int64
 int moe_route_topk(const float* logits, int32_t* ids, float* weights, int32_t T, int32_t E, int32_t top_k,
                    void* stream);
 
+/* DeepSeek-V3 "no-aux" routing, the routing block of the registered `moe` workload
+ * (tasks/moe/definition.json, "2) No-aux routing"; called inside trtllm_fp8_block_scale_moe with
+ * routing_method_type=2, n_group=8, topk_group=4 at tasks/moe/baseline.py:31-51): s = sigmoid(logit),
+ * selection on s + bias by groups of 32 experts (sum of the two best per group, topk_group groups kept, top_k
+ * experts among them), weight = s / (sum of selected s + 1e-20) * routed_scaling_factor.  bias: E values,
+ * bf16 (MOE_DTYPE_BF16, the task's dtype) or f32.  E = 32 * n_group, n_group <= 16. */
+int moe_route_deepseek(const float* logits, const void* bias, int32_t bias_dtype, int32_t* ids, float* weights, int32_t T,
+                       int32_t E, int32_t n_group, int32_t topk_group, int32_t top_k, float routed_scaling_factor,
+                       void* stream);
+
 /* Stable permutation plan into the contiguous grouped layout for local experts
  * [e_lo, e_lo + E_local): counts[E_local], offsets[E_local+1] (each expert padded to `align` rows,
  * offsets[E_local] = rows in use), pos[n_pairs] (destination row of pair p = t*top_k + j, -1 if
@@ -182,7 +192,9 @@ int moe_combine(const void* y_bf16, const int32_t* pos, const float* w, void* ou
  * candidate contract of the registered `moe` workload (tasks/moe/benchmark.py:143-182:
  * setup(data, T) -> callable writing the preallocated bf16 output).
  *   x_q e4m3 [T,H], x_scale f32 at [t*xs_stride_row + b*xs_stride_blk]
- *   logits f32 [T, E_global] (softmax top-k routing) or, if NULL, topk_ids/topk_weights [T, top_k]
+ *   logits f32 [T, E_global]: softmax top-k routing, or DeepSeek-V3 no-aux routing when routing_bias is
+ *   given (the registered `moe` task; only experts [e_lo, e_lo+E) contribute, as with its
+ *   local_expert_offset); if logits is NULL, topk_ids/topk_weights [T, top_k] are used as they are
  *   w13 e4m3 [E, 2I, H], w13_scale f32 [E, 2I/128, H/128]; w2 e4m3 [E, H, I], w2_scale f32 [E, H/128, I/128]
  *   E local experts = global ids [e_lo, e_lo+E); out bf16 [T, H] */
 typedef struct moe_layer_args {
@@ -201,6 +213,9 @@ typedef struct moe_layer_args {
     uint64_t workspace_bytes;
     int32_t T, H, I, E, E_global, e_lo, top_k, align, gate_first;
     int32_t fuse_act;        /* != 0: SiLU*mul requant inside the gate_up GEMM (no gate_up matrix in memory) */
+    const void* routing_bias; /* bf16 [E_global] or NULL.  Non-NULL selects DeepSeek-V3 no-aux routing on `logits` */
+    int32_t n_group, topk_group;   /* 0 = the task's 8 and 4 */
+    float routed_scaling_factor;
 } moe_layer_args;
 
 size_t moe_workspace_bytes(int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k, int32_t align);

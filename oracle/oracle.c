@@ -535,3 +535,53 @@ ORC_API int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* DeepSeek-V3 "no-aux" routing of the registered `moe` workload
+ * (evolution/benchmark/flashinfer_bench_evolve/tasks/moe/definition.json, block "2) No-aux routing"):
+ *   s = sigmoid(logit); swb = s + bias; experts are split into n_group groups; a group's score is
+ *   the sum of its two largest swb; the topk_group best groups are kept; among their experts the
+ *   top_k largest swb are selected; weight = s / (sum of selected s + 1e-20) * routed_scaling_factor.
+ * Ties go to the lowest index.  ids are written in descending swb order. */
+ORC_API void orc_route_deepseek(const float* logits, const float* bias, int32_t* ids, float* w, int64_t T,
+                                int64_t E, int64_t n_group, int64_t topk_group, int64_t top_k, float rsf) {
+    const int64_t gs = E / n_group;
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < T; ++t) {
+        float s[1024], swb[1024], gscore[64];
+        int keep[64];
+        for (int64_t e = 0; e < E; ++e) {
+            s[e] = 1.0f / (1.0f + expf(-logits[t * E + e]));
+            swb[e] = s[e] + bias[e];
+        }
+        for (int64_t g = 0; g < n_group; ++g) {
+            int64_t b1 = -1, b2 = -1;
+            for (int64_t j = 0; j < gs; ++j) {
+                int64_t e = g * gs + j;
+                if (b1 < 0 || swb[e] > swb[b1]) { b2 = b1; b1 = e; }
+                else if (b2 < 0 || swb[e] > swb[b2]) b2 = e;
+            }
+            gscore[g] = swb[b1] + swb[b2];
+            keep[g] = 0;
+        }
+        for (int64_t k = 0; k < topk_group; ++k) {
+            int64_t best = -1;
+            for (int64_t g = 0; g < n_group; ++g)
+                if (!keep[g] && (best < 0 || gscore[g] > gscore[best])) best = g;
+            keep[best] = 1;
+        }
+        float sum = 0.0f;
+        for (int64_t k = 0; k < top_k; ++k) {
+            int64_t best = -1;
+            for (int64_t e = 0; e < E; ++e) {
+                if (!keep[e / gs]) continue;
+                int taken = 0;
+                for (int64_t j = 0; j < k; ++j) if (ids[t * top_k + j] == e) taken = 1;
+                if (taken) continue;
+                if (best < 0 || swb[e] > swb[best]) best = e;
+            }
+            ids[t * top_k + k] = (int32_t)best;
+            sum += s[best];
+        }
+        for (int64_t k = 0; k < top_k; ++k) w[t * top_k + k] = s[ids[t * top_k + k]] / (sum + 1e-20f) * rsf;
+    }
+}

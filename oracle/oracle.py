@@ -236,6 +236,18 @@ def route_softmax_topk(logits, top_k: int):
     return ids, w
 
 
+def route_deepseek(logits, bias, top_k=8, n_group=8, topk_group=4, routed_scaling_factor=1.0):
+    """DeepSeek-V3 no-aux routing -> (ids int32 [T, top_k], weights f32 [T, top_k])."""
+    l = _c_arr(logits, np.float32)
+    b = _c_arr(bias, np.float32).reshape(-1)
+    T, E = l.shape
+    ids = np.empty((T, top_k), np.int32)
+    w = np.empty((T, top_k), np.float32)
+    lib().orc_route_deepseek(_p(l), _p(b), _p(ids), _p(w), _i64(T), _i64(E), _i64(n_group), _i64(topk_group),
+                             _i64(top_k), _c.c_float(routed_scaling_factor))
+    return ids, w
+
+
 def permute_plan(ids, e_lo: int, e_local: int, align: int, cap_rows: int | None = None):
     """-> dict(counts, offsets, pos, grouped_layout, src_pair, total_rows)."""
     flat = _c_arr(ids, np.int32).reshape(-1)

@@ -173,8 +173,31 @@ def alphamoe_oracle():
     )
 
 
+def moe_routing():
+    """Runs the routing block of the reference's `moe` task oracle (definition.json, between the markers
+    "# 2) No-aux routing" and "# 3) Local expert compute") on random logits and stores what it selects."""
+    import torch
+    d = json.load(open(os.path.join(
+        REF, "evolution/benchmark/flashinfer_bench_evolve/tasks/moe/definition.json")))
+    src = d["reference"]
+    a = src.index("    # 2) No-aux routing")
+    b = src.index("    # 3) Local expert compute")
+    block = "\n".join(line[4:] if line.startswith("    ") else line for line in src[a:b].splitlines())
+    torch.manual_seed(9)
+    T, E = 96, 256
+    ns = dict(torch=torch, routing_logits=torch.randn(T, E) * 2.0,
+              routing_bias=(torch.randn(E) * 0.1).bfloat16(), T=T, E_global=E, N_GROUP=8, TOPK_GROUP=4, TOP_K=8,
+              routed_scaling_factor=2.5)
+    exec(compile(block, "moe/definition.json:routing", "exec"), ns)
+    idx = torch.sort(ns["topk_idx"], dim=1).values.int().numpy()
+    np.savez_compressed(os.path.join(OUT, "moe_routing.npz"), logits=ns["routing_logits"].numpy(),
+                        bias=ns["routing_bias"].float().numpy(), topk_idx_sorted=idx,
+                        weights_dense=ns["weights"].numpy(), rsf=np.float32(2.5))
+
+
 if __name__ == "__main__":
     ref = _load_gemm_helpers()
+    moe_routing()
     cvt_goldens()
     codec_and_gemm(ref)
     alphamoe_oracle()

@@ -252,3 +252,48 @@ def test_layer_fused_activation_matches_oracle(ops):
     got, ref = dev["output"].float().cpu().numpy(), orc.bf16_to_f32(full["out"])
     assert np.isfinite(got).all()
     assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean())
+
+
+def test_deepseek_routing_ids_exact(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "moe_routing.npz"))
+    logits = torch.from_numpy(g["logits"]).cuda()
+    bias = torch.from_numpy(g["bias"]).bfloat16().cuda()
+    ids, w = ops.route_deepseek(logits, bias, routed_scaling_factor=float(g["rsf"]))
+    assert ops.status() == 0
+    rid, rw = orc.route_deepseek(g["logits"], g["bias"], routed_scaling_factor=float(g["rsf"]))
+    np.testing.assert_array_equal(ids.cpu().numpy(), rid)
+    np.testing.assert_allclose(npf(w), rw, rtol=2e-6)
+    np.testing.assert_array_equal(np.sort(ids.cpu().numpy(), 1), g["topk_idx_sorted"])      # the reference's own picks
+    # ties everywhere: lowest groups, then lowest experts
+    z = torch.zeros((3, 256), device="cuda")
+    ids0, w0 = ops.route_deepseek(z, torch.zeros(256, dtype=torch.bfloat16, device="cuda"))
+    np.testing.assert_array_equal(ids0.cpu().numpy()[0], [0, 1, 2, 3, 4, 5, 6, 7])
+    np.testing.assert_allclose(npf(w0), 0.125, rtol=1e-6)
+
+
+def test_layer_with_registered_moe_task_keys(ops):
+    """The `moe` task's data dict (DeepSeek routing, MN-major input scales, local_expert_offset): only the local
+    experts' contributions are summed, as in tasks/moe/definition.json."""
+    from tirx_harness_b200 import moe_layer
+    T, H, I, E_loc, E_glob, top_k = 200, 256, 128, 32, 256, 8
+    dev, host = _make_layer(T, H, I, E_loc, top_k, seed=33)
+    gen = torch.Generator().manual_seed(7)
+    logits = torch.randn((T, E_glob), generator=gen) * 2
+    bias = (torch.randn(E_glob, generator=gen) * 0.1).bfloat16()
+    off, rsf = 64, 2.5
+    data = dict(dev, routing_logits=logits.cuda(), routing_bias=bias.cuda(), local_expert_offset=off,
+                routed_scaling_factor=rsf, hidden_states_scale=dev["hidden_states_scale"].t().contiguous())
+    data["output"].fill_(float("nan"))
+    layer = moe_layer.setup(data, T)
+    layer()
+    assert ops.status() == 0
+    rid, rw = orc.route_deepseek(logits.numpy(), bias.float().numpy(), routed_scaling_factor=rsf)
+    v = layer.view()
+    np.testing.assert_array_equal(v["ids"].cpu().numpy(), rid)
+    full = orc.moe_layer(u8(host["hidden_states"]), host["hidden_states_scale"].numpy(), None, u8(host["gemm1_weights"]),
+                         host["gemm1_weights_scale"].numpy(), u8(host["gemm2_weights"]),
+                         host["gemm2_weights_scale"].numpy(), top_k=top_k, e_lo=off, routes=(rid, rw))
+    np.testing.assert_array_equal(v["counts"].cpu().numpy(), full["plan"]["counts"])
+    got, ref = data["output"].float().cpu().numpy(), orc.bf16_to_f32(full["out"])
+    assert np.isfinite(got).all()
+    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean())

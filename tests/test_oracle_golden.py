@@ -205,3 +205,12 @@ def test_route_softmax_topk_ties_and_weights():
     np.testing.assert_allclose(w.sum(1), 1.0, rtol=1e-6)
     p = np.exp(logits[1] - logits[1].max())
     np.testing.assert_allclose(w[1], p[ids[1]] / p[ids[1]].sum(), rtol=1e-6)
+
+
+def test_deepseek_routing_matches_reference_routing_block(golden_dir):
+    g = _g(golden_dir, "moe_routing.npz")
+    ids, w = orc.route_deepseek(g["logits"], g["bias"], routed_scaling_factor=float(g["rsf"]))
+    np.testing.assert_array_equal(np.sort(ids, 1), g["topk_idx_sorted"])
+    dense = np.zeros_like(g["weights_dense"])
+    np.put_along_axis(dense, ids.astype(np.int64), w, 1)
+    np.testing.assert_allclose(dense, g["weights_dense"], rtol=2e-6, atol=1e-7)

@@ -37,7 +37,8 @@ class LayerArgs(_c.Structure):
         ("out", _c.c_void_p), ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
         ("T", _c.c_int32), ("H", _c.c_int32), ("I", _c.c_int32), ("E", _c.c_int32), ("E_global", _c.c_int32),
         ("e_lo", _c.c_int32), ("top_k", _c.c_int32), ("align", _c.c_int32), ("gate_first", _c.c_int32),
-        ("fuse_act", _c.c_int32),
+        ("fuse_act", _c.c_int32), ("routing_bias", _c.c_void_p), ("n_group", _c.c_int32), ("topk_group", _c.c_int32),
+        ("routed_scaling_factor", _c.c_float),
     ]
 
 
@@ -82,7 +83,7 @@ def lib():
 # every symbol include/b200moe.h declares
 EXPORTS = (
     "moe_gg_fp8_contiguous", "moe_gg_fp8_masked", "moe_gg_fp8_gate_up_act", "moe_gg_workspace_bytes", "moe_quant_1x128", "moe_silu_mul_requant",
-    "moe_route_topk", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute_plan_static", "moe_permute",
+    "moe_route_topk", "moe_route_deepseek", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute_plan_static", "moe_permute",
     "moe_combine",
     "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
     "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",

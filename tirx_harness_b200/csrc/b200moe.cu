@@ -474,6 +474,23 @@ int moe_route_topk(const float* logits, int32_t* ids, float* weights, int32_t T,
     return MOE_OK;
 }
 
+int moe_route_deepseek(const float* logits, const void* bias, int32_t bias_dtype, int32_t* ids, float* weights, int32_t T,
+                       int32_t E, int32_t n_group, int32_t topk_group, int32_t top_k, float routed_scaling_factor,
+                       void* stream) {
+    if (!logits || !bias || !ids || !weights) return fail(MOE_ERR_INVALID, "logits, bias, ids and weights must be non-NULL");
+    if (n_group <= 0 || n_group > DS_MAX_GROUPS || E != 32 * n_group)
+        return fail(MOE_ERR_UNSUPPORTED, "E=%d must be 32 * n_group with n_group in [1, %d]", E, DS_MAX_GROUPS);
+    if (topk_group <= 0 || topk_group > n_group) return fail(MOE_ERR_INVALID, "topk_group must be in [1, n_group]");
+    if (top_k <= 0 || top_k > 32 || top_k > 32 * topk_group) return fail(MOE_ERR_INVALID, "top_k out of range");
+    if (bias_dtype != MOE_DTYPE_BF16 && bias_dtype != MOE_DTYPE_F32) return fail(MOE_ERR_INVALID, "bias_dtype must be bf16 or f32");
+    if (T <= 0) return T == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "T must be non-negative");
+    const int wpb = 8;
+    route_deepseek_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, bias, bias_dtype == MOE_DTYPE_BF16, ids, weights, T, n_group, topk_group, top_k, routed_scaling_factor);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
 size_t moe_permute_workspace_bytes(int64_t n_pairs, int32_t E_local) {
     const int64_t n_chunks = (n_pairs + PLAN_CHUNK - 1) / PLAN_CHUNK;
     return align256((size_t)(n_chunks > 0 ? n_chunks : 1) * (size_t)E_local * 4);
@@ -559,7 +576,13 @@ int moe_layer_forward(const moe_layer_args* L, void* stream) {
     const int32_t* ids = L->topk_ids;
     const float* wts = L->topk_weights;
     if (L->logits) {
-        rc = moe_route_topk(L->logits, w.ids, w.weights, L->T, L->E_global > 0 ? L->E_global : L->E, L->top_k, stream);
+        const int32_t e_glob = L->E_global > 0 ? L->E_global : L->E;
+        if (L->routing_bias != nullptr)      // DeepSeek-V3 no-aux routing of the registered `moe` workload
+            rc = moe_route_deepseek(L->logits, L->routing_bias, MOE_DTYPE_BF16, w.ids, w.weights, L->T, e_glob,
+                                    L->n_group > 0 ? L->n_group : 8, L->topk_group > 0 ? L->topk_group : 4, L->top_k,
+                                    L->routed_scaling_factor, stream);
+        else
+            rc = moe_route_topk(L->logits, w.ids, w.weights, L->T, e_glob, L->top_k, stream);
         if (rc != MOE_OK) return rc;
         ids = w.ids;
         wts = w.weights;

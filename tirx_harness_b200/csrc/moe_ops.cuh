@@ -160,6 +160,84 @@ __global__ void route_softmax_topk_kernel(const float* __restrict__ logits, int*
     }
 }
 
+// DeepSeek-V3 "no-aux" routing: s = sigmoid(logit), swb = s + bias; n_group groups of 32 experts (lane l of
+// the warp holds expert g*32 + l of every group g); group score = sum of its two largest swb; the
+// topk_group best groups are kept; among their experts the top_k largest swb win; weight =
+// s / (sum of selected s + 1e-20) * rsf.  Ties -> lowest index.  One warp per token, n_group <= 16.
+constexpr int DS_MAX_GROUPS = 16;
+__device__ __forceinline__ float warp_max_f(float v) { return warp_max(v); }
+__global__ void route_deepseek_kernel(const float* __restrict__ logits, const void* __restrict__ bias, int bias_is_bf16,
+                                      int* __restrict__ ids, float* __restrict__ weights, int T, int n_group,
+                                      int topk_group, int top_k, float rsf) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const int E = n_group * 32;
+    float s[DS_MAX_GROUPS], swb[DS_MAX_GROUPS], gscore[DS_MAX_GROUPS];
+#pragma unroll
+    for (int g = 0; g < DS_MAX_GROUPS; ++g) {
+        if (g < n_group) {
+            const int e = g * 32 + lane;
+            const float b = bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[e])
+                                         : reinterpret_cast<const float*>(bias)[e];
+            s[g] = __fdiv_rn(1.0f, 1.0f + expf(-__ldg(logits + (long long)t * E + e)));
+            swb[g] = s[g] + b;
+            // two largest of the group: the maximum, then the maximum with its first holder removed
+            const float m1 = warp_max(swb[g]);
+            const unsigned holders = __ballot_sync(0xffffffffu, swb[g] == m1);
+            const int first = __ffs(holders) - 1;
+            const float m2 = warp_max(lane == first ? -INFINITY : swb[g]);
+            gscore[g] = m1 + m2;
+        } else {
+            s[g] = 0.0f; swb[g] = -INFINITY; gscore[g] = -INFINITY;
+        }
+    }
+    unsigned keep = 0;
+    for (int k = 0; k < topk_group; ++k) {
+        int best = -1;
+        float bv = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < DS_MAX_GROUPS; ++g)
+            if (g < n_group && !((keep >> g) & 1u) && (best < 0 || gscore[g] > bv)) { best = g; bv = gscore[g]; }
+        keep |= 1u << best;
+    }
+    unsigned taken = 0;
+    float my_s = 0.0f, sum = 0.0f;
+    int my_id = 0;
+    for (int k = 0; k < top_k; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7FFFFFFF;
+#pragma unroll
+        for (int g = 0; g < DS_MAX_GROUPS; ++g) {
+            if (g < n_group && ((keep >> g) & 1u) && !((taken >> g) & 1u) && (best_e == 0x7FFFFFFF || swb[g] > best)) {
+                best = swb[g];
+                best_e = g * 32 + lane;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe != 0x7FFFFFFF && (best_e == 0x7FFFFFFF || ob > best || (ob == best && oe < best_e))) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        const int bg = best_e >> 5;
+        float sel_s = 0.0f;
+#pragma unroll
+        for (int g = 0; g < DS_MAX_GROUPS; ++g) if (g == bg) sel_s = s[g];
+        sel_s = __shfl_sync(0xffffffffu, sel_s, best_e & 31);
+        if ((best_e & 31) == lane) taken |= 1u << bg;
+        sum += sel_s;
+        if (lane == k) { my_s = sel_s; my_id = best_e; }
+    }
+    if (lane < top_k) {
+        ids[(long long)t * top_k + lane] = my_id;
+        weights[(long long)t * top_k + lane] = __fdiv_rn(my_s, sum + 1e-20f) * rsf;
+    }
+}
+
 // ------------------------------------------------------------------ permutation plan
 // Pairs p = t*top_k + j are processed in chunks of 1024 (one block each, 32 warps in pair order).
 // Step 1 (count):  chunk_counts[chunk][e] = pairs of the chunk routed to local expert e.

@@ -34,6 +34,12 @@ class MoeLayer:
         out = data["output"]
         logits = data.get("routing_logits")
         ids, wts = data.get("topk_ids"), data.get("topk_weights")
+        bias = data.get("routing_bias")               # present in the registered `moe` task: DeepSeek-V3 routing
+        if bias is not None:
+            if bias.dtype != torch.bfloat16 or not bias.is_contiguous():
+                raise TypeError("routing_bias must be contiguous bfloat16")
+            e_lo = int(data.get("local_expert_offset", e_lo))
+        rsf = float(data.get("routed_scaling_factor", 1.0))
         H = x_q.shape[1]
         E, two_i, _ = w13.shape
         inter = two_i // 2
@@ -55,14 +61,15 @@ class MoeLayer:
         self.ws_bytes = L.moe_workspace_bytes(T, H, inter, E, top_k, align)
         self.workspace = torch.empty(self.ws_bytes, dtype=torch.uint8, device=self.device)
         e_global = logits.shape[1] if logits is not None else E
-        self._keep = (x_q, xs, logits, ids, wts, w13, s13, w2, s2, out)
+        self._keep = (x_q, xs, logits, ids, wts, w13, s13, w2, s2, out, bias)
         self.dims = dict(T=T, H=H, I=inter, E=E, top_k=top_k, align=align)
         self.args = _lib.LayerArgs(
             x_q=_p(x_q), x_scale=_p(xs), xs_stride_row=xs.stride(0), xs_stride_blk=xs.stride(1),
             logits=_p(logits), topk_ids=_p(ids), topk_weights=_p(wts), w13=_p(w13), w13_scale=_p(s13.contiguous()),
             w2=_p(w2), w2_scale=_p(s2.contiguous()), out=_p(out), workspace=_p(self.workspace),
             workspace_bytes=self.ws_bytes, T=T, H=H, I=inter, E=E, E_global=e_global, e_lo=e_lo, top_k=top_k,
-            align=align, gate_first=1 if gate_first else 0, fuse_act=1 if fuse_act else 0)
+            align=align, gate_first=1 if gate_first else 0, fuse_act=1 if fuse_act else 0,
+            routing_bias=_p(bias), n_group=0, topk_group=0, routed_scaling_factor=rsf)
         self.out = out
 
     def __call__(self):
@@ -105,5 +112,7 @@ class MoeLayer:
 def setup(data: dict, T: int, **kw) -> MoeLayer:
     """``data``: hidden_states fp8 [T,H], hidden_states_scale f32 [T,H/128] or [H/128,T],
     routing_logits f32 [T,E] (or topk_ids/topk_weights), gemm1_weights fp8 [E,2I,H] (+_scale),
-    gemm2_weights fp8 [E,H,I] (+_scale), output bf16 [T,H]."""
+    gemm2_weights fp8 [E,H,I] (+_scale), output bf16 [T,H].  With the registered `moe` task's extra keys
+    (routing_bias bf16 [E_global], local_expert_offset, routed_scaling_factor) the layer uses that task's
+    DeepSeek-V3 routing and computes only the local experts' contributions."""
     return MoeLayer(data, T, **kw)

@@ -62,6 +62,22 @@ def route_topk(logits: torch.Tensor, top_k: int):
     return ids, w
 
 
+def route_deepseek(logits: torch.Tensor, bias: torch.Tensor, top_k: int = 8, n_group: int = 8, topk_group: int = 4,
+                   routed_scaling_factor: float = 1.0):
+    """DeepSeek-V3 no-aux routing: f32 [T, E], bias bf16/f32 [E] -> (ids int32 [T, top_k], weights f32 [T, top_k])."""
+    assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
+    assert bias.dtype in (torch.bfloat16, torch.float32) and bias.is_contiguous()
+    T, E = logits.shape
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.lib().moe_route_deepseek(_vp(logits.data_ptr()), _vp(bias.data_ptr()),
+                                                 _i32(0 if bias.dtype == torch.bfloat16 else 1), _vp(ids.data_ptr()),
+                                                 _vp(w.data_ptr()), _i32(T), _i32(E), _i32(n_group), _i32(topk_group),
+                                                 _i32(top_k), ctypes.c_float(routed_scaling_factor), _stream(logits)))
+    return ids, w
+
+
 def plan_cap_rows(n_pairs: int, e_local: int, align: int) -> int:
     return (n_pairs + align - 1) // align * align + e_local * align
 
