@@ -282,7 +282,7 @@ def run_layer(args, world, rank, device, barrier, steps, warmup):
     cfg = LAYER_SMALL if getattr(args, "layer_small", False) else LAYER
     data = _layer_case(world, rank, device, cfg)
     Tl = cfg["T"] // world
-    layer = ep_layer.setup(data, Tl, top_k=cfg["top_k"])
+    layer = ep_layer.setup(data, Tl, top_k=cfg["top_k"], combine=args.combine)
     for _ in range(max(warmup, 3)):
         layer()
     barrier()
@@ -336,7 +336,8 @@ def run_layer(args, world, rank, device, barrier, steps, warmup):
         "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": cfg["desc"], "tokens_per_rank": Tl, "experts_per_rank": cfg["E"] // world,
                    "routing": "softmax top-8, ties to lowest index, weights renormalised",
-                   "l2": "weights (1.4-11 GB per rank) larger than L2, no flush", "rows_this_rank": int(counts)},
+                   "l2": "weights (1.4-11 GB per rank) larger than L2, no flush", "rows_this_rank": int(counts),
+                   "combine": args.combine},
         "clocks": clocks.summary(),
         "e2e": {"value": cfg["T"] / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": hx.numel() + hs_.numel() * 4 + hl.numel() * 4, "d2h_bytes_per_step": ho.numel() * 2,
@@ -505,6 +506,8 @@ def main():
                     help="skip the expert-parallel MoE layer measurement that follows the grouped-GEMM one "
                          "(it is reported as the extra object `moe_layer` of the same JSON line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--combine", choices=["pull", "push"], default="push",
+                    help="layer workload: how expert outputs travel back (see ep_layer.EpMoeLayer)")
     ap.add_argument("--layer-small", action="store_true", help="layer workload at 2048 tokens / 32 experts (profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()

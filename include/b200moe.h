@@ -57,6 +57,8 @@ extern "C" {
  *           promotion -- same exact products, fp32 accumulation, about 1.5x faster.  Otherwise, and
  *           always without workspace, the promotion kernel runs.  The decision is taken per call on
  *           the device from the current scale values; nothing is cached between calls.
+ *   lda     row pitch of a in bytes; 0 = K (dense).  A larger pitch (multiple of 16) lets rows carry a
+ *           trailer, e.g. their own scales, as the expert-parallel receive buffer does.
  *   sf_format  MOE_SF_F32 (default, 0) or MOE_SF_UE8M0_PACKED: the scale format of the registered
  *           grouped_gemm/fp8 workload (evolution/tasks/grouped_gemm_fp8.yaml:16-19; packing as in
  *           tools/tests/numsim/corpus/kernels/gemm.py:252-263: byte j of a word = K block 4*word+j).
@@ -89,6 +91,7 @@ typedef struct moe_gg_args {
     void* scatter_base[8];
     int32_t sf_format;
     int64_t sfb_stride[3];
+    int64_t lda;
 } moe_gg_args;
 
 /* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With
@@ -245,8 +248,9 @@ int moe_ipc_open(const void* handle64, void** ptr);        /* map a peer's alloc
 int moe_ipc_close(void* ptr);
 
 /* Peer table: entry i = rank i's buffers as mapped in THIS process (own buffers at i == rank).
- *   a      e4m3 [cap_rows, H]       receive buffer in the contiguous grouped layout
- *   sa     f32  [H/128, cap_rows]   its row scales, MN-major
+ *   a      cap_rows records of `pitch` bytes in the contiguous grouped layout: H e4m3 bytes, then the row's
+ *          H/128 fp32 scales (pitch >= H + H/32, multiple of 16)
+ *   sa     = a + H: scales of (row r, block b) at sa[r*pitch/4 + b]
  *   y      bf16 [cap_rows, H]       down-GEMM output rows
  *   counts int32 [world, E_total]   row s = number of pairs rank s routes to each expert
  *   flags  int32 [world]            barrier epochs
@@ -284,7 +288,7 @@ int moe_ep_plan(const moe_ep_peers* peers, const int32_t* ids, int64_t n_pairs, 
  * into the owner rank's grouped-layout buffers, together with the row's return address (meta). */
 int moe_ep_dispatch(const moe_ep_peers* peers, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
                     const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
-                    int32_t cap_rows, int32_t rank, int32_t world, void* stream);
+                    int32_t cap_rows, int64_t pitch, int32_t rank, int32_t world, void* stream);
 
 /* Combine all-to-all fused with the weighted sum: each token loads its top_k expert rows from the owners'
  * y buffers and accumulates w * row in fp32 (slot order), writing bf16. */

@@ -29,7 +29,7 @@ def build_global(T, H, I, E, seed):
                 gemm2_weights_scale=s2 * 0.05)
 
 
-def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="pull"):
+def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="push"):
     import torch.distributed as dist
     from tirx_harness_b200 import ep_layer, grouped_gemm, moe_layer
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -85,4 +85,4 @@ def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="pull"):
 
 
 if __name__ == "__main__":
-    run(combine=os.environ.get("EP_COMBINE", "pull"))
+    run(combine=os.environ.get("EP_COMBINE", "push"))

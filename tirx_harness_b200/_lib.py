@@ -24,7 +24,7 @@ class GGArgs(_c.Structure):
         ("d_dtype", _c.c_int32), ("rows_used", _c.c_void_p),
         ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
         ("scatter_meta", _c.c_void_p), ("scatter_base", _c.c_void_p * 8),
-        ("sf_format", _c.c_int32), ("sfb_stride", _c.c_int64 * 3),
+        ("sf_format", _c.c_int32), ("sfb_stride", _c.c_int64 * 3), ("lda", _c.c_int64),
     ]
 
 

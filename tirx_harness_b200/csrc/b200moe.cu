@@ -58,11 +58,12 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 }
 
 // 2-D K-major e4m3 matrix [rows, K]; box = box_rows x 128 bytes, SWIZZLE_128B, OOB reads give 0.
-int encode_fp8_kmajor(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+int encode_fp8_kmajor(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows,
+                      uint64_t pitch = 0) {
     auto fn = get_encode_fn();
     if (!fn) return fail(MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {K, rows};
-    cuuint64_t strides[1] = {K};
+    cuuint64_t strides[1] = {pitch ? pitch : K};
     cuuint32_t box[2] = {128, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -130,6 +131,8 @@ int device_info(DeviceInfo** out) {
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg::SMEM_BYTES_SCATTER));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg2::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -213,7 +216,8 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     const bool use_pair_kernel = env_kernel && strcmp(env_kernel, "2cta") == 0;
     const bool allow_mx = !(env_mx && strcmp(env_mx, "0") == 0);
     CUtensorMap tmap_a, tmap_b;
-    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::BM);
+    if (a->lda != 0 && (a->lda < a->K || a->lda % 16)) return fail(MOE_ERR_INVALID, "lda must be 0 or >= K and a multiple of 16");
+    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
     if (rc != MOE_OK) return rc;
     rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, use_pair_kernel ? gg2::BN / 2 : gg::BN);
     if (rc != MOE_OK) return rc;
@@ -298,6 +302,15 @@ int launch_gg(const moe_gg_args* a, void* stream) {
                                  : (long long)p.num_m_blocks * p.num_n_blocks;
     int grid = (int)(max_tiles < di->num_sms ? max_tiles : di->num_sms);
     if (grid < 1) grid = 1;
+    if constexpr (!MASKED) {
+        if (p.scatter_meta != nullptr) {
+            if (a->N % 128 != 0) return fail(MOE_ERR_INVALID, "scattered output needs N %% 128 == 0");
+            gg_fp8_kernel<false, false, true><<<grid, gg::THREADS, gg::SMEM_BYTES_SCATTER, static_cast<cudaStream_t>(stream)>>>(
+                tmap_a, tmap_b, p, status_ptr());
+            CUDA_TRY(cudaGetLastError());
+            return MOE_OK;
+        }
+    }
     gg_fp8_kernel<MASKED><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
         tmap_a, tmap_b, p, status_ptr());
     CUDA_TRY(cudaGetLastError());
@@ -375,7 +388,8 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     int rc = device_info(&di);
     if (rc != MOE_OK) return rc;
     CUtensorMap tmap_a, tmap_b;
-    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)a->M, (uint64_t)a->K, gg::BM);
+    if (a->lda != 0 && (a->lda < a->K || a->lda % 16)) return fail(MOE_ERR_INVALID, "lda must be 0 or >= K and a multiple of 16");
+    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)a->M, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
     if (rc != MOE_OK) return rc;
     rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, 64);
     if (rc != MOE_OK) return rc;
@@ -750,16 +764,32 @@ int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int3
 
 int moe_ep_dispatch(const moe_ep_peers* P, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
                     const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
-                    int32_t cap_rows, int32_t rank, int32_t world, void* stream) {
+                    int32_t cap_rows, int64_t pitch, int32_t rank, int32_t world, void* stream) {
     int rc = ep_check(P, rank, world);
     if (rc != MOE_OK) return rc;
     if (!x_q || !x_scale || !ids || !pos) return fail(MOE_ERR_INVALID, "dispatch pointers must be non-NULL");
-    if (H <= 0 || H % 128 || top_k <= 0 || E_local <= 0) return fail(MOE_ERR_INVALID, "H must be a multiple of 128; top_k, E_local positive");
+    if (H <= 0 || H % 128 || top_k <= 0 || E_local <= 0)
+        return fail(MOE_ERR_INVALID, "H must be a positive multiple of 128; top_k, E_local positive");
     if (n_pairs <= 0) return n_pairs == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "n_pairs must be non-negative");
-    const int wpb = 8;
-    ep_dispatch_kernel<<<(unsigned)((n_pairs + wpb - 1) / wpb), wpb * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+    if (n_pairs % top_k) return fail(MOE_ERR_INVALID, "n_pairs must be a multiple of top_k");
+    if (top_k > 32) return fail(MOE_ERR_INVALID, "top_k must be at most 32");
+    const long long rec = ((long long)H + H / 32 + 15) & ~15ll;
+    if (pitch < rec || pitch % 16) return fail(MOE_ERR_INVALID, "pitch must be >= H + H/32 (rounded up to 16) and a multiple of 16");
+    if ((reinterpret_cast<uintptr_t>(x_q) & 15)) return fail(MOE_ERR_INVALID, "x_q must be 16-byte aligned");
+    const long long tokens = n_pairs / top_k;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    const size_t smem = (size_t)DISPATCH_WARPS * rec;
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        CUDA_TRY(cudaFuncSetAttribute(ep_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        attr_done[dev] = true;
+    }
+    if (smem > 64 * 1024) return fail(MOE_ERR_INVALID, "H too large for the dispatch staging buffer");
+    ep_dispatch_kernel<<<(unsigned)((tokens + DISPATCH_WARPS - 1) / DISPATCH_WARPS), DISPATCH_WARPS * 32, smem,
+                         static_cast<cudaStream_t>(stream)>>>(
         ep_convert(P), static_cast<const uint8_t*>(x_q), x_scale, xs_row, xs_blk, ids, pos, n_pairs, top_k, E_local, H,
-        cap_rows, rank);
+        cap_rows, rank, pitch, status_ptr());
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }

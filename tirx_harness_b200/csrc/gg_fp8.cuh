@@ -44,6 +44,9 @@ constexpr int A_STAGE_BYTES = BM * BK;             // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK;             // 32 KB
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_MASKED_GROUPS = 1024;
+constexpr int SCATTER_STAGES = 3;                  // scattered-output variant: one stage fewer ...
+constexpr int STAGING_ROW_BYTES = 528;             // ... and 128 staging rows of 512 B + 16 B pad (bank-conflict free)
+constexpr int STAGING_BYTES = 128 * STAGING_ROW_BYTES;
 constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int SF_SLOTS = 8;                        // scale ring: per slot 128 row scales + 2 block scales
 constexpr int SF_SLOT_FLOATS = 132;
@@ -53,6 +56,7 @@ constexpr int OFF_AMAX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;     // fused ac
 constexpr int OFF_PREFIX = OFF_AMAX + 2 * 2 * 128 * 4;
 // + masked-layout prefix table + slack for 1024-byte alignment
 constexpr int SMEM_BYTES = OFF_PREFIX + (MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
+constexpr int SMEM_BYTES_SCATTER = SMEM_BYTES - (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES;
 }  // namespace gg
 
 struct GGParams {
@@ -183,40 +187,49 @@ struct Scheduler {
     }
 };
 
-template <bool MASKED, bool FUSE_ACT = false>
+template <bool MASKED, bool FUSE_ACT = false, bool SCATTER = false>
 __global__ void __launch_bounds__(gg::THREADS, 1)
 gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const GGParams p, int* status) {
     static_assert(!(MASKED && FUSE_ACT), "the fused activation epilogue exists for the contiguous layout only");
+    static_assert(!(SCATTER && (MASKED || FUSE_ACT)), "scattered output exists for the plain contiguous GEMM only");
     using namespace gg;
+    // SCATTER trades one pipeline stage for a 128 x 528-byte staging area from which finished rows leave
+    // as 256-byte bulk stores (possibly to another GPU) without holding up the promotion warps.
+    constexpr int NSTAGES = SCATTER ? gg::SCATTER_STAGES : gg::STAGES;
+    constexpr int TILES_END = NSTAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+    constexpr int BARS_AT = TILES_END + (SCATTER ? gg::STAGING_BYTES : 0);
+    constexpr int SF_AT = BARS_AT + 512;
+    constexpr int AMAX_AT = SF_AT + SF_SLOTS * SF_SLOT_FLOATS * 4;
+    constexpr int PREFIX_AT = AMAX_AT + 2 * 2 * 128 * 4;
     if (p.mode_flag != nullptr && *p.mode_flag == 0) return;   // the power-of-two-scale path took this call
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms the MMA descriptors address
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
+    uint8_t* smem_b = smem + NSTAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS_AT);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty,
     // then SF_SLOTS scale-full and SF_SLOTS scale-empty barriers
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1);
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-    float* sf_ring = reinterpret_cast<float*>(smem + OFF_SF);
-    int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
+    float* sf_ring = reinterpret_cast<float*>(smem + SF_AT);
+    int* prefix = reinterpret_cast<int*>(smem + PREFIX_AT);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     const uint32_t full_bar = smem_u32(bars);
-    const uint32_t empty_bar = smem_u32(bars + STAGES);
-    const uint32_t tfull_bar = smem_u32(bars + 2 * STAGES);
-    const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + ACC_STAGES);
-    const uint32_t sffull_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES);
-    const uint32_t sfempty_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES + SF_SLOTS);
-    const uint32_t amax_bar = smem_u32(bars + 2 * STAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
-    float* amax_x = reinterpret_cast<float*>(smem + OFF_AMAX);
+    const uint32_t empty_bar = smem_u32(bars + NSTAGES);
+    const uint32_t tfull_bar = smem_u32(bars + 2 * NSTAGES);
+    const uint32_t tempty_bar = smem_u32(bars + 2 * NSTAGES + ACC_STAGES);
+    const uint32_t sffull_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES);
+    const uint32_t sfempty_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES + SF_SLOTS);
+    const uint32_t amax_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
+    float* amax_x = reinterpret_cast<float*>(smem + AMAX_AT);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NSTAGES; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
@@ -304,13 +317,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     __syncwarp();
                     issued |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
                 }
             }
             // Unwinding after a failed wait: give every copy this warp issued a bounded chance to
             // land before the CTA exits (on the normal path the MMA warp has consumed them all).
             if (!ok && lane == 0) {
-                for (int s = 0; s < STAGES; ++s) {
+                for (int s = 0; s < NSTAGES; ++s) {
                     if (!((issued >> s) & 1u)) continue;
                     const uint32_t par = (issued_parity >> s) & 1u;
                     for (int it = 0; it < (1 << 20); ++it)
@@ -346,7 +359,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         umma_commit(tfull_bar + 8 * acc);     // accumulator of this K block complete
                     }
                     __syncwarp();
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
                     if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                 }
             }
@@ -512,6 +525,27 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         *reinterpret_cast<float4*>(drow + j) = o;
                     }
                 }
+            } else if (SCATTER) {
+                // this thread's 128 columns -> its own 256-byte slice of the staging row -> one bulk store
+                uint8_t* stg = smem + TILES_END + row_in_tile * gg::STAGING_ROW_BYTES + half * 256;
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // previous tile's store has read it
+#pragma unroll
+                for (int j = 0; j < 128; j += 8) {
+                    uint4 out;
+                    out.x = cvt_bf16x2(accr[j / 2 + 0]);
+                    out.y = cvt_bf16x2(accr[j / 2 + 1]);
+                    out.z = cvt_bf16x2(accr[j / 2 + 2]);
+                    out.w = cvt_bf16x2(accr[j / 2 + 3]);
+                    *reinterpret_cast<uint4*>(stg + j * 2) = out;
+                }
+                fence_proxy_async_smem();
+                if (row_valid) {
+                    const int meta = __ldg(p.scatter_meta + row);
+                    __nv_bfloat16* drow = p.scatter_base[(meta >> 24) & 7] + (long long)(meta & 0xFFFFFF) * p.ldd + n0;
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;"
+                                 ::"l"(drow), "r"(smem_u32(stg)) : "memory");
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             } else if (row_valid) {
                 __nv_bfloat16* drow;
                 if (p.scatter_meta != nullptr) {
@@ -536,6 +570,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
 
     // ---------------------------------------------------------- teardown
+    if (SCATTER) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this thread's bulk stores are complete
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {

@@ -424,8 +424,9 @@ namespace b200 {
 constexpr int EP_MAX_WORLD = 8;
 
 struct EpPeers {
-    uint8_t* a[EP_MAX_WORLD];            // e4m3 [cap_rows, H] receive buffer of each rank
-    float* sa[EP_MAX_WORLD];             // f32 [H/128, cap_rows] (MN-major) scales of each rank
+    uint8_t* a[EP_MAX_WORLD];            // receive buffer of each rank: cap_rows records of `pitch` bytes,
+                                         // each = H e4m3 bytes followed by H/128 fp32 scales
+    float* sa[EP_MAX_WORLD];             // = a + H: the scales of row r at sa + r*pitch/4
     const __nv_bfloat16* y[EP_MAX_WORLD];// bf16 [cap_rows, H] expert outputs of each rank
     int* counts[EP_MAX_WORLD];           // int32 [world, E_total]: row s = pairs rank s routes to each expert
     int* flags[EP_MAX_WORLD];            // int32 [world]: barrier epochs written by each peer
@@ -527,25 +528,61 @@ __global__ void ep_layout_kernel(const int* __restrict__ offsets, const int* __r
 }
 
 // Dispatch: pair p = t*top_k + j goes to row pos[p] of the rank that owns expert ids[p].
-// One warp per pair: H bytes of e4m3 + H/128 scales stored into the owner's buffers.
+// Receive rows are `pitch` bytes apart and hold the H e4m3 bytes followed by the H/128 fp32 scales, so one
+// token -> one contiguous record.  One warp per token: the record is assembled once in shared memory (bulk
+// load of the e4m3 row + the scales) and leaves as ONE bulk store of H + H/32 bytes per destination, issued
+// by lane j for destination j.  NVLink then carries large packets instead of 16-byte stores.
+constexpr int DISPATCH_WARPS = 4;
 __global__ void ep_dispatch_kernel(EpPeers peers, const uint8_t* __restrict__ x, const float* __restrict__ xs,
                                    long long xs_r, long long xs_b, const int* __restrict__ ids,
                                    const int* __restrict__ pos, long long n_pairs, int top_k, int E_local,
-                                   int H, int cap_rows, int rank) {
-    const long long p = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (p >= n_pairs) return;
-    const int row = __ldg(pos + p);
-    if (row < 0 || row >= cap_rows) return;
-    const int d = __ldg(ids + p) / E_local;
-    const long long t = p / top_k;
-    const uint4* src = reinterpret_cast<const uint4*>(x + t * H);
-    uint4* dst = reinterpret_cast<uint4*>(peers.a[d] + (long long)row * H);
-    for (int i = lane; i < (H >> 4); i += 32) dst[i] = __ldg(src + i);
-    float* sdst = peers.sa[d];
-    for (int b = lane; b < (H >> 7); b += 32) sdst[(long long)b * cap_rows + row] = __ldg(xs + t * xs_r + b * xs_b);
-    // where this row's result has to go back to: lets the owner's down GEMM store it straight into our slot
-    if (lane == 0) peers.meta[d][row] = (rank << 24) | (int)p;
+                                   int H, int cap_rows, int rank, long long pitch, int* status) {
+    extern __shared__ __align__(128) uint8_t dsm[];
+    __shared__ uint64_t bars[DISPATCH_WARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * DISPATCH_WARPS + warp;
+    const int rec = (H + (H >> 5) + 15) & ~15;         // record bytes: row + scales, rounded up to 16
+    uint8_t* buf = dsm + (long long)warp * rec;
+    const uint32_t bar = smem_u32(&bars[warp]);
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    if (t * top_k >= n_pairs) return;
+    if (lane == 0) {
+        mbar_arrive_expect_tx(bar, (uint32_t)H);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_u32(buf)), "l"(x + t * H), "r"(H), "r"(bar) : "memory");
+    }
+    float* sbuf = reinterpret_cast<float*>(buf + H);
+    for (int b = lane; b < (H >> 7); b += 32) sbuf[b] = __ldg(xs + t * xs_r + (long long)b * xs_b);
+    // bounded wait for the row (2 s), then make the generic-proxy scale writes visible to the bulk engine
+    {
+        bool ok = mbar_try_wait(bar, 0);
+        const uint64_t t0 = globaltimer_ns();
+        while (!ok) {
+            ok = mbar_try_wait(bar, 0);
+            if (!ok && globaltimer_ns() - t0 > kWaitLimitNs) { atomicOr(status, STATUS_TIMEOUT_SMEM_FULL); break; }
+        }
+        if (!__all_sync(0xffffffffu, ok)) return;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane < top_k) {
+        const long long p = t * top_k + lane;
+        const int row = __ldg(pos + p);
+        if (row >= 0 && row < cap_rows) {
+            const int d = __ldg(ids + p) / E_local;
+            uint8_t* dst = peers.a[d] + (long long)row * pitch;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(dst), "r"(smem_u32(buf)), "r"(rec) : "memory");
+            // where this row's result has to go back to: lets the owner's down GEMM send it straight to our slot
+            peers.meta[d][row] = (rank << 24) | (int)p;
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
 }
 
 // Combine: out[t,:] = bf16( sum_j w[t,j] * Y_owner(ids[t,j])[pos[t,j], :] ), rows fetched from the

@@ -6,11 +6,11 @@
 Rank r owns experts [r*E_local, (r+1)*E_local) with their weights resident and T_local tokens.
 Per forward: route -> publish per-expert counts to all peers -> barrier -> plan -> dispatch (rows are
 stored straight into the owner's grouped-layout buffer over NVLink, with their return address) -> barrier
--> gate_up grouped GEMM -> SiLU*mul requant -> down grouped GEMM -> barrier -> combine (each token loads
-its expert rows from the owners' buffers with 16-byte peer loads and forms the weighted sum).
-``combine="push"`` instead lets the down GEMM's epilogue store every output row directly into the slot of
-the rank that owns the token, followed by a local weighted sum; it is correct but slower at present
-(its 16-byte scattered stores use NVLink poorly: measured 3.6 ms vs 1.6 ms for the down GEMM on 2 GPUs).  The reference emulates this sharding on one GPU
+-> gate_up grouped GEMM -> SiLU*mul requant -> down grouped GEMM whose epilogue sends every finished
+output row straight to the slot of the rank that owns the token (256-byte bulk stores from a shared-memory
+staging area, so the combine all-to-all rides on the GEMM and costs it nothing measurable) -> barrier ->
+local weighted sum.  ``combine="pull"`` keeps the expert outputs local instead and lets the combine kernel
+load them from the owners with 16-byte peer loads (2 GPUs: 0.78 ms for that stage against 0.23 ms).  The reference emulates this sharding on one GPU
 with ``local_expert_offset`` (mlc-ai/TIRx-harness: evolution/benchmark/flashinfer_bench_evolve/tasks/
 moe/definition.json); with world size 1 this class computes exactly what ``moe_layer.MoeLayer`` does.
 
@@ -74,7 +74,7 @@ class SymmetricBuffer:
 
 class EpMoeLayer:
     def __init__(self, data: dict, T_local: int, top_k: int = 8, align: int = 128, gate_first: bool = False,
-                 group=None, fuse_act: bool = False, combine: str = "pull"):
+                 group=None, fuse_act: bool = False, combine: str = "push"):
         import torch.distributed as dist
         self.L = _lib.lib()
         x_q, xs = data["hidden_states"], data["hidden_states_scale"]
@@ -111,7 +111,9 @@ class EpMoeLayer:
         # ---- symmetric region: a | sa | y (pull: [cap,H] expert outputs; push: [T_local*top_k,H] return slots)
         #      | counts | flags | meta
         y_rows = cap if combine == "pull" else n_pairs
-        sizes = [cap * H, (H // 128) * cap * 4, y_rows * H * 2, self.world * E_total * 4, 256, cap * 4]
+        pitch = (H + (H // 128) * 4 + 15) // 16 * 16     # one record per row: e4m3 bytes, then its fp32 scales
+        self.pitch = pitch
+        sizes = [cap * pitch, 0, y_rows * H * 2, self.world * E_total * 4, 256, cap * 4]
         offs, o = [], 0
         for s in sizes:
             offs.append(o)
@@ -121,10 +123,10 @@ class EpMoeLayer:
         self.peers = _lib.EpPeers()
         for r in range(self.world):
             base = self.symm.ptrs[r]
-            self.peers.a[r], self.peers.sa[r], self.peers.y[r] = base + offs[0], base + offs[1], base + offs[2]
+            self.peers.a[r], self.peers.sa[r], self.peers.y[r] = base + offs[0], base + offs[0] + H, base + offs[2]
             self.peers.counts[r], self.peers.flags[r] = base + offs[3], base + offs[4]
             self.peers.meta[r] = base + offs[5]
-        self._local = dict(a=self.symm.local + offs[0], sa=self.symm.local + offs[1], y=self.symm.local + offs[2])
+        self._local = dict(a=self.symm.local + offs[0], y=self.symm.local + offs[2])
         # ---- private scratch
         i32 = dict(dtype=torch.int32, device=dev)
         self.ids = torch.empty((T_local, top_k), **i32)
@@ -142,8 +144,9 @@ class EpMoeLayer:
         self.s2 = torch.empty((inter // 128, cap), dtype=torch.float32, device=dev)
         self._keep = (w13, s13, w2, s2)
         # the grouped GEMMs see the symmetric buffers as ordinary tensors of this process
-        self.a1_t = self._wrap(self._local["a"], (cap, H), torch.uint8).view(torch.float8_e4m3fn)
-        self.s1_t = self._wrap(self._local["sa"], (H // 128, cap), torch.float32).t()
+        rec = self._wrap(self._local["a"], (cap, pitch), torch.uint8)
+        self.a1_t = rec[:, :H].view(torch.float8_e4m3fn)                    # [cap, H], row pitch = record size
+        self.s1_t = rec.view(torch.float32)[:, H // 4:H // 4 + H // 128]     # [cap, H/128], row stride = pitch/4
         self.y_t = self._wrap(self._local["y"], (y_rows, H), torch.bfloat16)
         self.meta_t = self._wrap(self.symm.local + offs[5], (cap,), torch.int32)
         rows_used = self.offsets[E_local:E_local + 1]
@@ -209,8 +212,8 @@ class EpMoeLayer:
             mark("plan")
             _lib.check(L.moe_ep_dispatch(P, _vp(self.x_q.data_ptr()), _vp(self.xs.data_ptr()), _i64(self.xs.stride(0)),
                                          _i64(self.xs.stride(1)), _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
-                                         _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap, self.rank,
-                                         self.world, st))
+                                         _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap,
+                                         _i64(self.pitch), self.rank, self.world, st))
             self._barrier(st)
             mark("dispatch+barrier")
             self.gemm1()

@@ -23,11 +23,15 @@ def _ptr(t: torch.Tensor) -> int:
     return t.data_ptr()
 
 
-def _check_fp8(t: torch.Tensor, name: str) -> None:
+def _check_fp8(t: torch.Tensor, name: str, allow_pitch: bool = False) -> None:
     if t.dtype not in (torch.float8_e4m3fn, torch.uint8):
         raise TypeError(f"{name} must be float8_e4m3fn (or its uint8 bytes), got {t.dtype}")
-    if not t.is_cuda or not t.is_contiguous():
-        raise ValueError(f"{name} must be a contiguous CUDA tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if allow_pitch and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1] and t.stride(0) % 16 == 0:
+        return                      # rows with a trailer (pitch > K)
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
 
 
 def _scale_strides(sfa: torch.Tensor, rows: int, kblocks: int, name: str):
@@ -55,7 +59,7 @@ class _BoundGG:
         self._args = _lib.GGArgs(
             a=_ptr(a), b=_ptr(b), sfa=_ptr(sfa), sfa_stride_row=sfa_strides[0], sfa_stride_kblk=sfa_strides[1],
             sfb=_ptr(sfb), layout=_ptr(layout), d=_ptr(d), ldd=d.stride(-2), G=G, M=M, N=N, K=K,
-            d_dtype=1 if d.dtype == torch.float32 else 0,
+            d_dtype=1 if d.dtype == torch.float32 else 0, lda=a.stride(-2) if a.dim() == 2 else 0,
             rows_used=_ptr(rows_used) if rows_used is not None else None,
             workspace=_ptr(self._ws) if self._ws is not None else None, workspace_bytes=ws_bytes)
         if scatter is not None:          # (meta int32[M] tensor, list of up to 8 base addresses)
@@ -75,10 +79,10 @@ class _BoundGG:
 
 
 def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace=True, scatter=None) -> _BoundGG:
-    """a fp8[M,K], sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb f32[G,ceil(N/128),K/128],
-    d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row); rows_used: optional
-    int32[1] device tensor with the number of leading rows in use."""
-    _check_fp8(a, "a"); _check_fp8(b, "b")
+    """a fp8[M,K] (row pitch may exceed K), sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb
+    f32[G,ceil(N/128),K/128], d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row);
+    rows_used: optional int32[1] device tensor with the number of leading rows in use."""
+    _check_fp8(a, "a", allow_pitch=True); _check_fp8(b, "b")
     M, K = a.shape
     G, N, Kb = b.shape
     if Kb != K or K % 128:
@@ -131,7 +135,7 @@ class _BoundGateUpAct:
         self._device = a.device
         self._args = _lib.GGArgs(a=_ptr(a), b=_ptr(b), sfa=_ptr(sfa), sfa_stride_row=sfa_strides[0],
                                  sfa_stride_kblk=sfa_strides[1], sfb=_ptr(sfb), layout=_ptr(layout), d=None, ldd=0,
-                                 G=G, M=M, N=N, K=K, d_dtype=0,
+                                 G=G, M=M, N=N, K=K, d_dtype=0, lda=a.stride(0),
                                  rows_used=_ptr(rows_used) if rows_used is not None else None, workspace=None,
                                  workspace_bytes=0)
         self._act = (ctypes.c_void_p(_ptr(act_q)), ctypes.c_void_p(_ptr(act_s)), ctypes.c_int64(act_s.stride(0)),
@@ -148,7 +152,7 @@ class _BoundGateUpAct:
 def bind_gate_up_act(a, sfa, b, sfb, act_q, act_s, grouped_layout, gate_first=False, rows_used=None):
     """a fp8[M,K], sfa f32[M,K/128], b fp8[G,2I,K], sfb f32[G,2I/128,K/128] -> act_q fp8[M,I], act_s f32[M,I/128]
     (any strides) = 1x128 requant of silu(gate)*up, computed from the fp32 accumulators inside the GEMM."""
-    _check_fp8(a, "a"); _check_fp8(b, "b"); _check_fp8(act_q, "act_q")
+    _check_fp8(a, "a", allow_pitch=True); _check_fp8(b, "b"); _check_fp8(act_q, "act_q")
     M, K = a.shape
     G, N, Kb = b.shape
     if Kb != K or K % 128 or N % 256:
