@@ -27,9 +27,9 @@ if ROOT not in sys.path:
 DATASHEET_FP8_TFLOPS = 4500.0
 DATASHEET_HBM_GBS = 8000.0
 
-# DRAM bytes per launch of gg_fp8_kernel on the `gemm` workload from the committed ncu capture
-# (profiles/): dram__bytes_read.sum + dram__bytes_write.sum.  None until captured.
-NCU_TRAFFIC_BYTES = {"gemm": None}
+# DRAM bytes per launch of the dominant kernel (gg_fp8_mx_kernel on the `gemm` workload) from the committed ncu
+# capture (profiles/gg_fp8_mx_kernel_contiguous_c1.md): dram__bytes_read.sum + dram__bytes_write.sum.
+NCU_TRAFFIC_BYTES = {"gemm": 799.4e6}
 
 WORKLOADS = {
     # contiguous layout: G groups of m rows (or `sizes` rows each, padded to 128)
