@@ -234,6 +234,48 @@ typedef struct moe_layer_view {
 int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, int32_t E, int32_t top_k,
                              int32_t align, moe_layer_view* view);
 
+/* ---- decode-regime layer from bf16 activations and preselected routes ------------------------ */
+/* Replaces the timed callable of the reference's `alphamoe` task: `setup(data, M)` of
+ * candidates/alphamoe/<name>/solution.py (evolution/tasks/alphamoe.yaml:17-47; data keys and shapes
+ * flashinfer_bench_evolve/tasks/alphamoe/benchmark.py, oracle `run` in its definition.json).  Everything the
+ * task times is inside the call: 1x128 quantisation of hidden_states (s = max(amax,1e-8)/448, true
+ * division), expert alignment, gate_up GEMM on rows stacked [gate; up] (fp32 kept), SiLU(gate)*up, 1x128
+ * requantisation, down GEMM, and the reduction: each route's down contribution times
+ * fp32(topk_weight * routed_scaling_factor) is rounded to bf16 and added to a zero bf16 accumulator with a
+ * rounding per update, experts in ascending id (definition.json `_reference_quantized`).
+ * Limits: I == 128 (one down contribution per route, as in the task's rows), H % 128 == 0, E <= 1024,
+ * top_k <= 32, M * top_k <= 32768, ids of one token distinct (an expert that receives more than M routes
+ * raises status bit 4096 and the excess routes are dropped).  The call launches on `stream`, allocates
+ * nothing and never synchronises (graph-capturable).                                             */
+typedef struct moe_alpha_args {
+    const void* hidden;           /* bf16 [M, H] */
+    const int32_t* topk_ids;      /* [M, top_k]; ids outside [0, E) are skipped */
+    const float* topk_weights;    /* [M, top_k] */
+    const void* w13;              /* e4m3 [E, 2I, H], rows [gate; up] */
+    const float* w13_scale;       /* [E, 2I/128, H/128] */
+    const void* w2;               /* e4m3 [E, H, I] */
+    const float* w2_scale;        /* [E, H/128, I/128] */
+    void* out;                    /* bf16 [M, H], overwritten */
+    int32_t M, H, I, E, top_k;
+    float routed_scaling_factor;
+    void* workspace;              /* moe_alpha_workspace_bytes(M, H, I, E, top_k), 256-byte aligned */
+    uint64_t workspace_bytes;
+} moe_alpha_args;
+size_t moe_alpha_workspace_bytes(int32_t M, int32_t H, int32_t I, int32_t E, int32_t top_k);
+int moe_alpha_forward(const moe_alpha_args* args, void* stream);
+
+/* Where moe_alpha_forward keeps its intermediates (for inspection / tests).  Expert e owns rows
+ * [e*max_m, e*max_m + counts[e]) of a1/g1/a2/d2; rowpos[p] is the row of route p (-1 = skipped);
+ * s1/s2 are MN-major: scale of (row, block b) at s[b*E*max_m + row].                             */
+typedef struct moe_alpha_view {
+    int32_t *counts, *rowpos;
+    float *s1, *s2, *g1, *d2;     /* g1 fp32 [E*max_m, 2I], d2 fp32 [E*max_m, H] */
+    void *a1, *a2;                /* e4m3 [E*max_m, H], [E*max_m, I] */
+    int64_t max_m;
+} moe_alpha_view;
+int moe_alpha_workspace_view(void* workspace, int32_t M, int32_t H, int32_t I, int32_t E, int32_t top_k,
+                             moe_alpha_view* view);
+
 /* ---- expert parallelism over NVLink peer memory --------------------------------------------- */
 /* The reference has no multi-GPU path: it emulates expert parallelism on one GPU through
  * `local_expert_offset` (tasks/moe/definition.json, inputs `local_expert_offset`; offsets 0..224 in

@@ -303,3 +303,47 @@ def moe_layer(x_q, x_scale, logits, w13, w13_scale, w2, w2_scale, top_k=8, e_lo=
     y = gg_contiguous(a2, w2, s2, w2_scale, gl, model=model)
     out = combine(y, plan["pos"], w)
     return dict(ids=ids, weights=w, plan=plan, a1=a1, s1=s1, g1=g1, a2=a2, s2=s2, y=y, out=out)
+
+
+# ---------------------------------------------------------------- alpha-MoE (decode-regime layer)
+def alpha_moe_layer(hidden_bits, ids, w, w13, w13_scale, w2, w2_scale, routed_scaling_factor=1.0,
+                    model=SIM_CHAIN):
+    """The `alphamoe` task operator, restated from its definition.json (`_quantize_inputs`,
+    `_reference_quantized`): bf16 activations [M,H] (uint16 bits) are quantised per 1x128 inside; each
+    route's expert computes gate_up (rows stacked [gate; up]) and SiLU(gate)*up in fp32, requantises
+    per 128, multiplies by the down weights; the down contribution times
+    fp32(weight * routed_scaling_factor) is rounded to bf16 and added to a zero bf16 accumulator with
+    a bf16 rounding per update, experts in ascending id (the reference's `for expert in range(E)`).
+    Intermediate size must be 128 (one down contribution per route), as in the task's rows.
+    Returns dict(out=bf16 bits [M,H], abs_sum, x_q, x_s, counts, order, g1, a2, s2, d2)."""
+    hidden_bits = _c_arr(hidden_bits, np.uint16)
+    ids = _c_arr(ids, np.int32)
+    w = _c_arr(w, np.float32)
+    M, H = hidden_bits.shape
+    top_k = ids.shape[1]
+    E = w13.shape[0]
+    inter = w2.shape[2]
+    if inter != 128:
+        raise ValueError("alpha_moe_layer models intermediate size 128 only")
+    x_q, x_s = quant_1x128(bf16_to_f32(hidden_bits))
+    expert = ids.reshape(-1)
+    pair = np.arange(expert.size)
+    keep = (expert >= 0) & (expert < E)
+    order = pair[keep][np.lexsort((pair[keep], expert[keep]))]          # expert ascending, then pair index
+    tok = order // top_k
+    gl = expert[order].astype(np.int32)
+    g1 = gg_contiguous(x_q[tok], w13, x_s[tok], w13_scale, gl, model=model, out_f32=True)
+    a2, s2 = silu_mul_requant(g1, gate_first=True)
+    d2 = gg_contiguous(a2, w2, s2, w2_scale, gl, model=model, out_f32=True)
+    out = np.zeros((M, H), np.float32)
+    abs_sum = np.zeros((M, H), np.float32)
+    rsf = np.float32(routed_scaling_factor)
+    for r, p in enumerate(order):
+        t = p // top_k
+        scale = np.float32(w.reshape(-1)[p] * rsf)
+        c = bf16_to_f32(bf16_rne(d2[r] * scale))
+        out[t] = bf16_to_f32(bf16_rne(out[t] + c))
+        abs_sum[t] += np.abs(c)
+    counts = np.bincount(expert[keep], minlength=E).astype(np.int32)
+    return dict(out=bf16_rne(out), abs_sum=abs_sum, x_q=x_q, x_s=x_s, counts=counts, order=order.astype(np.int64),
+                g1=g1, a2=a2, s2=s2, d2=d2)

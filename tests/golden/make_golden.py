@@ -173,6 +173,42 @@ def alphamoe_oracle():
     )
 
 
+def alphamoe_bf16_layer():
+    """The alphamoe task's full operator (`run` of its definition.json: bf16 activations quantised inside,
+    preselected routes, expert-order bf16 accumulation) on a small case with a non-trivial
+    routed_scaling_factor; stores the inputs and what the reference returns."""
+    import torch
+    d = json.load(open(os.path.join(
+        REF, "evolution/benchmark/flashinfer_bench_evolve/tasks/alphamoe/definition.json")))
+    ns: dict = {}
+    exec(compile(d["reference"], "alphamoe/definition.json:reference", "exec"), ns)
+    torch.manual_seed(11)
+    M, H, I, E, top_k, rsf = 12, 256, 128, 8, 3, 2.5
+    hs = (torch.randn(M, H) * torch.exp2(torch.randint(-2, 3, (M, 1)).float())).bfloat16()
+
+    def qw(shape):
+        w = torch.randn(*shape) * 0.5
+        blocks = w.reshape(shape[0], shape[1] // 128, 128, shape[2] // 128, 128)
+        sc = blocks.abs().amax(dim=(2, 4)).clamp_min(1e-8) / 448.0
+        wq = (blocks / sc[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+        return wq.reshape(shape), sc.float()
+    w13, s13 = qw((E, 2 * I, H))
+    w2, s2 = qw((E, H, I))
+    ids = torch.stack([torch.randperm(E)[:top_k] for _ in range(M)]).int()
+    tw = torch.rand(M, top_k).float()
+    tw = tw / tw.sum(dim=1, keepdim=True)
+    out, bound = ns["reference_for_check"](hs, ids, tw, w13, s13, w2, s2, top_k, rsf)
+    xq, xs = ns["_quantize_inputs"](hs)
+    _, abs_sum = ns["_reference_quantized"](xq, xs, ids, tw, w13, s13, w2, s2, top_k, rsf)
+    u8 = lambda t: t.view(torch.uint8).numpy()
+    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)
+    np.savez_compressed(
+        os.path.join(OUT, "alphamoe_bf16_layer.npz"),
+        hidden_bits=bits(hs), ids=ids.numpy(), w=tw.numpy(), w13=u8(w13), s13=s13.numpy(), w2=u8(w2), s2=s2.numpy(),
+        rsf=np.float32(rsf), xq=u8(xq), xs=xs.numpy(), out_bits=bits(out), bound=bound.numpy(), abs_sum=abs_sum.numpy(),
+    )
+
+
 def moe_routing():
     """Runs the routing block of the reference's `moe` task oracle (definition.json, between the markers
     "# 2) No-aux routing" and "# 3) Local expert compute") on random logits and stores what it selects."""
@@ -201,6 +237,7 @@ if __name__ == "__main__":
     cvt_goldens()
     codec_and_gemm(ref)
     alphamoe_oracle()
+    alphamoe_bf16_layer()
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(OUT, f)))

@@ -36,7 +36,8 @@ def test_struct_layouts_match_header_field_order():
     from tirx_harness_b200 import _lib
     text = open(os.path.join(ROOT, "include", "b200moe.h")).read()
     for cname, pystruct in (("moe_gg_args", _lib.GGArgs), ("moe_layer_args", _lib.LayerArgs),
-                            ("moe_layer_view", _lib.LayerView), ("moe_ep_peers", _lib.EpPeers)):
+                            ("moe_layer_view", _lib.LayerView), ("moe_ep_peers", _lib.EpPeers),
+                            ("moe_alpha_args", _lib.AlphaArgs), ("moe_alpha_view", _lib.AlphaView)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -57,3 +58,7 @@ def test_workspace_size_is_monotonic_and_cpu_callable():
     assert 0 < a < b
     assert L.moe_workspace_bytes(-1, 256, 256, 4, 2, 128) == 0
     assert L.moe_permute_workspace_bytes(ctypes.c_int64(4096), 32) >= 4 * 32 * 4
+    # decode-regime layer: the workspace grows with the token count, not with it times the expert count squared
+    small, big = L.moe_alpha_workspace_bytes(1, 2048, 128, 512, 10), L.moe_alpha_workspace_bytes(128, 2048, 128, 512, 10)
+    assert 0 < small < big < (1 << 30)
+    assert L.moe_alpha_workspace_bytes(8, 0, 128, 512, 10) == 0

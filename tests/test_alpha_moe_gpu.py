@@ -1,0 +1,183 @@
+"""Decode-regime MoE layer (the reference's `alphamoe` workload) on the GPU, through the C ABI, against the
+CPU oracle's restatement of the task's definition.json and against the fixture its own `run` produced."""
+import os
+
+import numpy as np
+import pytest
+
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _quant_weights(rng, E, rows, cols, std=0.125):
+    """128x128-block e4m3 weights the way the task's generator makes them (scale = amax/448)."""
+    w = (rng.standard_normal((E, rows, cols)) * std).astype(np.float32)
+    blocks = w.reshape(E, rows // 128, 128, cols // 128, 128)
+    sc = np.maximum(np.abs(blocks).max(axis=(2, 4)), 1e-8).astype(np.float32) / np.float32(448.0)
+    q = orc.e4m3_encode(np.clip(blocks / sc[:, :, None, :, None], -448, 448).astype(np.float32).reshape(E, rows, cols))
+    return q.reshape(E, rows, cols), sc.astype(np.float32)
+
+
+def _case(M, H, E, top_k, seed, rsf=1.0, skew=0.0):
+    rng = np.random.default_rng(seed)
+    hs = torch.from_numpy((rng.standard_normal((M, H)) * 0.25).astype(np.float32)).bfloat16()
+    scores = rng.standard_normal((M, E)).astype(np.float32)
+    scores[:, 0] += skew
+    ids = np.argsort(-scores, axis=1, kind="stable")[:, :top_k].astype(np.int32)
+    logits = rng.standard_normal((M, top_k)).astype(np.float32)
+    w = np.exp(logits - logits.max(axis=1, keepdims=True))
+    w = (w / w.sum(axis=1, keepdims=True)).astype(np.float32)
+    w13, s13 = _quant_weights(rng, E, 256, H)
+    w2, s2 = _quant_weights(rng, E, H, 128)
+    return dict(hs=hs, ids=ids, w=w, w13=w13, s13=s13, w2=w2, s2=s2, rsf=rsf)
+
+
+def _dev(x, dev):
+    return x.to(dev) if isinstance(x, torch.Tensor) else torch.from_numpy(x).to(dev)
+
+
+def _run_gpu(c, M):
+    from tirx_harness_b200 import alpha_moe
+    dev = torch.device("cuda:0")
+    data = {
+        "hidden_states": c["hs"].to(dev), "topk_ids": torch.from_numpy(c["ids"]).to(dev),
+        "topk_weights": torch.from_numpy(c["w"]).to(dev),
+        "gemm1_weights": _dev(c["w13"], dev).view(torch.float8_e4m3fn),
+        "gemm1_weights_scale": _dev(c["s13"], dev),
+        "gemm2_weights": _dev(c["w2"], dev).view(torch.float8_e4m3fn),
+        "gemm2_weights_scale": _dev(c["s2"], dev),
+        "top_k": c["ids"].shape[1], "routed_scaling_factor": c["rsf"],
+        "output": torch.full((M, c["hs"].shape[1]), float("nan"), dtype=torch.bfloat16, device=dev),
+    }
+    op = alpha_moe.setup(data, M)
+    op()
+    torch.cuda.synchronize()
+    from tirx_harness_b200 import grouped_gemm
+    assert grouped_gemm.device_status() == 0
+    return op, data
+
+
+def _check_against_oracle(c, op, data, M):
+    E, top_k = c["w13"].shape[0], c["ids"].shape[1]
+    res = orc.alpha_moe_layer(_bits(c["hs"]), c["ids"], c["w"], c["w13"], c["s13"], c["w2"], c["s2"],
+                              routed_scaling_factor=c["rsf"])
+    it = op.intermediates()
+    max_m = it["max_m"]
+    counts = it["counts"].cpu().numpy()
+    rowpos = it["rowpos"].cpu().numpy().reshape(-1)
+    # integer artefacts: counts == bincount(routes); every route sits in its expert's row range, slots in route order
+    np.testing.assert_array_equal(counts, res["counts"])
+    expert = c["ids"].reshape(-1)
+    assert ((rowpos // max_m) == expert).all()
+    for e in np.unique(expert):
+        slots = rowpos[expert == e] - e * max_m
+        np.testing.assert_array_equal(slots, np.arange(slots.size))
+    # quantised activations of every route: bit-exact (bytes and scales)
+    rows = rowpos[res["order"]]
+    tok = res["order"] // top_k
+    a1 = it["a1"].cpu().numpy()
+    s1 = it["s1"].cpu().numpy()
+    np.testing.assert_array_equal(a1[rows], res["x_q"][tok])
+    np.testing.assert_array_equal(s1[:, rows].T, res["x_s"][tok])
+    # fp32 gate_up: the task-wide tolerance on the accumulator
+    g1 = it["g1"].cpu().numpy()[rows]
+    ref = res["g1"]
+    floor = 2.0**-7 * np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+    assert (np.abs(g1 - ref) / np.maximum(np.abs(ref), floor)).max() <= 1e-3
+    # final bf16 output: inside the task's bound around the oracle (atol = rtol = 0.02), and mostly equal to the bit
+    got = orc.bf16_to_f32(_bits(data["output"]))
+    want = orc.bf16_to_f32(res["out"])
+    assert np.isfinite(got).all()
+    bound = np.maximum(0.02 + 0.02 * np.abs(want), 2.0 * res["abs_sum"] * 2.0**-7)
+    assert (np.abs(got - want) <= bound).all()
+    assert (_bits(data["output"]) == res["out"]).mean() > 0.9
+    return res
+
+
+@pytest.mark.parametrize("M,H,E,top_k,skew", [(1, 256, 8, 3, 0.0), (5, 512, 16, 4, 0.0), (16, 256, 64, 6, 3.0),
+                                                (33, 2048, 48, 10, 0.0)])
+def test_alpha_layer_matches_oracle(M, H, E, top_k, skew):
+    c = _case(M, H, E, top_k, seed=100 + M, rsf=1.0 if M % 2 else 2.5, skew=skew)
+    op, data = _run_gpu(c, M)
+    _check_against_oracle(c, op, data, M)
+
+
+def test_alpha_layer_matches_reference_fixture(golden_dir):
+    g = np.load(os.path.join(golden_dir, "alphamoe_bf16_layer.npz"))
+    M = g["hidden_bits"].shape[0]
+    hs = torch.from_numpy(g["hidden_bits"].view(np.int16).copy()).view(torch.bfloat16)
+    c = dict(hs=hs, ids=g["ids"], w=g["w"], w13=g["w13"], s13=g["s13"], w2=g["w2"], s2=g["s2"], rsf=float(g["rsf"]))
+    op, data = _run_gpu(c, M)
+    got = orc.bf16_to_f32(_bits(data["output"]))
+    ref = orc.bf16_to_f32(g["out_bits"])
+    assert (np.abs(got - ref) <= g["bound"]).all()                          # the task's own gate (atol = rtol = 0.1)
+    tight = np.maximum(0.02 + 0.02 * np.abs(ref), 2.0 * g["abs_sum"] * 2.0**-7)
+    assert (np.abs(got - ref) <= tight).all()
+    it = op.intermediates()
+    rowpos = it["rowpos"].cpu().numpy().reshape(-1)
+    tok = np.arange(rowpos.size) // g["ids"].shape[1]
+    np.testing.assert_array_equal(it["a1"].cpu().numpy()[rowpos], g["xq"][tok])     # in-call quantisation, bit-exact
+    np.testing.assert_array_equal(it["s1"].cpu().numpy()[:, rowpos].T, g["xs"][tok])
+
+
+def test_alpha_layer_recomputes_from_current_inputs_and_overwrites_output():
+    """The harness poisons the output before every checked call and perturbs inputs in place afterwards."""
+    M = 8
+    c = _case(M, 256, 32, 4, seed=7)
+    op, data = _run_gpu(c, M)
+    first = data["output"].clone()
+    data["output"].fill_(float("nan"))
+    op()
+    torch.cuda.synchronize()
+    assert torch.equal(first, data["output"])
+    data["hidden_states"].mul_(2.0)
+    op()
+    torch.cuda.synchronize()
+    assert not torch.equal(first, data["output"])
+    c2 = dict(c, hs=data["hidden_states"].cpu())
+    _check_against_oracle(c2, op, data, M)
+
+
+def test_alpha_layer_full_size_row_m128_properties():
+    """The task's largest official row (M=128, K=2048, I=128, E=512, top-10): conservation laws only (the oracle
+    takes minutes at this size): counts, finite output, and linearity in the route weights: doubling
+    routed_scaling_factor doubles every bf16 contribution exactly, hence the output."""
+    M, H, E, top_k = 128, 2048, 512, 10
+    c = _case(M, H, 8, top_k if top_k <= 8 else 8, seed=42)        # activations only; routes and weights below
+    rng = np.random.default_rng(42)
+    c["ids"] = np.argsort(-rng.standard_normal((M, E)), axis=1, kind="stable")[:, :top_k].astype(np.int32)
+    c["w"] = rng.dirichlet(np.ones(top_k), size=M).astype(np.float32)
+    gen = torch.Generator(device="cuda:0").manual_seed(42)
+
+    def rand_fp8(*shape):          # random e4m3 bytes without the two NaN codes
+        b = torch.randint(0, 256, shape, dtype=torch.uint8, device="cuda:0", generator=gen)
+        return torch.where((b & 0x7F) == 0x7F, torch.zeros_like(b), b)
+    c["w13"], c["w2"] = rand_fp8(E, 256, H), rand_fp8(E, H, 128)
+    c["s13"] = torch.rand((E, 2, H // 128), device="cuda:0", generator=gen) * 2e-4 + 1e-4
+    c["s2"] = torch.rand((E, H // 128, 1), device="cuda:0", generator=gen) * 2e-4 + 1e-4
+    op, data = _run_gpu(c, M)
+    out1 = data["output"].float().clone()
+    counts = op.intermediates()["counts"].cpu().numpy()
+    np.testing.assert_array_equal(counts, np.bincount(c["ids"].reshape(-1), minlength=E))
+    assert torch.isfinite(out1).all() and out1.abs().max() > 0
+    c2 = dict(c, rsf=2.0)
+    op2, data2 = _run_gpu(c2, M)
+    assert torch.equal(data2["output"].float(), 2.0 * out1)
+
+
+def test_alpha_layer_rejects_unsupported_shapes():
+    from tirx_harness_b200 import _lib
+    c = _case(4, 256, 8, 2, seed=3)
+    c["w13"] = np.concatenate([c["w13"], c["w13"]], axis=1)          # I = 256
+    c["s13"] = np.concatenate([c["s13"], c["s13"]], axis=1)
+    c["w2"] = np.concatenate([c["w2"], c["w2"]], axis=2)
+    c["s2"] = np.concatenate([c["s2"], c["s2"]], axis=2)
+    with pytest.raises(_lib.B200MoeError):
+        _run_gpu(c, 4)

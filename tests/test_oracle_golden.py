@@ -194,6 +194,26 @@ def test_moe_layer_matches_alphamoe_oracle_within_its_bound(golden_dir):
         assert rows.size == plan["counts"][e] and (plan["offsets"][e] % 128 == 0)
 
 
+def test_alpha_moe_layer_matches_alphamoe_run_within_its_bound(golden_dir):
+    """bf16 in, quantised inside, expert-order bf16 accumulation: against `run` of alphamoe/definition.json."""
+    g = _g(golden_dir, "alphamoe_bf16_layer.npz")
+    res = orc.alpha_moe_layer(g["hidden_bits"], g["ids"], g["w"], g["w13"], g["s13"], g["w2"], g["s2"],
+                              routed_scaling_factor=float(g["rsf"]))
+    # the in-call quantisation is integer work: bit-exact against the reference's eager Torch recipe
+    np.testing.assert_array_equal(res["x_q"], g["xq"])
+    np.testing.assert_array_equal(res["x_s"], g["xs"])
+    np.testing.assert_array_equal(res["counts"], np.bincount(g["ids"].reshape(-1), minlength=g["w13"].shape[0]))
+    got = orc.bf16_to_f32(res["out"])
+    ref = orc.bf16_to_f32(g["out_bits"])
+    bound = np.maximum(0.02 + 0.02 * np.abs(ref), 2.0 * g["abs_sum"] * 2.0**-7)      # the task's bound, atol=rtol=0.02
+    assert (np.abs(got - ref) <= bound).all()
+    assert (np.abs(got - ref) <= g["bound"]).all()                                   # and as published (0.1/0.1)
+    # the accumulated contribution mass follows the same rounding rule: close to the reference's
+    np.testing.assert_allclose(res["abs_sum"], g["abs_sum"], rtol=0.02, atol=0.02)
+    # most elements agree to the bit: the differences are fp32 summation order inside the GEMMs
+    assert (res["out"] == g["out_bits"]).mean() > 0.8
+
+
 def test_route_softmax_topk_ties_and_weights():
     logits = np.zeros((3, 16), np.float32)
     logits[1, [5, 9, 2]] = [3.0, 3.0, 1.0]

@@ -48,6 +48,22 @@ class LayerView(_c.Structure):
                                            "weights", "s1", "s2", "a1", "g1", "a2", "y")] + [("cap_rows", _c.c_int64)]
 
 
+class AlphaArgs(_c.Structure):
+    """``moe_alpha_args`` of include/b200moe.h."""
+    _fields_ = [
+        ("hidden", _c.c_void_p), ("topk_ids", _c.c_void_p), ("topk_weights", _c.c_void_p),
+        ("w13", _c.c_void_p), ("w13_scale", _c.c_void_p), ("w2", _c.c_void_p), ("w2_scale", _c.c_void_p),
+        ("out", _c.c_void_p),
+        ("M", _c.c_int32), ("H", _c.c_int32), ("I", _c.c_int32), ("E", _c.c_int32), ("top_k", _c.c_int32),
+        ("routed_scaling_factor", _c.c_float), ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
+    ]
+
+
+class AlphaView(_c.Structure):
+    """``moe_alpha_view`` of include/b200moe.h."""
+    _fields_ = [(n, _c.c_void_p) for n in ("counts", "rowpos", "s1", "s2", "g1", "d2", "a1", "a2")] + [("max_m", _c.c_int64)]
+
+
 class EpPeers(_c.Structure):
     """``moe_ep_peers`` of include/b200moe.h."""
     _fields_ = [("a", _c.c_void_p * 8), ("sa", _c.c_void_p * 8), ("y", _c.c_void_p * 8),
@@ -86,12 +102,14 @@ EXPORTS = (
     "moe_route_topk", "moe_route_deepseek", "moe_permute_workspace_bytes", "moe_permute_plan", "moe_permute_plan_static", "moe_permute",
     "moe_combine",
     "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
+    "moe_alpha_workspace_bytes", "moe_alpha_forward", "moe_alpha_workspace_view",
     "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",
     "moe_ep_barrier", "moe_ep_workspace_bytes", "moe_ep_count_publish", "moe_ep_plan", "moe_ep_dispatch",
     "moe_ep_combine",
     "moe_last_error", "moe_version",
 )
-_SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes")
+_SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes",
+                  "moe_alpha_workspace_bytes")
 
 
 def check(rc: int) -> None:

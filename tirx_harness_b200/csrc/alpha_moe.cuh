@@ -1,0 +1,182 @@
+// Decode-regime MoE layer from bf16 activations and preselected routes (few tokens, hundreds of experts,
+// intermediate size 128): the kernels around the two masked-layout grouped GEMMs.
+//
+//   alpha_plan_kernel          per-expert route counts and the slot of every route inside its expert
+//   alpha_quant_scatter_kernel token row -> 1x128 FP8 quantisation -> the route's row of the masked A matrix
+//   alpha_silu_requant_kernel  fp32 [gate; up] row -> SiLU(gate)*up -> 1x128 requant
+//   alpha_combine_kernel       per token: contributions in ascending expert id, each rounded to bf16 and
+//                              added to a bf16 accumulator with a rounding per update
+//
+// Every expert owns `max_m` consecutive rows of the intermediate matrices; only the first counts[e] are
+// written or read, so the kernels touch (routes x row bytes) of memory whatever E is.
+#pragma once
+
+#include "moe_ops.cuh"
+
+namespace b200 {
+
+constexpr int ALPHA_PLAN_THREADS = 1024;
+constexpr int STATUS_ALPHA_OVERFLOW = 1 << 12;      // an expert received more routes than max_m rows
+
+// One CTA.  Deterministic: route p's slot is the number of earlier routes (smaller p) to the same expert.
+// hist: [32 warps][E] in dynamic shared memory.  Warp w owns the contiguous routes [w*per, (w+1)*per).
+__global__ void __launch_bounds__(ALPHA_PLAN_THREADS, 1)
+alpha_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int max_m, int* __restrict__ counts,
+                  int* __restrict__ rowpos, int* status) {
+    extern __shared__ int hist[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 32 * E; i += ALPHA_PLAN_THREADS) hist[i] = 0;
+    __syncthreads();
+    const int per = (((n_pairs + 31) / 32) + 31) & ~31;
+    const int begin = warp * per;
+    const int end = min(begin + per, n_pairs);
+    for (int base = begin; base < end; base += 32) {
+        const int p = base + lane;
+        const int e = p < end ? __ldg(ids + p) : -1;
+        const bool valid = e >= 0 && e < E;
+        const unsigned mask = __match_any_sync(0xffffffffu, valid ? e : E + lane);
+        if (valid && lane == __ffs(mask) - 1) hist[warp * E + e] += __popc(mask);
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += ALPHA_PLAN_THREADS) {
+        int run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const int c = hist[w * E + e];
+            hist[w * E + e] = run;
+            run += c;
+        }
+        if (run > max_m) {
+            atomicOr(status, STATUS_ALPHA_OVERFLOW);
+            run = max_m;
+        }
+        counts[e] = run;
+    }
+    __syncthreads();
+    for (int base = begin; base < end; base += 32) {
+        const int p = base + lane;
+        const int e = p < end ? __ldg(ids + p) : -1;
+        const bool valid = e >= 0 && e < E;
+        const unsigned mask = __match_any_sync(0xffffffffu, valid ? e : E + lane);
+        const int leader = __ffs(mask) - 1;
+        int first = 0;
+        if (valid && lane == leader) {
+            first = hist[warp * E + e];
+            hist[warp * E + e] = first + __popc(mask);
+        }
+        first = __shfl_sync(0xffffffffu, first, leader);
+        const int slot = first + __popc(mask & ((1u << lane) - 1u));
+        if (p < end) rowpos[p] = (valid && slot < max_m) ? e * max_m + slot : -1;
+        __syncwarp();
+    }
+}
+
+// One warp per route.  x bf16 [M, H]; q e4m3 [rows_total, H]; scales MN-major: scale of (row, block b) at
+// s[b * rows_total + row].
+__global__ void alpha_quant_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rowpos,
+                                           int n_pairs, int top_k, int H, long long rows_total,
+                                           uint8_t* __restrict__ q, float* __restrict__ s) {
+    const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (p >= n_pairs) return;
+    const int row = __ldg(rowpos + p);
+    if (row < 0) return;
+    const __nv_bfloat16* src = x + (long long)(p / top_k) * H + lane * 4;
+    uint8_t* dst = q + (long long)row * H + lane * 4;
+    const int nb = H >> 7;
+    for (int b0 = 0; b0 < nb; b0 += 4) {
+        uint2 raw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (b0 + i < nb) raw[i] = __ldg(reinterpret_cast<const uint2*>(src + (b0 + i) * 128));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (b0 + i < nb) {
+                float v[4], sc;
+                bf16x4_to_float(raw[i], v);
+                const uint32_t packed = quant_block_4(v, &sc);
+                *reinterpret_cast<uint32_t*>(dst + (b0 + i) * 128) = packed;
+                if (lane == 0) s[(long long)(b0 + i) * rows_total + row] = sc;
+            }
+        }
+    }
+}
+
+// One warp per route.  gu fp32 [rows_total, 2I] with gate = columns [0, I) when gate_first, else [I, 2I).
+__global__ void alpha_silu_requant_kernel(const float* __restrict__ gu, const int* __restrict__ rowpos, int n_pairs,
+                                          int inter, int gate_first, long long rows_total, uint8_t* __restrict__ q,
+                                          float* __restrict__ s) {
+    const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (p >= n_pairs) return;
+    const int row = __ldg(rowpos + p);
+    if (row < 0) return;
+    const float* grow = gu + (long long)row * 2 * inter + (gate_first ? 0 : inter) + lane * 4;
+    const float* urow = gu + (long long)row * 2 * inter + (gate_first ? inter : 0) + lane * 4;
+    const int nb = inter >> 7;
+    for (int b = 0; b < nb; ++b) {
+        const float4 g = *reinterpret_cast<const float4*>(grow + b * 128);
+        const float4 u = *reinterpret_cast<const float4*>(urow + b * 128);
+        float a[4], sc;
+        a[0] = __fmul_rn(silu_f32(g.x), u.x);
+        a[1] = __fmul_rn(silu_f32(g.y), u.y);
+        a[2] = __fmul_rn(silu_f32(g.z), u.z);
+        a[3] = __fmul_rn(silu_f32(g.w), u.w);
+        const uint32_t packed = quant_block_4(a, &sc);
+        *reinterpret_cast<uint32_t*>(q + (long long)row * inter + b * 128 + lane * 4) = packed;
+        if (lane == 0) s[(long long)b * rows_total + row] = sc;
+    }
+}
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// One CTA per token.  d fp32 [rows_total, H] holds the unweighted down projections.  The token's routes are
+// ordered by expert id (ties by route index); out = bf16 chain: acc = bf16(acc + bf16(d * (w * rsf))).
+__global__ void alpha_combine_kernel(const float* __restrict__ d, const int* __restrict__ ids,
+                                     const float* __restrict__ w, const int* __restrict__ rowpos, float rsf, int top_k,
+                                     int H, __nv_bfloat16* __restrict__ out) {
+    __shared__ int s_row[32];
+    __shared__ float s_scale[32];
+    __shared__ int s_n;
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int key[32], idx[32], n = 0;
+        for (int j = 0; j < top_k; ++j) {
+            if (__ldg(rowpos + t * top_k + j) < 0) continue;
+            const int e = __ldg(ids + t * top_k + j);
+            int k = n++;
+            while (k > 0 && key[k - 1] > e) {      // stable insertion sort, at most 32 entries
+                key[k] = key[k - 1];
+                idx[k] = idx[k - 1];
+                --k;
+            }
+            key[k] = e;
+            idx[k] = j;
+        }
+        for (int k = 0; k < n; ++k) {
+            s_row[k] = __ldg(rowpos + t * top_k + idx[k]);
+            s_scale[k] = __fmul_rn(__ldg(w + t * top_k + idx[k]), rsf);
+        }
+        s_n = n;
+    }
+    __syncthreads();
+    const int n = s_n;
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (int k = 0; k < n; ++k) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(d + (long long)s_row[k] * H + c));
+            const float sc = s_scale[k];
+            a0 = round_bf16(a0 + round_bf16(__fmul_rn(v.x, sc)));
+            a1 = round_bf16(a1 + round_bf16(__fmul_rn(v.y, sc)));
+            a2 = round_bf16(a2 + round_bf16(__fmul_rn(v.z, sc)));
+            a3 = round_bf16(a3 + round_bf16(__fmul_rn(v.w, sc)));
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a0, a1), hi = __floats2bfloat162_rn(a2, a3);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + (long long)t * H + c) = o;
+    }
+}
+
+}  // namespace b200

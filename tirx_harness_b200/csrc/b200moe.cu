@@ -16,6 +16,7 @@
 #include "gg_fp8_2cta.cuh"
 #include "gg_fp8_mx.cuh"
 #include "moe_ops.cuh"
+#include "alpha_moe.cuh"
 
 namespace {
 
@@ -141,6 +142,10 @@ int device_info(DeviceInfo** out) {
                                       mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      mx1::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      mx1::SMEM_BYTES));
         {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(2 * di.num_sms, 1, 1);
@@ -271,19 +276,31 @@ int launch_gg(const moe_gg_args* a, void* stream) {
             mx_prep_kernel<<<pgrid, 128, 0, st>>>(a->sfa, a->sfa_stride_row, a->sfa_stride_kblk, a->sfb, (int)rows_total,
                                                   p.num_k_blocks, a->G, p.nb128, ws);
         CUDA_TRY(cudaGetLastError());
+        const char* env_mxk = getenv("B200MOE_MX_KERNEL");        // "pair" or "single"
+        // measured: CTA pairs win on full 256-row blocks (contiguous layout), single CTAs on the masked
+        // layout, where a pair multiplies up to 255 empty rows per group
+        const bool mx_single = env_mxk ? strcmp(env_mxk, "single") == 0 : MASKED;
         CUtensorMap tmap_b2, tmap_sfa, tmap_sfb;
-        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx::BN / 2);
+        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx_single ? mx1::BN : mx::BN / 2);
         if (rc != MOE_OK) return rc;
         rc = encode_words_1d(&tmap_sfa, ws.sfa_packed, (uint64_t)ml.row_blocks * ml.quads * 128);
         if (rc != MOE_OK) return rc;
         rc = encode_words_1d(&tmap_sfb, ws.sfb_packed, (uint64_t)a->G * p.nb128 * ml.quads * 128);
         if (rc != MOE_OK) return rc;
-        const long long row_blocks256 = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
-        const long long tiles = row_blocks256 * p.num_n_blocks;
-        int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
-        if (pairs < 1) pairs = 1;
-        gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
-                                                                               ws.flag, ml.quads, status_ptr());
+        if (mx_single) {
+            const long long tiles1 = (MASKED ? (long long)a->G * p.num_m_blocks : (long long)p.num_m_blocks) * p.num_n_blocks;
+            int grid1 = (int)(tiles1 < di->num_sms ? tiles1 : di->num_sms);
+            if (grid1 < 1) grid1 = 1;
+            gg_fp8_mx1_kernel<MASKED><<<grid1, mx1::THREADS, mx1::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
+                                                                                   ws.flag, ml.quads, status_ptr());
+        } else {
+            const long long row_blocks256 = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
+            const long long tiles = row_blocks256 * p.num_n_blocks;
+            int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
+            if (pairs < 1) pairs = 1;
+            gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
+                                                                                   ws.flag, ml.quads, status_ptr());
+        }
         CUDA_TRY(cudaGetLastError());
         p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
         if (packed_sf) return MOE_OK;    // UE8M0 bytes are powers of two by construction: nothing else to run
@@ -414,6 +431,45 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     gg_fp8_kernel<false, true><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
         tmap_a, tmap_b, p, status_ptr());
     CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+struct AlphaWorkspace {
+    int32_t *counts, *rowpos;
+    float *s1, *s2, *g1, *d2;
+    uint8_t *a1, *a2;
+    int64_t max_m, rows_total;
+    size_t bytes;
+};
+
+// Rows per expert: no expert can receive more than M routes (ids of a token are distinct); at least 128 rows in
+// total so that a 128-row TMA box never exceeds the tensor.
+AlphaWorkspace carve_alpha(void* base, int64_t M, int64_t H, int64_t I, int64_t E, int64_t top_k) {
+    AlphaWorkspace w{};
+    w.max_m = M > 0 ? M : 1;
+    while (w.max_m * E < 128) ++w.max_m;
+    w.rows_total = w.max_m * E;
+    char* b = static_cast<char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char* p = b ? b + off : nullptr; off += align256(bytes); return p; };
+    w.counts = reinterpret_cast<int32_t*>(take((size_t)E * 4));
+    w.rowpos = reinterpret_cast<int32_t*>(take((size_t)(M * top_k > 0 ? M * top_k : 1) * 4));
+    w.a1 = reinterpret_cast<uint8_t*>(take((size_t)w.rows_total * H));
+    w.s1 = reinterpret_cast<float*>(take((size_t)w.rows_total * (H / 128) * 4));
+    w.g1 = reinterpret_cast<float*>(take((size_t)w.rows_total * 2 * I * 4));
+    w.a2 = reinterpret_cast<uint8_t*>(take((size_t)w.rows_total * I));
+    w.s2 = reinterpret_cast<float*>(take((size_t)w.rows_total * (I / 128) * 4));
+    w.d2 = reinterpret_cast<float*>(take((size_t)w.rows_total * H * 4));
+    w.bytes = off;
+    return w;
+}
+
+int check_alpha_dims(int32_t M, int32_t H, int32_t I, int32_t E, int32_t top_k) {
+    if (M < 0 || H <= 0 || H % 128) return fail(MOE_ERR_INVALID, "M must be non-negative and H a positive multiple of 128");
+    if (I != 128) return fail(MOE_ERR_UNSUPPORTED, "the decode-regime layer supports I == 128 only (I=%d)", I);
+    if (E <= 0 || E > gg::MAX_MASKED_GROUPS) return fail(MOE_ERR_INVALID, "E=%d must be in [1, %d]", E, gg::MAX_MASKED_GROUPS);
+    if (top_k <= 0 || top_k > 32) return fail(MOE_ERR_INVALID, "top_k=%d must be in [1, 32]", top_k);
+    if ((int64_t)M * top_k > 32768) return fail(MOE_ERR_UNSUPPORTED, "M*top_k=%lld exceeds 32768 routes", (long long)M * top_k);
     return MOE_OK;
 }
 
@@ -641,6 +697,76 @@ int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, i
     view->pos = w.pos; view->src_pair = w.src_pair; view->grouped_layout = w.layout;
     view->a1 = w.a1; view->s1 = w.s1; view->g1 = w.g1; view->a2 = w.a2; view->s2 = w.s2; view->y = w.y;
     view->cap_rows = w.cap_rows;
+    return MOE_OK;
+}
+
+/* ---------------------------------------------------------------- decode-regime layer (alphamoe task) */
+size_t moe_alpha_workspace_bytes(int32_t M, int32_t H, int32_t I, int32_t E, int32_t top_k) {
+    if (M < 0 || H <= 0 || I <= 0 || E <= 0 || top_k <= 0) return 0;
+    return carve_alpha(nullptr, M, H, I, E, top_k).bytes;
+}
+
+int moe_alpha_workspace_view(void* workspace, int32_t M, int32_t H, int32_t I, int32_t E, int32_t top_k,
+                             moe_alpha_view* view) {
+    if (!view) return fail(MOE_ERR_INVALID, "view is NULL");
+    int rc = check_alpha_dims(M, H, I, E, top_k);
+    if (rc != MOE_OK) return rc;
+    AlphaWorkspace w = carve_alpha(workspace, M, H, I, E, top_k);
+    view->counts = w.counts; view->rowpos = w.rowpos; view->s1 = w.s1; view->s2 = w.s2; view->g1 = w.g1;
+    view->d2 = w.d2; view->a1 = w.a1; view->a2 = w.a2; view->max_m = w.max_m;
+    return MOE_OK;
+}
+
+int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
+    if (!A) return fail(MOE_ERR_INVALID, "args is NULL");
+    int rc = check_alpha_dims(A->M, A->H, A->I, A->E, A->top_k);
+    if (rc != MOE_OK) return rc;
+    if (!A->hidden || !A->topk_ids || !A->topk_weights || !A->w13 || !A->w13_scale || !A->w2 || !A->w2_scale || !A->out ||
+        !A->workspace)
+        return fail(MOE_ERR_INVALID, "hidden, topk_ids, topk_weights, weights, scales, out and workspace must be non-NULL");
+    if ((reinterpret_cast<uintptr_t>(A->hidden) & 15) || (reinterpret_cast<uintptr_t>(A->out) & 15) ||
+        (reinterpret_cast<uintptr_t>(A->workspace) & 255))
+        return fail(MOE_ERR_INVALID, "hidden and out must be 16-byte aligned, workspace 256-byte aligned");
+    const size_t need = moe_alpha_workspace_bytes(A->M, A->H, A->I, A->E, A->top_k);
+    if (A->workspace_bytes < need)
+        return fail(MOE_ERR_INVALID, "workspace too small: %zu < %zu bytes", (size_t)A->workspace_bytes, need);
+    if (A->M == 0) return MOE_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    AlphaWorkspace w = carve_alpha(A->workspace, A->M, A->H, A->I, A->E, A->top_k);
+    const int n_pairs = A->M * A->top_k;
+    const size_t hist_bytes = (size_t)32 * A->E * 4;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+        CUDA_TRY(cudaFuncSetAttribute(alpha_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * gg::MAX_MASKED_GROUPS * 4));
+        attr_set[dev] = true;
+    }
+    alpha_plan_kernel<<<1, ALPHA_PLAN_THREADS, hist_bytes, st>>>(A->topk_ids, n_pairs, A->E, (int)w.max_m, w.counts, w.rowpos,
+                                                               status_ptr());
+    CUDA_TRY(cudaGetLastError());
+    const int wpb = 8;
+    const int route_blocks = (n_pairs + wpb - 1) / wpb;
+    alpha_quant_scatter_kernel<<<route_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs,
+                                                                  A->top_k, A->H, w.rows_total, w.a1, w.s1);
+    CUDA_TRY(cudaGetLastError());
+    moe_gg_args g1 = {};
+    g1.a = w.a1; g1.b = A->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = w.rows_total;
+    g1.sfb = A->w13_scale; g1.layout = w.counts; g1.d = w.g1; g1.ldd = 2 * (int64_t)A->I;
+    g1.G = A->E; g1.M = (int32_t)w.max_m; g1.N = 2 * A->I; g1.K = A->H; g1.d_dtype = MOE_DTYPE_F32;
+    rc = moe_gg_fp8_masked(&g1, stream);
+    if (rc != MOE_OK) return rc;
+    alpha_silu_requant_kernel<<<route_blocks, wpb * 32, 0, st>>>(w.g1, w.rowpos, n_pairs, A->I, 1, w.rows_total, w.a2, w.s2);
+    CUDA_TRY(cudaGetLastError());
+    moe_gg_args g2 = {};
+    g2.a = w.a2; g2.b = A->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = w.rows_total;
+    g2.sfb = A->w2_scale; g2.layout = w.counts; g2.d = w.d2; g2.ldd = A->H;
+    g2.G = A->E; g2.M = (int32_t)w.max_m; g2.N = A->H; g2.K = A->I; g2.d_dtype = MOE_DTYPE_F32;
+    rc = moe_gg_fp8_masked(&g2, stream);
+    if (rc != MOE_OK) return rc;
+    alpha_combine_kernel<<<A->M, 256, 0, st>>>(w.d2, A->topk_ids, A->topk_weights, w.rowpos, A->routed_scaling_factor, A->top_k,
+                                               A->H, static_cast<__nv_bfloat16*>(A->out));
+    CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
 

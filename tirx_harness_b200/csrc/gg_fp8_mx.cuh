@@ -383,4 +383,259 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Single-CTA version of the same path: 128 x 256 tiles, cta_group::1, four 48 KB stages.  No cross-SM
+// signalling at all and only 128 rows per tile (half the wasted MMA work on ragged or masked groups).
+namespace mx1 {
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int STAGES = 4;
+constexpr int THREADS = 384;
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int B_STAGE_BYTES = BN * BK;
+constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+constexpr int SFQ_SLOTS = 4;
+constexpr int SFQ_SLOT_BYTES = 512 + 2 * 512;
+constexpr int OFF_SFQ = SMEM_TILE_BYTES;
+constexpr int OFF_BARS = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
+constexpr int OFF_PREFIX = OFF_BARS + 256;
+constexpr int SMEM_BYTES = OFF_PREFIX + (gg::MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
+}  // namespace mx1
+
+__device__ __forceinline__ void tma_load_1d(uint32_t smem_dst, const void* tmap, uint32_t bar, int32_t c0) {
+    asm volatile(
+        "cp.async.bulk.tensor.1d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3}], [%2];"
+        ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(c0)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+template <bool MASKED>
+__global__ void __launch_bounds__(mx1::THREADS, 1)
+gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                  const GGParams p, const int* __restrict__ flag, int quads, int* status) {
+    using namespace mx1;
+    if (*flag != 0) return;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+    uint8_t* smem_sfq = smem + OFF_SFQ;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t full_bar = smem_u32(bars);
+    const uint32_t empty_bar = smem_u32(bars + STAGES);
+    const uint32_t tfull_bar = smem_u32(bars + 2 * STAGES);
+    const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        mbar_init(tfull_bar, 1);
+        mbar_init(tempty_bar, 8);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_sfa);
+        tma_prefetch_desc(&tmap_sfb);
+    }
+    if (MASKED) {
+        if (warp == 3) {
+            int running = 0;
+            for (int base = 0; base < p.G; base += 32) {
+                int g = base + lane;
+                int mm = 0;
+                if (g < p.G) {
+                    mm = __ldg(p.layout + g);
+                    mm = mm < 0 ? 0 : (mm > p.M ? p.M : mm);
+                }
+                int blocks = (mm + BM - 1) / BM;
+                int incl = blocks;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                if (g < p.G) prefix[g] = running + incl - blocks;
+                running += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) prefix[p.G] = running;
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_base_slot), mx::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    const int KB = p.num_k_blocks;
+
+    if (warp < 4) {
+        setmaxnreg_dec<72>();
+        if (warp == 0) {
+            // ------------------------------------------------ TMA producer
+            Scheduler<MASKED> sched(p, prefix, lane);
+            Tile tile;
+            uint32_t stage = 0, phase = 0, qcount = 0;
+            bool ok = true;
+            while (ok && sched.next(tile)) {
+                const int b_row = tile.g * p.N + tile.n_blk * BN;
+                const int sfa_chunk = (tile.m0 >> 7) * quads;
+                const int sfb_chunk = (tile.g * p.nb128 + tile.n_blk * 2) * quads;
+                const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status, STATUS_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t fb = full_bar + 8 * stage;
+                        const bool with_sf = (kb & 3) == 0;
+                        mbar_arrive_expect_tx(fb, A_STAGE_BYTES + B_STAGE_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0));
+                        tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tile.m0);
+                        tma_load_2d(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
+                        if (with_sf) {
+                            const int q = kb >> 2;
+                            const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
+                            tma_load_1d(dst, &tmap_sfa, fb, (sfa_chunk + q) * 128);
+                            tma_load_1d(dst + 512, &tmap_sfb, fb, (sfb_chunk + q) * 128);
+                            tma_load_1d(dst + 1024, &tmap_sfb, fb, (sfb_chunk + (second_nb ? quads : 0) + q) * 128);
+                        }
+                    }
+                    __syncwarp();
+                    if ((kb & 3) == 0) ++qcount;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------ MMA issuer (lane 0 runs the K loop alone)
+            Scheduler<MASKED> sched(p, prefix, lane);
+            Tile tile;
+            uint32_t stage = 0, phase = 0, tile_phase = 0, qcount = 0;
+            bool ok = true;
+            const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem_a));
+            const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
+            const uint32_t idesc0 = make_idesc_mxf8(BM, BN, 0);
+            while (ok && sched.next(tile)) {
+                if (lane == 0) {
+                    ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                    for (int kb = 0; ok && kb < KB; ++kb) {
+                        ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t sub = kb & 3;
+                        if (sub == 0) {
+                            const uint32_t src = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
+                            const uint32_t tsf = tmem_base + mx::TMEM_SF_BASE + (qcount & 1) * mx::TMEM_SF_STRIDE;
+                            tmem_cp_sf(tsf, make_sf_desc(src));
+                            tmem_cp_sf(tsf + 4, make_sf_desc(src + 512));
+                            tmem_cp_sf(tsf + 8, make_sf_desc(src + 1024));
+                            ++qcount;
+                        }
+                        const uint32_t tsfa = tmem_base + mx::TMEM_SF_BASE + ((qcount - 1) & 1) * mx::TMEM_SF_STRIDE;
+                        const uint32_t tsfb = tsfa + 4;
+                        const uint32_t idesc = idesc0 | (sub << 4) | (sub << 29);
+                        const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
+                        const uint64_t bdesc = bdesc0 + stage * (B_STAGE_BYTES >> 4);
+                        umma_mxf8(tmem_base, adesc, bdesc, idesc, tsfa, tsfb, kb > 0 ? 1u : 0u);
+                        umma_mxf8(tmem_base, adesc + 2, bdesc + 2, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8(tmem_base, adesc + 4, bdesc + 4, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8(tmem_base, adesc + 6, bdesc + 6, idesc, tsfa, tsfb, 1u);
+                        umma_commit(empty_bar + 8 * stage);
+                        if (kb == KB - 1) umma_commit(tfull_bar);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    }
+                    tile_phase ^= 1;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                stage = __shfl_sync(0xffffffffu, stage, 0);
+                phase = __shfl_sync(0xffffffffu, phase, 0);
+                tile_phase = __shfl_sync(0xffffffffu, tile_phase, 0);
+                qcount = __shfl_sync(0xffffffffu, qcount, 0);
+            }
+        }
+    } else {
+        // ---------------------------------------------------- epilogue: one drain per tile
+        setmaxnreg_inc<208>();
+        const int ew = warp - 4;
+        const int quarter = warp & 3;
+        const int half = ew >> 2;
+        const int row_in_tile = quarter * 32 + lane;
+        Scheduler<MASKED> sched(p, prefix, lane);
+        Tile tile;
+        uint32_t tile_phase = 0;
+        bool ok = true;
+        while (ok && sched.next(tile)) {
+            const int n0 = tile.n_blk * BN + half * 128;
+            const int row = tile.m0 + row_in_tile;
+            bool row_valid;
+            if (MASKED) row_valid = row_in_tile < tile.rows;
+            else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
+            ok = mbar_wait_warp(tfull_bar, tile_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+            if (!ok) break;
+            tile_phase ^= 1;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + half * 128;
+            uint32_t v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_wait(v[c]);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar);
+            if (row_valid && p.d_f32) {
+                float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 4) {
+                    if (n0 + j + 4 <= p.N)
+                        *reinterpret_cast<float4*>(drow + j) =
+                            make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
+                                        __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
+                }
+            } else if (row_valid) {
+                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 8) {
+                    if (n0 + j + 8 <= p.N) {
+                        uint4 out;
+                        const uint32_t* s = &v[j / 32][j % 32];
+                        out.x = cvt_bf16x2(pack_f32x2(__uint_as_float(s[0]), __uint_as_float(s[1])));
+                        out.y = cvt_bf16x2(pack_f32x2(__uint_as_float(s[2]), __uint_as_float(s[3])));
+                        out.z = cvt_bf16x2(pack_f32x2(__uint_as_float(s[4]), __uint_as_float(s[5])));
+                        out.w = cvt_bf16x2(pack_f32x2(__uint_as_float(s[6]), __uint_as_float(s[7])));
+                        *reinterpret_cast<uint4*>(drow + j) = out;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, mx::TMEM_COLS);
+    }
+}
+
 }  // namespace b200
