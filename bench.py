@@ -352,6 +352,94 @@ def run_layer(args, world, rank, device, barrier, steps, warmup):
     return res
 
 
+ALPHA_ROWS = (1, 8, 16, 32, 64, 128)
+ALPHA = dict(H=2048, I=128, E=512, top_k=10,
+             desc="decode-regime MoE layer from bf16 activations and preselected routes (alphamoe contract): "
+                  "K=2048, I=128, E=512, top-10, rows M in {1,8,16,32,64,128}")
+
+
+def run_alpha(args, device):
+    """Times the decode-regime layer on the six official row sizes of the alphamoe contract.  Per row: L2 is
+    flushed (a 256 MB memset) before every timed call, each call is bracketed by its own CUDA events, the
+    median is reported; the same with the call captured into a CUDA graph (how that task's baseline is timed).
+    Roofline: the weights of the distinct experts touched must come from HBM once."""
+    import torch
+    from tirx_harness_b200 import alpha_moe
+    from tirx_harness_b200 import grouped_gemm as gg
+    cfg = ALPHA
+    H, I, E, k = cfg["H"], cfg["I"], cfg["E"], cfg["top_k"]
+    gen = torch.Generator(device=device).manual_seed(42)
+
+    def qweights(rows, cols):          # e4m3 bytes + 128x128 scales of N(0, 0.125) weights, made on the device
+        w = torch.randn((E, rows, cols), device=device, generator=gen) * 0.125
+        blocks = w.view(E, rows // 128, 128, cols // 128, 128)
+        sc = blocks.abs().amax(dim=(2, 4)).clamp_min(1e-8) / 448.0
+        q = (blocks / sc[:, :, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(E, rows, cols)
+        return q, sc.float().contiguous()
+    w13, s13 = qweights(2 * I, H)
+    w2, s2 = qweights(H, I)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    peaks = _peaks()
+    iters = max(10, min(args.steps, 50))
+    rows = []
+    with ClockSampler(device.index) as clocks:
+        for M in ALPHA_ROWS:
+            hs = (torch.randn((M, H), device=device, generator=gen) * 0.25).bfloat16()
+            scores = torch.randn((M, E), device=device, generator=gen)
+            ids = torch.topk(scores, k, dim=-1).indices.to(torch.int32).contiguous()
+            wts = torch.softmax(torch.randn((M, k), device=device, generator=gen), dim=-1).contiguous()
+            data = dict(hidden_states=hs, topk_ids=ids, topk_weights=wts, gemm1_weights=w13, gemm1_weights_scale=s13,
+                        gemm2_weights=w2, gemm2_weights_scale=s2, top_k=k, routed_scaling_factor=1.0,
+                        output=torch.zeros((M, H), dtype=torch.bfloat16, device=device))
+            op = alpha_moe.setup(data, M)
+            for _ in range(max(args.warmup, 3)):
+                op()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(device=device)
+            with torch.cuda.stream(side):
+                op()
+                with torch.cuda.graph(graph, stream=side):
+                    op()
+            torch.cuda.synchronize()
+
+            def timed(fn):
+                ts = []
+                for _ in range(iters):
+                    flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn()
+                    e1.record()
+                    e1.synchronize()
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+                ts.sort()
+                return ts[len(ts) // 2]
+            us = timed(op)
+            us_graph = timed(graph.replay)
+            distinct = int(torch.unique(ids).numel())
+            alg = distinct * (2 * I * H + H * I + (2 * I // 128) * (H // 128) * 4 + (H // 128) * (I // 128) * 4) + 2 * M * H * 2
+            rows.append({"M": M, "us": round(us, 2), "us_cuda_graph": round(us_graph, 2), "experts_touched": distinct,
+                         "algorithmic_bytes": alg, "hbm_frac_graph": round(alg / (us_graph * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)})
+            del op, graph
+    status = gg.device_status(device)
+    total_graph = sum(r["us_cuda_graph"] for r in rows)
+    big = rows[-1]
+    return {
+        "metric": "alphamoe_sum_latency_us", "value": total_graph, "unit": "us (sum over the six rows, CUDA-graph replay)",
+        "n_gpus": 1, "steps": iters, "warmup": max(args.warmup, 3), "ms_per_step": total_graph * 1e-3,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": cfg["desc"], "inputs": "N(0,0.25) bf16 tokens, N(0,0.125) weights quantised per 128x128, "
+                   "top-10 of random scores, softmax weights (the task generator's distributions)",
+                   "l2": "256 MB memset before every timed call", "timing": "CUDA events around each call, median"},
+        "clocks": clocks.summary(), "e2e": None, "gpu_launches": iters * 2 * 6 * len(rows), "rows": rows,
+        "roofline": {"bound": "hbm", "achieved": big["algorithmic_bytes"] / (big["us_cuda_graph"] * 1e-6) / 1e9,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": big["hbm_frac_graph"], "traffic": None,
+                     "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']}); row M=128"},
+        "device_status": status,
+    }
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -373,6 +461,11 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.workload == "alpha":
+        if world > 1:
+            raise SystemExit("the alpha workload is a single-GPU latency measurement")
+        print(json.dumps(run_alpha(args, device)), flush=True)
+        return
     if args.workload == "layer":
         res = run_layer(args, world, rank, device, barrier, args.steps, args.warmup)
         if rank == 0:
@@ -501,7 +594,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["layer"], default="gemm")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["layer", "alpha"], default="gemm")
     ap.add_argument("--no-layer", dest="with_layer", action="store_false",
                     help="skip the expert-parallel MoE layer measurement that follows the grouped-GEMM one "
                          "(it is reported as the extra object `moe_layer` of the same JSON line)")
