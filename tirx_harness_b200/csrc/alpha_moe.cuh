@@ -71,35 +71,24 @@ alpha_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int max_m, in
     }
 }
 
-// One warp per route.  x bf16 [M, H]; q e4m3 [rows_total, H]; scales MN-major: scale of (row, block b) at
-// s[b * rows_total + row].
+// One warp per (route, 128-block).  x bf16 [M, H]; q e4m3 [rows_total, H]; scales MN-major: scale of
+// (row, block b) at s[b * rows_total + row].
 __global__ void alpha_quant_scatter_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rowpos,
                                            int n_pairs, int top_k, int H, long long rows_total,
                                            uint8_t* __restrict__ q, float* __restrict__ s) {
-    const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int nb = H >> 7;
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    if (p >= n_pairs) return;
+    if (w >= n_pairs * nb) return;
+    const int p = w / nb, b = w - p * nb;
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (long long)(p / top_k) * H + b * 128 + lane * 4));
     const int row = __ldg(rowpos + p);
     if (row < 0) return;
-    const __nv_bfloat16* src = x + (long long)(p / top_k) * H + lane * 4;
-    uint8_t* dst = q + (long long)row * H + lane * 4;
-    const int nb = H >> 7;
-    for (int b0 = 0; b0 < nb; b0 += 4) {
-        uint2 raw[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            if (b0 + i < nb) raw[i] = __ldg(reinterpret_cast<const uint2*>(src + (b0 + i) * 128));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (b0 + i < nb) {
-                float v[4], sc;
-                bf16x4_to_float(raw[i], v);
-                const uint32_t packed = quant_block_4(v, &sc);
-                *reinterpret_cast<uint32_t*>(dst + (b0 + i) * 128) = packed;
-                if (lane == 0) s[(long long)(b0 + i) * rows_total + row] = sc;
-            }
-        }
-    }
+    float v[4], sc;
+    bf16x4_to_float(raw, v);
+    const uint32_t packed = quant_block_4(v, &sc);
+    *reinterpret_cast<uint32_t*>(q + (long long)row * H + b * 128 + lane * 4) = packed;
+    if (lane == 0) s[(long long)b * rows_total + row] = sc;
 }
 
 // One warp per route.  gu fp32 [rows_total, 2I] with gate = columns [0, I) when gate_first, else [I, 2I).
@@ -139,37 +128,45 @@ __global__ void alpha_combine_kernel(const float* __restrict__ d, const int* __r
     __shared__ float s_scale[32];
     __shared__ int s_n;
     const int t = blockIdx.x;
-    if (threadIdx.x == 0) {
-        int key[32], idx[32], n = 0;
-        for (int j = 0; j < top_k; ++j) {
-            if (__ldg(rowpos + t * top_k + j) < 0) continue;
-            const int e = __ldg(ids + t * top_k + j);
-            int k = n++;
-            while (k > 0 && key[k - 1] > e) {      // stable insertion sort, at most 32 entries
-                key[k] = key[k - 1];
-                idx[k] = idx[k - 1];
-                --k;
-            }
-            key[k] = e;
-            idx[k] = j;
+    if (threadIdx.x < 32) {
+        // lane j owns route j: its place in the order is the number of live routes with a smaller (expert, j)
+        const int j = threadIdx.x;
+        const bool have = j < top_k;
+        const int rp = have ? __ldg(rowpos + t * top_k + j) : -1;
+        const int e = have ? __ldg(ids + t * top_k + j) : 0;
+        const float wt = have ? __ldg(w + t * top_k + j) : 0.0f;
+        const bool live = rp >= 0;
+        const unsigned live_mask = __ballot_sync(0xffffffffu, live);
+        int rank = 0;
+        for (int o = 0; o < top_k; ++o) {
+            const int eo = __shfl_sync(0xffffffffu, e, o);
+            if (((live_mask >> o) & 1u) && (eo < e || (eo == e && o < j))) ++rank;
         }
-        for (int k = 0; k < n; ++k) {
-            s_row[k] = __ldg(rowpos + t * top_k + idx[k]);
-            s_scale[k] = __fmul_rn(__ldg(w + t * top_k + idx[k]), rsf);
+        if (live) {
+            s_row[rank] = rp;
+            s_scale[rank] = __fmul_rn(wt, rsf);
         }
-        s_n = n;
+        if (j == 0) s_n = __popc(live_mask);
     }
     __syncthreads();
     const int n = s_n;
     for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        for (int k = 0; k < n; ++k) {
-            const float4 v = __ldcs(reinterpret_cast<const float4*>(d + (long long)s_row[k] * H + c));
-            const float sc = s_scale[k];
-            a0 = round_bf16(a0 + round_bf16(__fmul_rn(v.x, sc)));
-            a1 = round_bf16(a1 + round_bf16(__fmul_rn(v.y, sc)));
-            a2 = round_bf16(a2 + round_bf16(__fmul_rn(v.z, sc)));
-            a3 = round_bf16(a3 + round_bf16(__fmul_rn(v.w, sc)));
+        for (int k0 = 0; k0 < n; k0 += 8) {
+            float4 v[8];                     // eight routes' loads in flight before the (ordered) bf16 chain
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (k0 + i < n) v[i] = __ldcs(reinterpret_cast<const float4*>(d + (long long)s_row[k0 + i] * H + c));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (k0 + i < n) {
+                    const float sc = s_scale[k0 + i];
+                    a0 = round_bf16(a0 + round_bf16(__fmul_rn(v[i].x, sc)));
+                    a1 = round_bf16(a1 + round_bf16(__fmul_rn(v[i].y, sc)));
+                    a2 = round_bf16(a2 + round_bf16(__fmul_rn(v[i].z, sc)));
+                    a3 = round_bf16(a3 + round_bf16(__fmul_rn(v[i].w, sc)));
+                }
+            }
         }
         __nv_bfloat162 lo = __floats2bfloat162_rn(a0, a1), hi = __floats2bfloat162_rn(a2, a3);
         uint2 o;

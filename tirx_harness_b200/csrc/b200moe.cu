@@ -129,7 +129,7 @@ int device_info(DeviceInfo** out) {
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      gg::SMEM_BYTES));
+                                      gg::SMEM_BYTES_MASKED));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -323,13 +323,18 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         if (p.scatter_meta != nullptr) {
             if (a->N % 128 != 0) return fail(MOE_ERR_INVALID, "scattered output needs N %% 128 == 0");
             gg_fp8_kernel<false, false, true><<<grid, gg::THREADS, gg::SMEM_BYTES_SCATTER, static_cast<cudaStream_t>(stream)>>>(
-                tmap_a, tmap_b, p, status_ptr());
+                tmap_a, tmap_b, tmap_a, p, status_ptr());
             CUDA_TRY(cudaGetLastError());
             return MOE_OK;
         }
     }
-    gg_fp8_kernel<MASKED><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-        tmap_a, tmap_b, p, status_ptr());
+    CUtensorMap tmap_a_small = tmap_a;
+    if (MASKED) {
+        rc = encode_fp8_kmajor(&tmap_a_small, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::SMALL_A_ROWS, (uint64_t)a->lda);
+        if (rc != MOE_OK) return rc;
+    }
+    gg_fp8_kernel<MASKED><<<grid, gg::THREADS, MASKED ? gg::SMEM_BYTES_MASKED : gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        tmap_a, tmap_b, tmap_a_small, p, status_ptr());
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
@@ -429,7 +434,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     int grid = (int)(max_tiles < di->num_sms ? max_tiles : di->num_sms);
     if (grid < 1) grid = 1;
     gg_fp8_kernel<false, true><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-        tmap_a, tmap_b, p, status_ptr());
+        tmap_a, tmap_b, tmap_a, p, status_ptr());
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
@@ -747,7 +752,8 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     CUDA_TRY(cudaGetLastError());
     const int wpb = 8;
     const int route_blocks = (n_pairs + wpb - 1) / wpb;
-    alpha_quant_scatter_kernel<<<route_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs,
+    const int quant_blocks = (n_pairs * (A->H / 128) + wpb - 1) / wpb;
+    alpha_quant_scatter_kernel<<<quant_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs,
                                                                   A->top_k, A->H, w.rows_total, w.a1, w.s1);
     CUDA_TRY(cudaGetLastError());
     moe_gg_args g1 = {};
@@ -764,7 +770,7 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     g2.G = A->E; g2.M = (int32_t)w.max_m; g2.N = A->H; g2.K = A->I; g2.d_dtype = MOE_DTYPE_F32;
     rc = moe_gg_fp8_masked(&g2, stream);
     if (rc != MOE_OK) return rc;
-    alpha_combine_kernel<<<A->M, 256, 0, st>>>(w.d2, A->topk_ids, A->topk_weights, w.rowpos, A->routed_scaling_factor, A->top_k,
+    alpha_combine_kernel<<<A->M, (A->H >= 2048 ? 512 : 256), 0, st>>>(w.d2, A->topk_ids, A->topk_weights, w.rowpos, A->routed_scaling_factor, A->top_k,
                                                A->H, static_cast<__nv_bfloat16*>(A->out));
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;

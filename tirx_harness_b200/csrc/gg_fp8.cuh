@@ -44,6 +44,7 @@ constexpr int A_STAGE_BYTES = BM * BK;             // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK;             // 32 KB
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_MASKED_GROUPS = 1024;
+constexpr int SMALL_A_ROWS = 16;                   // masked layout: A box for tiles with at most this many valid rows
 constexpr int SCATTER_STAGES = 3;                  // scattered-output variant: one stage fewer ...
 constexpr int STAGING_ROW_BYTES = 528;             // ... and 128 staging rows of 512 B + 16 B pad (bank-conflict free)
 constexpr int STAGING_BYTES = 128 * STAGING_ROW_BYTES;
@@ -56,6 +57,11 @@ constexpr int OFF_AMAX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;     // fused ac
 constexpr int OFF_PREFIX = OFF_AMAX + 2 * 2 * 128 * 4;
 // + masked-layout prefix table + slack for 1024-byte alignment
 constexpr int SMEM_BYTES = OFF_PREFIX + (MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
+// masked layout: after prefix[G+1] come the clamped masked_m[G] and a direct (group, row block) table of the
+// first MASKED_LIST_CAP row blocks, so that the per-tile schedule lookup is one shared-memory load
+constexpr int MASKED_LIST_CAP = 2048;
+constexpr int MASKED_TABLE_INTS = (MAX_MASKED_GROUPS + 1) + MAX_MASKED_GROUPS + MASKED_LIST_CAP;
+constexpr int SMEM_BYTES_MASKED = OFF_PREFIX + MASKED_TABLE_INTS * 4 + 12 + 1024;
 constexpr int SMEM_BYTES_SCATTER = SMEM_BYTES - (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES;
 }  // namespace gg
 
@@ -92,6 +98,42 @@ struct Tile {
     int g;           // group
     int rows;        // masked: number of valid rows in this tile (<= BM); contiguous: BM
 };
+
+// Masked layout tables in shared memory (all threads of the CTA call this before the first __syncthreads that
+// precedes any Scheduler use): tables[0..G] = prefix of 128-row blocks, then masked_m clamped to [0, M], then
+// the (group << 16 | row block) of each of the first MASKED_LIST_CAP row blocks.  The masked_m loads are
+// issued by all threads at once: one global round trip instead of one per 32 groups.
+__device__ __forceinline__ void build_masked_tables(const GGParams& p, int* tables, int scan_warp) {
+    int* prefix = tables;
+    int* mm_s = tables + gg::MAX_MASKED_GROUPS + 1;
+    int* list = mm_s + gg::MAX_MASKED_GROUPS;
+    for (int g = threadIdx.x; g < p.G; g += blockDim.x) {
+        int mm = __ldg(p.layout + g);
+        mm_s[g] = mm < 0 ? 0 : (mm > p.M ? p.M : mm);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == scan_warp) {
+        int running = 0;
+        for (int base = 0; base < p.G; base += 32) {
+            const int g = base + lane;
+            const int blocks = g < p.G ? (mm_s[g] + gg::BM - 1) / gg::BM : 0;
+            int incl = blocks;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int first = running + incl - blocks;
+            if (g < p.G) {
+                prefix[g] = first;
+                for (int mb = 0; mb < blocks && first + mb < gg::MASKED_LIST_CAP; ++mb) list[first + mb] = (g << 16) | mb;
+            }
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) prefix[p.G] = running;
+    }
+}
 
 // Static persistent schedule.  All warps of a CTA walk the same sequence.
 //  contiguous: tile index t -> (128-row block, column block); a row block is visited once per
@@ -146,18 +188,26 @@ struct Scheduler {
     __device__ __forceinline__ bool next(Tile& tile) {
         if (MASKED) {
             if (t >= total) return false;
-            int mbg = t / p.num_n_blocks;
-            int lo = 0, hi = p.G;            // find g with prefix[g] <= mbg < prefix[g+1]
-            while (hi - lo > 1) {
-                int mid = (lo + hi) >> 1;
-                if (prefix[mid] <= mbg) lo = mid; else hi = mid;
+            const int mbg = t / p.num_n_blocks;
+            const int* mm_s = prefix + gg::MAX_MASKED_GROUPS + 1;
+            int lo, mb;
+            if (mbg < gg::MASKED_LIST_CAP) {
+                const int e = mm_s[gg::MAX_MASKED_GROUPS + mbg];
+                lo = e >> 16;
+                mb = e & 0xFFFF;
+            } else {
+                lo = 0;
+                int hi = p.G;                // find g with prefix[g] <= mbg < prefix[g+1]
+                while (hi - lo > 1) {
+                    int mid = (lo + hi) >> 1;
+                    if (prefix[mid] <= mbg) lo = mid; else hi = mid;
+                }
+                mb = mbg - prefix[lo];
             }
-            int mb = mbg - prefix[lo];
             tile.g = lo;
             tile.n_blk = t % p.num_n_blocks;
             tile.m0 = lo * p.M + mb * gg::BM;
-            int left = __ldg(p.layout + lo) - mb * gg::BM;
-            if (left > p.M - mb * gg::BM) left = p.M - mb * gg::BM;
+            const int left = mm_s[lo] - mb * gg::BM;
             tile.rows = left < gg::BM ? left : gg::BM;
             t += gridDim.x;
             return true;
@@ -190,7 +240,7 @@ struct Scheduler {
 template <bool MASKED, bool FUSE_ACT = false, bool SCATTER = false>
 __global__ void __launch_bounds__(gg::THREADS, 1)
 gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-              const GGParams p, int* status) {
+              const __grid_constant__ CUtensorMap tmap_a_small, const GGParams p, int* status) {
     static_assert(!(MASKED && FUSE_ACT), "the fused activation epilogue exists for the contiguous layout only");
     static_assert(!(SCATTER && (MASKED || FUSE_ACT)), "scattered output exists for the plain contiguous GEMM only");
     using namespace gg;
@@ -247,30 +297,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
     }
-    if (MASKED) {
-        // prefix[g] = number of 128-row blocks of groups < g  (G <= MAX_MASKED_GROUPS)
-        if (warp == 3) {
-            int running = 0;
-            for (int base = 0; base < p.G; base += 32) {
-                int g = base + lane;
-                int mm = 0;
-                if (g < p.G) {
-                    mm = __ldg(p.layout + g);
-                    mm = mm < 0 ? 0 : (mm > p.M ? p.M : mm);
-                }
-                int blocks = (mm + BM - 1) / BM;
-                int incl = blocks;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    int v = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += v;
-                }
-                if (g < p.G) prefix[g] = running + incl - blocks;
-                running += __shfl_sync(0xffffffffu, incl, 31);
-            }
-            if (lane == 0) prefix[p.G] = running;
-        }
-    }
+    if (MASKED) build_masked_tables(p, prefix, 3);
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_base_slot), TMEM_COLS);
         tmem_relinquish();
@@ -299,8 +326,12 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     if (!ok) break;
                     if (lane == 0) {
                         const uint32_t fb = full_bar + 8 * stage;
-                        mbar_arrive_expect_tx(fb, A_STAGE_BYTES + B_STAGE_BYTES);
-                        tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tile.m0);
+                        // masked tiles with few valid rows (decode) fetch a SMALL_A_ROWS-row box of A only: the
+                        // other rows of the stage keep stale bytes whose products land in rows nobody stores
+                        const bool small_a = MASKED && tile.rows <= gg::SMALL_A_ROWS;
+                        mbar_arrive_expect_tx(fb, (small_a ? gg::SMALL_A_ROWS * BK : A_STAGE_BYTES) + B_STAGE_BYTES);
+                        tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), small_a ? &tmap_a_small : &tmap_a, fb, kb * BK,
+                                    tile.m0);
                         if (FUSE_ACT) {
                             // tmap_b has a 64-row box here: [up 64 | gate 64] for each warpgroup
                             const int up0 = tile.g * p.N + (p.gate_first ? p.inter : 0) + tile.n_blk * 128;
@@ -382,33 +413,21 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     nb = tile.n_blk + ((((lane & 1) != 0) != (p.gate_first != 0)) ? (p.inter >> 7) : 0);
                 if (nb >= p.nb128) nb = p.nb128 - 1;
                 const float* bp = p.sfb + ((long long)tile.g * p.nb128 + nb) * KB;
-                for (int kb0 = 0; kb0 < KB && ok; kb0 += 4) {
-                    float v[4][4], b[4];
+                // asynchronous 4-byte copies straight into the ring slot; the slot's `full` barrier gets one
+                // deferred arrival per lane.  Up to SF_SLOTS K blocks are in flight, across tile borders, so
+                // short-K tiles (one K block each) do not expose a global-load latency per tile.
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(sfempty_bar + 8 * slot, sphase ^ 1, abort_flag, status, STATUS_TIMEOUT_SF_EMPTY);
+                    if (!ok) break;
+                    const uint32_t dst = smem_u32(sf_ring + slot * SF_SLOT_FLOATS);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (kb0 + u < KB) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) v[u][j] = __ldg(rp[j] + (long long)(kb0 + u) * p.sfa_sk);
-                            b[u] = __ldg(bp + kb0 + u);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (ok && kb0 + u < KB) {
-                            ok = mbar_wait_warp(sfempty_bar + 8 * slot, sphase ^ 1, abort_flag, status,
-                                                STATUS_TIMEOUT_SF_EMPTY);
-                            if (ok) {
-                                float* dst = sf_ring + slot * SF_SLOT_FLOATS;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = v[u][j];
-                                if (lane < 2) dst[128 + lane] = b[u];
-                                mbar_arrive(sffull_bar + 8 * slot);
-                                if (++slot == SF_SLOTS) { slot = 0; sphase ^= 1; }
-                            }
-                        }
-                    }
+                    for (int j = 0; j < 4; ++j) cp_async_4(dst + (lane + 32 * j) * 4, rp[j] + (long long)kb * p.sfa_sk);
+                    if (lane < 2) cp_async_4(dst + (128 + lane) * 4, bp + kb);
+                    cp_async_mbar_arrive_noinc(sffull_bar + 8 * slot);
+                    if (++slot == SF_SLOTS) { slot = 0; sphase ^= 1; }
                 }
             }
+            cp_async_wait_all();      // nothing may still be writing this CTA's shared memory at exit
         }
     } else {
         // ---------------------------------------------------- promotion + epilogue

@@ -398,7 +398,7 @@ constexpr int SFQ_SLOT_BYTES = 512 + 2 * 512;
 constexpr int OFF_SFQ = SMEM_TILE_BYTES;
 constexpr int OFF_BARS = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
 constexpr int OFF_PREFIX = OFF_BARS + 256;
-constexpr int SMEM_BYTES = OFF_PREFIX + (gg::MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
+constexpr int SMEM_BYTES = OFF_PREFIX + gg::MASKED_TABLE_INTS * 4 + 12 + 1024;
 }  // namespace mx1
 
 __device__ __forceinline__ void tma_load_1d(uint32_t smem_dst, const void* tmap, uint32_t bar, int32_t c0) {
@@ -458,29 +458,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tma_prefetch_desc(&tmap_sfa);
         tma_prefetch_desc(&tmap_sfb);
     }
-    if (MASKED) {
-        if (warp == 3) {
-            int running = 0;
-            for (int base = 0; base < p.G; base += 32) {
-                int g = base + lane;
-                int mm = 0;
-                if (g < p.G) {
-                    mm = __ldg(p.layout + g);
-                    mm = mm < 0 ? 0 : (mm > p.M ? p.M : mm);
-                }
-                int blocks = (mm + BM - 1) / BM;
-                int incl = blocks;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    int v = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += v;
-                }
-                if (g < p.G) prefix[g] = running + incl - blocks;
-                running += __shfl_sync(0xffffffffu, incl, 31);
-            }
-            if (lane == 0) prefix[p.G] = running;
-        }
-    }
+    if (MASKED) build_masked_tables(p, prefix, 3);
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_base_slot), mx::TMEM_COLS);
         tmem_relinquish();

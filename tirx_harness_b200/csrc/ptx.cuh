@@ -90,6 +90,16 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, ok);
 }
 
+// ---- cp.async (LDGSTS): 4-byte global -> shared copies whose completion arrives on an mbarrier
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+// one arrival on `bar` once all earlier cp.async of this thread have landed (the barrier's count must include it)
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // Single-thread form of the bounded wait (no warp vote): used by the one thread that issues MMAs, where
 // every instruction between "operands ready" and "MMA issued" is on the critical path.
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag,
