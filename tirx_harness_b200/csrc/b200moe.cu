@@ -17,6 +17,7 @@
 #include "gg_fp8_mx.cuh"
 #include "moe_ops.cuh"
 #include "alpha_moe.cuh"
+#include "alpha_gemm.cuh"
 
 namespace {
 
@@ -439,6 +440,9 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     return MOE_OK;
 }
 
+constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
+constexpr bool ALPHA_SWAP_DOWN_DEFAULT = true;
+
 struct AlphaWorkspace {
     int32_t *counts, *rowpos;
     float *s1, *s2, *g1, *d2;
@@ -756,20 +760,72 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     alpha_quant_scatter_kernel<<<quant_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs,
                                                                   A->top_k, A->H, w.rows_total, w.a1, w.s1);
     CUDA_TRY(cudaGetLastError());
-    moe_gg_args g1 = {};
-    g1.a = w.a1; g1.b = A->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = w.rows_total;
-    g1.sfb = A->w13_scale; g1.layout = w.counts; g1.d = w.g1; g1.ldd = 2 * (int64_t)A->I;
-    g1.G = A->E; g1.M = (int32_t)w.max_m; g1.N = 2 * A->I; g1.K = A->H; g1.d_dtype = MOE_DTYPE_F32;
-    rc = moe_gg_fp8_masked(&g1, stream);
+    // The two projections run either as swapped-operand decode kernels (weights = MMA rows, 32 routed rows = MMA
+    // columns) or as row-major masked-layout grouped GEMMs (128 x 256 tiles); the intermediates have the same layout
+    // either way.  Developer switch B200MOE_ALPHA_PATH = swap | masked | mixed (masked gate_up, swapped down).
+    const char* env_path = getenv("B200MOE_ALPHA_PATH");
+    bool swap1 = ALPHA_SWAP_GATE_UP_DEFAULT, swap2 = ALPHA_SWAP_DOWN_DEFAULT;
+    if (env_path) {
+        swap1 = strcmp(env_path, "swap") == 0;
+        swap2 = strcmp(env_path, "swap") == 0 || strcmp(env_path, "mixed") == 0;
+    }
+    DeviceInfo* di = nullptr;
+    rc = device_info(&di);
     if (rc != MOE_OK) return rc;
-    alpha_silu_requant_kernel<<<route_blocks, wpb * 32, 0, st>>>(w.g1, w.rowpos, n_pairs, A->I, 1, w.rows_total, w.a2, w.s2);
-    CUDA_TRY(cudaGetLastError());
-    moe_gg_args g2 = {};
-    g2.a = w.a2; g2.b = A->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = w.rows_total;
-    g2.sfb = A->w2_scale; g2.layout = w.counts; g2.d = w.d2; g2.ldd = A->H;
-    g2.G = A->E; g2.M = (int32_t)w.max_m; g2.N = A->H; g2.K = A->I; g2.d_dtype = MOE_DTYPE_F32;
-    rc = moe_gg_fp8_masked(&g2, stream);
-    if (rc != MOE_OK) return rc;
+    static bool swap_attr_set[64] = {};
+    if (dev < 64 && !swap_attr_set[dev]) {
+        CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<1>::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<2>::SMEM_BYTES));
+        swap_attr_set[dev] = true;
+    }
+    // (expert, chunk) units: at most one per expert that has rows plus one per further 32 rows
+    const long long unit_bound = (n_pairs < A->E ? n_pairs : A->E) + n_pairs / asw::NT;
+    const char* env_trace = getenv("B200MOE_ALPHA_TRACE");      // developer aid: device address of int64 [2][148][8]
+    long long* trace = env_trace ? reinterpret_cast<long long*>(strtoull(env_trace, nullptr, 10)) : nullptr;
+    AlphaGemmParams gp{};
+    gp.counts = w.counts; gp.E = A->E; gp.max_m = (int)w.max_m; gp.rows_total = w.rows_total;
+    gp.a2 = w.a2; gp.s2 = w.s2; gp.g1 = w.g1; gp.d2 = w.d2; gp.H = A->H;
+    if (swap1) {
+        CUtensorMap tm_w13, tm_x1;
+        rc = encode_fp8_kmajor(&tm_w13, A->w13, (uint64_t)A->E * 2 * A->I, (uint64_t)A->H, 128);
+        if (rc != MOE_OK) return rc;
+        rc = encode_fp8_kmajor(&tm_x1, w.a1, (uint64_t)w.rows_total, (uint64_t)A->H, asw::NT);
+        if (rc != MOE_OK) return rc;
+        gp.trace = trace;
+        gp.s_rows = w.s1; gp.sfb = A->w13_scale; gp.KB = A->H / 128; gp.NF = 1;
+        int grid1 = (int)(unit_bound < di->num_sms ? unit_bound : di->num_sms);
+        alpha_swap_kernel<1><<<grid1, asw::Cfg<1>::THREADS, asw::Cfg<1>::SMEM_BYTES, st>>>(tm_w13, tm_x1, gp, status_ptr());
+        CUDA_TRY(cudaGetLastError());
+    } else {
+        moe_gg_args g1 = {};
+        g1.a = w.a1; g1.b = A->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = w.rows_total;
+        g1.sfb = A->w13_scale; g1.layout = w.counts; g1.d = w.g1; g1.ldd = 2 * (int64_t)A->I;
+        g1.G = A->E; g1.M = (int32_t)w.max_m; g1.N = 2 * A->I; g1.K = A->H; g1.d_dtype = MOE_DTYPE_F32;
+        rc = moe_gg_fp8_masked(&g1, stream);
+        if (rc != MOE_OK) return rc;
+        alpha_silu_requant_kernel<<<route_blocks, wpb * 32, 0, st>>>(w.g1, w.rowpos, n_pairs, A->I, 1, w.rows_total, w.a2, w.s2);
+        CUDA_TRY(cudaGetLastError());
+    }
+    if (swap2) {
+        CUtensorMap tm_w2, tm_x2;
+        rc = encode_fp8_kmajor(&tm_w2, A->w2, (uint64_t)A->E * A->H, (uint64_t)A->I, 128);
+        if (rc != MOE_OK) return rc;
+        rc = encode_fp8_kmajor(&tm_x2, w.a2, (uint64_t)w.rows_total, (uint64_t)A->I, asw::NT);
+        if (rc != MOE_OK) return rc;
+        gp.s_rows = w.s2; gp.sfb = A->w2_scale; gp.KB = 1; gp.NF = A->H / 128;
+        gp.trace = trace ? trace + 148 * 8 : nullptr;
+        const long long units2 = unit_bound * gp.NF;
+        int grid2 = (int)(units2 < di->num_sms ? units2 : di->num_sms);
+        alpha_swap_kernel<2><<<grid2, asw::Cfg<2>::THREADS, asw::Cfg<2>::SMEM_BYTES, st>>>(tm_w2, tm_x2, gp, status_ptr());
+        CUDA_TRY(cudaGetLastError());
+    } else {
+        moe_gg_args g2 = {};
+        g2.a = w.a2; g2.b = A->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = w.rows_total;
+        g2.sfb = A->w2_scale; g2.layout = w.counts; g2.d = w.d2; g2.ldd = A->H;
+        g2.G = A->E; g2.M = (int32_t)w.max_m; g2.N = A->H; g2.K = A->I; g2.d_dtype = MOE_DTYPE_F32;
+        rc = moe_gg_fp8_masked(&g2, stream);
+        if (rc != MOE_OK) return rc;
+    }
     alpha_combine_kernel<<<A->M, (A->H >= 2048 ? 512 : 256), 0, st>>>(w.d2, A->topk_ids, A->topk_weights, w.rowpos, A->routed_scaling_factor, A->top_k,
                                                A->H, static_cast<__nv_bfloat16*>(A->out));
     CUDA_TRY(cudaGetLastError());
