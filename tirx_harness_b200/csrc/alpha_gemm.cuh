@@ -274,11 +274,14 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         tma_prefetch_desc(&tmap_w);
         tma_prefetch_desc(&tmap_x);
     }
-    alpha_build_units(p, tables);
+    pdl_launch_dependents();
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_base_slot), TMEM_COLS);
         tmem_relinquish();
     }
+    // everything above overlaps the previous kernel of the stream; its outputs (counts, operands) are read below
+    pdl_wait();
+    alpha_build_units(p, tables);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

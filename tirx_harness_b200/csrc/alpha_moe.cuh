@@ -25,7 +25,9 @@ alpha_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int max_m, in
                   int* __restrict__ rowpos, int* status) {
     extern __shared__ int hist[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
     for (int i = threadIdx.x; i < 32 * E; i += ALPHA_PLAN_THREADS) hist[i] = 0;
+    pdl_wait();              // counts / rowpos may still be in use by the previous call's kernels
     __syncthreads();
     const int per = (((n_pairs + 31) / 32) + 31) & ~31;
     const int begin = warp * per;
@@ -79,6 +81,8 @@ __global__ void alpha_quant_scatter_kernel(const __nv_bfloat16* __restrict__ x, 
     const int nb = H >> 7;
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     if (w >= n_pairs * nb) return;
     const int p = w / nb, b = w - p * nb;
     const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (long long)(p / top_k) * H + b * 128 + lane * 4));
@@ -97,6 +101,8 @@ __global__ void alpha_silu_requant_kernel(const float* __restrict__ gu, const in
                                           float* __restrict__ s) {
     const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     if (p >= n_pairs) return;
     const int row = __ldg(rowpos + p);
     if (row < 0) return;
@@ -128,6 +134,8 @@ __global__ void alpha_combine_kernel(const float* __restrict__ d, const int* __r
     __shared__ float s_scale[32];
     __shared__ int s_n;
     const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (threadIdx.x < 32) {
         // lane j owns route j: its place in the order is the number of live routes with a smaller (expert, j)
         const int j = threadIdx.x;

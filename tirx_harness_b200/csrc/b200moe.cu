@@ -443,6 +443,21 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
 constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
 constexpr bool ALPHA_SWAP_DOWN_DEFAULT = true;
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream
+// still runs and orders itself with pdl_wait() (ptx.cuh).  B200MOE_PDL=0 falls back to plain launches.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    static const bool enabled = [] { const char* e = getenv("B200MOE_PDL"); return !(e && strcmp(e, "0") == 0); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 struct AlphaWorkspace {
     int32_t *counts, *rowpos;
     float *s1, *s2, *g1, *d2;
@@ -751,15 +766,13 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         CUDA_TRY(cudaFuncSetAttribute(alpha_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * gg::MAX_MASKED_GROUPS * 4));
         attr_set[dev] = true;
     }
-    alpha_plan_kernel<<<1, ALPHA_PLAN_THREADS, hist_bytes, st>>>(A->topk_ids, n_pairs, A->E, (int)w.max_m, w.counts, w.rowpos,
-                                                               status_ptr());
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_pdl(alpha_plan_kernel, dim3(1), dim3(ALPHA_PLAN_THREADS), hist_bytes, st, A->topk_ids, n_pairs, A->E,
+                        (int)w.max_m, w.counts, w.rowpos, status_ptr()));
     const int wpb = 8;
     const int route_blocks = (n_pairs + wpb - 1) / wpb;
     const int quant_blocks = (n_pairs * (A->H / 128) + wpb - 1) / wpb;
-    alpha_quant_scatter_kernel<<<quant_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs,
-                                                                  A->top_k, A->H, w.rows_total, w.a1, w.s1);
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_pdl(alpha_quant_scatter_kernel, dim3(quant_blocks), dim3(wpb * 32), 0, st,
+                        static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs, A->top_k, A->H, w.rows_total, w.a1, w.s1));
     // The two projections run either as swapped-operand decode kernels (weights = MMA rows, 32 routed rows = MMA
     // columns) or as row-major masked-layout grouped GEMMs (128 x 256 tiles); the intermediates have the same layout
     // either way.  Developer switch B200MOE_ALPHA_PATH = swap | masked | mixed (masked gate_up, swapped down).
@@ -794,8 +807,8 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         gp.trace = trace;
         gp.s_rows = w.s1; gp.sfb = A->w13_scale; gp.KB = A->H / 128; gp.NF = 1;
         int grid1 = (int)(unit_bound < di->num_sms ? unit_bound : di->num_sms);
-        alpha_swap_kernel<1><<<grid1, asw::Cfg<1>::THREADS, asw::Cfg<1>::SMEM_BYTES, st>>>(tm_w13, tm_x1, gp, status_ptr());
-        CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(launch_pdl(alpha_swap_kernel<1>, dim3(grid1), dim3(asw::Cfg<1>::THREADS), asw::Cfg<1>::SMEM_BYTES, st, tm_w13, tm_x1,
+                            gp, status_ptr()));
     } else {
         moe_gg_args g1 = {};
         g1.a = w.a1; g1.b = A->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = w.rows_total;
@@ -803,8 +816,8 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         g1.G = A->E; g1.M = (int32_t)w.max_m; g1.N = 2 * A->I; g1.K = A->H; g1.d_dtype = MOE_DTYPE_F32;
         rc = moe_gg_fp8_masked(&g1, stream);
         if (rc != MOE_OK) return rc;
-        alpha_silu_requant_kernel<<<route_blocks, wpb * 32, 0, st>>>(w.g1, w.rowpos, n_pairs, A->I, 1, w.rows_total, w.a2, w.s2);
-        CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(launch_pdl(alpha_silu_requant_kernel, dim3(route_blocks), dim3(wpb * 32), 0, st, (const float*)w.g1,
+                            (const int*)w.rowpos, n_pairs, A->I, 1, w.rows_total, w.a2, w.s2));
     }
     if (swap2) {
         CUtensorMap tm_w2, tm_x2;
@@ -816,8 +829,8 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         gp.trace = trace ? trace + 148 * 8 : nullptr;
         const long long units2 = unit_bound * gp.NF;
         int grid2 = (int)(units2 < di->num_sms ? units2 : di->num_sms);
-        alpha_swap_kernel<2><<<grid2, asw::Cfg<2>::THREADS, asw::Cfg<2>::SMEM_BYTES, st>>>(tm_w2, tm_x2, gp, status_ptr());
-        CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(launch_pdl(alpha_swap_kernel<2>, dim3(grid2), dim3(asw::Cfg<2>::THREADS), asw::Cfg<2>::SMEM_BYTES, st, tm_w2, tm_x2,
+                            gp, status_ptr()));
     } else {
         moe_gg_args g2 = {};
         g2.a = w.a2; g2.b = A->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = w.rows_total;
@@ -826,9 +839,9 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         rc = moe_gg_fp8_masked(&g2, stream);
         if (rc != MOE_OK) return rc;
     }
-    alpha_combine_kernel<<<A->M, (A->H >= 2048 ? 512 : 256), 0, st>>>(w.d2, A->topk_ids, A->topk_weights, w.rowpos, A->routed_scaling_factor, A->top_k,
-                                               A->H, static_cast<__nv_bfloat16*>(A->out));
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_pdl(alpha_combine_kernel, dim3(A->M), dim3(A->H >= 2048 ? 512 : 256), 0, st, (const float*)w.d2, A->topk_ids,
+                        A->topk_weights, (const int*)w.rowpos, A->routed_scaling_factor, A->top_k, A->H,
+                        static_cast<__nv_bfloat16*>(A->out)));
     return MOE_OK;
 }
 
