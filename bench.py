@@ -383,7 +383,7 @@ def run_alpha(args, device):
     iters = max(10, min(args.steps, 50))
     rows = []
     with ClockSampler(device.index) as clocks:
-        for M in ALPHA_ROWS:
+        for M in (args.alpha_rows or ALPHA_ROWS):
             hs = (torch.randn((M, H), device=device, generator=gen) * 0.25).bfloat16()
             scores = torch.randn((M, E), device=device, generator=gen)
             ids = torch.topk(scores, k, dim=-1).indices.to(torch.int32).contiguous()
@@ -602,6 +602,8 @@ def main():
     ap.add_argument("--combine", choices=["pull", "push"], default="push",
                     help="layer workload: how expert outputs travel back (see ep_layer.EpMoeLayer)")
     ap.add_argument("--layer-small", action="store_true", help="layer workload at 2048 tokens / 32 experts (profiling)")
+    ap.add_argument("--alpha-rows", type=int, nargs="*", default=None,
+                    help="alpha workload: row sizes to run instead of the six official ones (profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
