@@ -440,6 +440,64 @@ def run_alpha(args, device):
     }
 
 
+KGROUPED = dict(G=8, M=4096, N=7168, k=4096,
+                desc="k-grouped FP8 GEMM (weight-gradient layout), fp32 accumulation onto D: G=8 groups x 4096 K rows, "
+                     "M=4096, N=7168 (a [K_total,M], b [K_total,N] MN-major, packed UE8M0 scales per row and 128 K)")
+
+
+def run_kgrouped(args, device):
+    """d[g] += a[K rows of g].T @ b[K rows of g]: the transposing pre-pass plus one block-scaled launch per group."""
+    import torch
+    from tirx_harness_b200 import grouped_gemm as gg
+    cfg = KGROUPED
+    G, M, N, k = cfg["G"], cfg["M"], cfg["N"], cfg["k"]
+    K = G * k
+    gen = torch.Generator(device=device).manual_seed(0)
+
+    def fp8(rows, cols):          # random e4m3 bytes without the two NaN codes, magnitudes below 2
+        b = torch.randint(0, 256, (rows, cols), dtype=torch.uint8, device=device, generator=gen) & 0xBF
+        return b.view(torch.float8_e4m3fn)
+
+    def words(rows, cols):        # four UE8M0 exponents per word, 2^{-4..0}
+        e = torch.randint(123, 128, (rows, cols, 4), dtype=torch.int32, device=device, generator=gen)
+        return (e[..., 0] | (e[..., 1] << 8) | (e[..., 2] << 16) | (e[..., 3] << 24)).contiguous()
+    a, b = fp8(K, M), fp8(K, N)
+    srows = G * ((k + 511) // 512)
+    sfa, sfb = words(srows, M), words(srows, N)
+    d = torch.zeros((G, M, N), dtype=torch.float32, device=device)
+    launch = gg.bind_k_grouped(a, sfa, b, sfb, d, [k] * G)
+    for _ in range(max(args.warmup, 3)):
+        launch()
+    torch.cuda.synchronize()
+    steps = min(args.steps, 50)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(device.index) as clocks:
+        e0.record()
+        for _ in range(steps):
+            launch()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    status = gg.device_status(device)
+    flops = 2.0 * G * M * N * k
+    alg_bytes = K * (M + N) + 2 * G * M * N * 4 + srows * (M + N) * 4
+    peaks = _peaks()
+    fp8_peak = 2.0 * (peaks["bf16_sustained"] or peaks["bf16_burst"])
+    tf = flops / (ms * 1e-3) / 1e12
+    return {
+        "metric": "k_grouped_gemm_fp8_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": cfg["desc"], "l2": f"operands and D ({alg_bytes / 1e6:.0f} MB per call) larger than L2, no flush",
+                   "timing": "CUDA events around back-to-back calls; a call = 2 transposes + 8 x (scale packing + GEMM)"},
+        "clocks": clocks.summary(), "e2e": None, "gpu_launches": steps * (2 + 2 * G),
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s", "frac": tf / fp8_peak,
+                     "traffic": None, "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})",
+                     "algorithmic_gbs": alg_bytes / (ms * 1e-3) / 1e9},
+        "device_status": status,
+    }
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -461,6 +519,11 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.workload == "kgrouped":
+        if world > 1:
+            raise SystemExit("the kgrouped workload is a single-GPU measurement")
+        print(json.dumps(run_kgrouped(args, device)), flush=True)
+        return
     if args.workload == "alpha":
         if world > 1:
             raise SystemExit("the alpha workload is a single-GPU latency measurement")
@@ -580,9 +643,15 @@ def run_ours(args):
         del data, launch
         torch.cuda.empty_cache()
         layer_res = run_layer(args, world, rank, device, barrier, min(args.steps, 20), args.warmup)
+    alpha_res = None
+    if args.with_layer and world == 1 and args.workload == "gemm":
+        torch.cuda.empty_cache()
+        alpha_res = run_alpha(args, device)       # the decode-regime layer's six rows, a few seconds
     if rank == 0:
         if layer_res is not None:
             line["moe_layer"] = layer_res
+        if alpha_res is not None:
+            line["alpha_layer"] = alpha_res
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -594,10 +663,11 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["layer", "alpha"], default="gemm")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["layer", "alpha", "kgrouped"], default="gemm")
     ap.add_argument("--no-layer", dest="with_layer", action="store_false",
                     help="skip the expert-parallel MoE layer measurement that follows the grouped-GEMM one "
-                         "(it is reported as the extra object `moe_layer` of the same JSON line)")
+                         "(it is reported as the extra object `moe_layer` of the same JSON line; on one GPU the "
+                         "decode-regime layer's rows follow as `alpha_layer`)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--combine", choices=["pull", "push"], default="push",
                     help="layer workload: how expert outputs travel back (see ep_layer.EpMoeLayer)")

@@ -66,6 +66,8 @@ extern "C" {
  *           word (group g, column n, q) of B at sfb[g*sfb_stride[0] + n*sfb_stride[1] + q*sfb_stride[2]]
  *           (B scales per column, as that format stores them).  Needs workspace; always takes the
  *           block-scaled-MMA path.
+ *   ldb     row pitch of b in bytes; 0 = K (dense).  With lda it lets a K window of wider matrices be multiplied.
+ *   accumulate  non-zero: d (fp32 only) is added to instead of overwritten (d += a*b^T), block-scaled path only.
  *   scatter_meta  contiguous layout, bf16 output only, may be NULL.  If given (int32 [M]), valid row r is not
  *           stored at d + r*ldd but at scatter_base[meta >> 24] + (meta & 0xFFFFFF)*ldd, meta = scatter_meta[r]:
  *           the expert-parallel down GEMM uses it to store every output row directly into the slot of the
@@ -92,6 +94,8 @@ typedef struct moe_gg_args {
     int32_t sf_format;
     int64_t sfb_stride[3];
     int64_t lda;
+    int64_t ldb;
+    int32_t accumulate;
 } moe_gg_args;
 
 /* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With
@@ -107,6 +111,33 @@ int moe_gg_fp8_contiguous(const moe_gg_args* args, void* stream);
 /* Masked layout.  Stands in for the masked grouped kernel exercised by
  * tools/tests/numsim/corpus/kernels/gemm.py:705-795 (deepgemm_sm100_m_grouped_fp8_gemm_masked). */
 int moe_gg_fp8_masked(const moe_gg_args* args, void* stream);
+
+
+/* ---- k-grouped layout (weight-gradient shape) ------------------------------------------------ */
+/* D_g [M, N] (fp32) += A_g^T * B_g for g < G, where group g owns the K rows [sum(ks[:g]), +ks[g]) of the
+ * MN-major operands a e4m3 [K_total, M] and b e4m3 [K_total, N]; scales are the packed UE8M0 words of that
+ * layout, one word per (row m or n, four 128-K blocks of one group): sfa int32 [sum(ceil(ks[g]/512)), M],
+ * sfb likewise [.., N]; d fp32 [G, M, N] is accumulated into.  Stands in for the k-grouped entry of the
+ * reference's DeepGEMM kernel family (deepgemm_sm100_k_grouped_fp8_gemm_contiguous as exercised by
+ * tools/tests/numsim/corpus/kernels/gemm.py:610-702: per-group K cursors, MN-major operands, fp32 accumulation
+ * onto the existing D).  `ks` is a HOST array (the shapes of a weight gradient are known on the host);
+ * every ks[g] must be a multiple of 128, M % 128 == 0, N % 8 == 0.  This version transposes the operands
+ * into K-major scratch (one pass over a and b) and runs the block-scaled kernel once per group on its K
+ * window.  workspace: moe_kg_workspace_bytes, 256-byte aligned.                                      */
+typedef struct moe_kg_args {
+    const void* a;                /* e4m3 [K_total, M] */
+    const void* b;                /* e4m3 [K_total, N] */
+    const int32_t* sfa;           /* packed UE8M0 [scale_rows, M] */
+    const int32_t* sfb;           /* packed UE8M0 [scale_rows, N] */
+    float* d;                     /* fp32 [G, M, N], accumulated into */
+    const int32_t* ks;            /* host pointer, int32 [G] */
+    int32_t G, M, N;
+    int64_t K_total;
+    void* workspace;
+    uint64_t workspace_bytes;
+} moe_kg_args;
+size_t moe_kg_workspace_bytes(int32_t M, int32_t N, int64_t K_total);
+int moe_kg_fp8_contiguous(const moe_kg_args* args, void* stream);
 
 
 /* ---- memory-bound stages around the GEMMs ------------------------------------------------- */

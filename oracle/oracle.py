@@ -347,3 +347,34 @@ def alpha_moe_layer(hidden_bits, ids, w, w13, w13_scale, w2, w2_scale, routed_sc
     counts = np.bincount(expert[keep], minlength=E).astype(np.int32)
     return dict(out=bf16_rne(out), abs_sum=abs_sum, x_q=x_q, x_s=x_s, counts=counts, order=order.astype(np.int64),
                 g1=g1, a2=a2, s2=s2, d2=d2)
+
+
+# ---------------------------------------------------------------- k-grouped layout (weight-gradient shape)
+def kg_contiguous(A, B, SFA, SFB, ks, D):
+    """k-grouped FP8 GEMM with fp32 accumulation onto D, following the reference's corpus case
+    (tools/tests/numsim/corpus/kernels/gemm.py:610-702: per-group K cursors, MN-major operands, D as the start of
+    the fp32 chain).  A u8[K_total,M], B u8[K_total,N], SFA u32[sum(ceil(ks/512)),M], SFB u32[..,N] (UE8M0, byte j of
+    a word = K block 4*word+j of its group), ks list of multiples of 128, D f32[G,M,N].  Returns the new D:
+    D[g][m,n] = fma-chain over the group's k (increasing) of (a*sfa)*(b*sfb), starting from D[g][m,n]."""
+    A = _c_arr(A, np.uint8)
+    B = _c_arr(B, np.uint8)
+    SFA = _c_arr(SFA, np.uint32)
+    SFB = _c_arr(SFB, np.uint32)
+    D = np.array(D, np.float32, copy=True)
+    koff = srow = 0
+    for g, k in enumerate(int(x) for x in ks):
+        if k == 0:
+            continue
+        kb = k // 128
+        words = (k + 511) // 512
+        def scales(W):          # [words, rows] u32 -> f32 [rows, kb]
+            b = np.stack([(W[srow:srow + words] >> np.uint32(8 * j)) & np.uint32(0xFF) for j in range(4)], axis=1)  # [words,4,rows]
+            codes = b.reshape(words * 4, -1)[:kb].astype(np.uint8)
+            return ue8m0_decode(codes).T.copy()
+        sa, sb = scales(SFA), scales(SFB)
+        a = e4m3_decode(A[koff:koff + k]).T * np.repeat(sa, 128, axis=1)       # [M, k], exact (powers of two)
+        b = e4m3_decode(B[koff:koff + k]).T * np.repeat(sb, 128, axis=1)
+        D[g] = fma_abt_increasing_k(a, b, d_init=D[g])
+        koff += k
+        srow += words
+    return D

@@ -37,7 +37,8 @@ def test_struct_layouts_match_header_field_order():
     text = open(os.path.join(ROOT, "include", "b200moe.h")).read()
     for cname, pystruct in (("moe_gg_args", _lib.GGArgs), ("moe_layer_args", _lib.LayerArgs),
                             ("moe_layer_view", _lib.LayerView), ("moe_ep_peers", _lib.EpPeers),
-                            ("moe_alpha_args", _lib.AlphaArgs), ("moe_alpha_view", _lib.AlphaView)):
+                            ("moe_alpha_args", _lib.AlphaArgs), ("moe_alpha_view", _lib.AlphaView),
+                            ("moe_kg_args", _lib.KgArgs)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []

@@ -234,3 +234,21 @@ def test_deepseek_routing_matches_reference_routing_block(golden_dir):
     dense = np.zeros_like(g["weights_dense"])
     np.put_along_axis(dense, ids.astype(np.int64), w, 1)
     np.testing.assert_allclose(dense, g["weights_dense"], rtol=2e-6, atol=1e-7)
+
+
+def test_k_grouped_oracle_matches_the_reference_case_expectation():
+    """tools/tests/numsim/corpus/kernels/gemm.py:610-702: all-ones A, B = 1.0 for the first group's K rows and 2.0
+    after, unit scales, D preset to 1.25 / -2.5: expected D[0] += k_0, D[1] += 2*k_1, compared with rtol=atol=0."""
+    M = N = 128
+    ks = [128, 256]
+    K = sum(ks)
+    A = np.full((K, M), 0x38, np.uint8)
+    B = np.full((K, N), 0x38, np.uint8)
+    B[ks[0]:] = 0x40
+    rows = sum((k + 511) // 512 for k in ks)
+    SFA = np.full((rows, M), 0x7F7F7F7F, np.uint32)
+    SFB = np.full((rows, N), 0x7F7F7F7F, np.uint32)
+    D = np.stack([np.full((M, N), 1.25, np.float32), np.full((M, N), -2.5, np.float32)])
+    out = orc.kg_contiguous(A, B, SFA, SFB, ks, D)
+    np.testing.assert_array_equal(out[0], np.float32(1.25 + ks[0]))
+    np.testing.assert_array_equal(out[1], np.float32(-2.5 + 2 * ks[1]))

@@ -25,6 +25,7 @@ class GGArgs(_c.Structure):
         ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
         ("scatter_meta", _c.c_void_p), ("scatter_base", _c.c_void_p * 8),
         ("sf_format", _c.c_int32), ("sfb_stride", _c.c_int64 * 3), ("lda", _c.c_int64),
+        ("ldb", _c.c_int64), ("accumulate", _c.c_int32),
     ]
 
 
@@ -46,6 +47,15 @@ class LayerView(_c.Structure):
     """``moe_layer_view`` of include/b200moe.h."""
     _fields_ = [(n, _c.c_void_p) for n in ("ids", "counts", "offsets", "pos", "src_pair", "grouped_layout",
                                            "weights", "s1", "s2", "a1", "g1", "a2", "y")] + [("cap_rows", _c.c_int64)]
+
+
+class KgArgs(_c.Structure):
+    """``moe_kg_args`` of include/b200moe.h."""
+    _fields_ = [
+        ("a", _c.c_void_p), ("b", _c.c_void_p), ("sfa", _c.c_void_p), ("sfb", _c.c_void_p), ("d", _c.c_void_p),
+        ("ks", _c.POINTER(_c.c_int32)), ("G", _c.c_int32), ("M", _c.c_int32), ("N", _c.c_int32), ("K_total", _c.c_int64),
+        ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
+    ]
 
 
 class AlphaArgs(_c.Structure):
@@ -103,13 +113,14 @@ EXPORTS = (
     "moe_combine",
     "moe_workspace_bytes", "moe_layer_forward", "moe_layer_workspace_view", "moe_device_status",
     "moe_alpha_workspace_bytes", "moe_alpha_forward", "moe_alpha_workspace_view",
+    "moe_kg_workspace_bytes", "moe_kg_fp8_contiguous",
     "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",
     "moe_ep_barrier", "moe_ep_workspace_bytes", "moe_ep_count_publish", "moe_ep_plan", "moe_ep_dispatch",
     "moe_ep_combine",
     "moe_last_error", "moe_version",
 )
 _SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes",
-                  "moe_alpha_workspace_bytes")
+                  "moe_alpha_workspace_bytes", "moe_kg_workspace_bytes")
 
 
 def check(rc: int) -> None:

@@ -223,9 +223,13 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     const bool allow_mx = !(env_mx && strcmp(env_mx, "0") == 0);
     CUtensorMap tmap_a, tmap_b;
     if (a->lda != 0 && (a->lda < a->K || a->lda % 16)) return fail(MOE_ERR_INVALID, "lda must be 0 or >= K and a multiple of 16");
+    if (a->ldb != 0 && (a->ldb < a->K || a->ldb % 16)) return fail(MOE_ERR_INVALID, "ldb must be 0 or >= K and a multiple of 16");
+    if (a->accumulate && (a->d_dtype != MOE_DTYPE_F32 || a->scatter_meta || !packed_sf))
+        return fail(MOE_ERR_UNSUPPORTED, "accumulate needs fp32 output, packed UE8M0 scales and no scattered output");
     rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
     if (rc != MOE_OK) return rc;
-    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, use_pair_kernel ? gg2::BN / 2 : gg::BN);
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, use_pair_kernel ? gg2::BN / 2 : gg::BN,
+                           (uint64_t)a->ldb);
     if (rc != MOE_OK) return rc;
 
     GGParams p;
@@ -244,6 +248,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.d = a->d;
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
+    p.d_accumulate = a->accumulate ? 1 : 0;
     p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
     p.rows_total = (int)rows_total;
     p.num_n_blocks = (a->N + gg::BN - 1) / gg::BN;
@@ -282,7 +287,8 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         // layout, where a pair multiplies up to 255 empty rows per group
         const bool mx_single = env_mxk ? strcmp(env_mxk, "single") == 0 : MASKED;
         CUtensorMap tmap_b2, tmap_sfa, tmap_sfb;
-        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx_single ? mx1::BN : mx::BN / 2);
+        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx_single ? mx1::BN : mx::BN / 2,
+                               (uint64_t)a->ldb);
         if (rc != MOE_OK) return rc;
         rc = encode_words_1d(&tmap_sfa, ws.sfa_packed, (uint64_t)ml.row_blocks * ml.quads * 128);
         if (rc != MOE_OK) return rc;
@@ -412,6 +418,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     if (rc != MOE_OK) return rc;
     CUtensorMap tmap_a, tmap_b;
     if (a->lda != 0 && (a->lda < a->K || a->lda % 16)) return fail(MOE_ERR_INVALID, "lda must be 0 or >= K and a multiple of 16");
+    if (a->ldb != 0 || a->accumulate) return fail(MOE_ERR_UNSUPPORTED, "ldb and accumulate are not supported by the fused-activation GEMM");
     rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)a->M, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
     if (rc != MOE_OK) return rc;
     rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, 64);
@@ -419,7 +426,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     GGParams p = {};
     p.sfa = a->sfa; p.sfa_sr = a->sfa_stride_row; p.sfa_sk = a->sfa_stride_kblk;
     p.sfb = a->sfb; p.layout = a->layout; p.rows_used = a->rows_used; p.mode_flag = nullptr;
-    p.d = nullptr; p.ldd = 0; p.d_f32 = 0;
+    p.d = nullptr; p.ldd = 0; p.d_f32 = 0; p.d_accumulate = 0;
     p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
     p.rows_total = a->M;
     p.inter = a->N / 2;
@@ -456,6 +463,53 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     cfg.attrs = attr;
     cfg.numAttrs = enabled ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// out[c * R + r] = in[r * C + c] for a byte matrix in [R, C]; 64 x 64 tiles through shared memory, 16-byte accesses.
+// R % 64 == 0 and C % 16 == 0.
+__global__ void transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, long long R, int C) {
+    __shared__ __align__(16) uint8_t t[64][80];
+    const long long r0 = (long long)blockIdx.y * 64;
+    const int c0 = blockIdx.x * 64;
+    const int row = threadIdx.x >> 2, seg = threadIdx.x & 3;
+    if (c0 + seg * 16 < C) {
+        const uint4 v = *reinterpret_cast<const uint4*>(in + (r0 + row) * C + c0 + seg * 16);
+        *reinterpret_cast<uint4*>(&t[row][seg * 16]) = v;
+    }
+    __syncthreads();
+    const int crow = row;                  // output row = input column c0 + crow
+    if (c0 + crow < C) {
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t x = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x |= (uint32_t)t[seg * 16 + q * 4 + i][crow] << (8 * i);
+            w[q] = x;
+        }
+        *reinterpret_cast<uint4*>(out + (long long)(c0 + crow) * R + r0 + seg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+struct KgWorkspace {
+    uint8_t *at, *bt;
+    int32_t* layout0;
+    void* gg_ws;
+    size_t gg_ws_bytes, bytes;
+};
+
+KgWorkspace carve_kg(void* base, int64_t M, int64_t N, int64_t K_total) {
+    KgWorkspace w{};
+    char* b = static_cast<char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char* p = b ? b + off : nullptr; off += align256(bytes); return p; };
+    w.at = reinterpret_cast<uint8_t*>(take((size_t)M * K_total));
+    w.bt = reinterpret_cast<uint8_t*>(take((size_t)N * K_total));
+    w.layout0 = reinterpret_cast<int32_t*>(take((size_t)M * 4));
+    w.gg_ws_bytes = mx_layout(1, M, (int)N, (int)K_total).bytes;
+    w.gg_ws = take(w.gg_ws_bytes);
+    w.bytes = off;
+    return w;
 }
 
 struct AlphaWorkspace {
@@ -721,6 +775,62 @@ int moe_layer_workspace_view(void* workspace, int32_t T, int32_t H, int32_t I, i
     view->pos = w.pos; view->src_pair = w.src_pair; view->grouped_layout = w.layout;
     view->a1 = w.a1; view->s1 = w.s1; view->g1 = w.g1; view->a2 = w.a2; view->s2 = w.s2; view->y = w.y;
     view->cap_rows = w.cap_rows;
+    return MOE_OK;
+}
+
+/* ---------------------------------------------------------------- k-grouped layout */
+size_t moe_kg_workspace_bytes(int32_t M, int32_t N, int64_t K_total) {
+    if (M <= 0 || N <= 0 || K_total <= 0 || K_total % 128 || K_total > 0x7FFFFFFFll) return 0;
+    return carve_kg(nullptr, M, N, K_total).bytes;
+}
+
+int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
+    if (!A) return fail(MOE_ERR_INVALID, "args is NULL");
+    if (!A->a || !A->b || !A->sfa || !A->sfb || !A->d || !A->ks || !A->workspace)
+        return fail(MOE_ERR_INVALID, "a, b, sfa, sfb, d, ks and workspace must be non-NULL");
+    if (A->G <= 0 || A->M <= 0 || A->N <= 0 || A->M % 128 || A->N % 16)
+        return fail(MOE_ERR_INVALID, "G, M, N must be positive, M a multiple of 128 and N of 16 (G=%d M=%d N=%d)", A->G, A->M, A->N);
+    int64_t k_sum = 0;
+    for (int g = 0; g < A->G; ++g) {
+        if (A->ks[g] < 0 || A->ks[g] % 128) return fail(MOE_ERR_INVALID, "ks[%d]=%d must be a non-negative multiple of 128", g, A->ks[g]);
+        k_sum += A->ks[g];
+    }
+    if (k_sum != A->K_total || k_sum <= 0 || k_sum > 0x7FFFFFFFll)
+        return fail(MOE_ERR_INVALID, "sum(ks)=%lld must equal K_total=%lld (positive, < 2^31)", (long long)k_sum, (long long)A->K_total);
+    if ((reinterpret_cast<uintptr_t>(A->a) & 15) || (reinterpret_cast<uintptr_t>(A->b) & 15) || (reinterpret_cast<uintptr_t>(A->d) & 15) ||
+        (reinterpret_cast<uintptr_t>(A->workspace) & 255))
+        return fail(MOE_ERR_INVALID, "a, b, d must be 16-byte aligned and workspace 256-byte aligned");
+    const size_t need = moe_kg_workspace_bytes(A->M, A->N, A->K_total);
+    if (A->workspace_bytes < need) return fail(MOE_ERR_INVALID, "workspace too small: %zu < %zu bytes", (size_t)A->workspace_bytes, need);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    KgWorkspace w = carve_kg(A->workspace, A->M, A->N, A->K_total);
+    CUDA_TRY(cudaMemsetAsync(w.layout0, 0, (size_t)A->M * 4, st));        // every row belongs to group 0 of its launch
+    transpose_u8_kernel<<<dim3((A->M + 63) / 64, (unsigned)(A->K_total / 64)), 256, 0, st>>>(
+        static_cast<const uint8_t*>(A->a), w.at, A->K_total, A->M);
+    CUDA_TRY(cudaGetLastError());
+    transpose_u8_kernel<<<dim3((A->N + 63) / 64, (unsigned)(A->K_total / 64)), 256, 0, st>>>(
+        static_cast<const uint8_t*>(A->b), w.bt, A->K_total, A->N);
+    CUDA_TRY(cudaGetLastError());
+    int64_t koff = 0, srow = 0;
+    for (int g = 0; g < A->G; ++g) {
+        const int32_t k = A->ks[g];
+        if (k == 0) continue;
+        moe_gg_args gg = {};
+        gg.a = w.at + koff; gg.lda = A->K_total;
+        gg.b = w.bt + koff; gg.ldb = A->K_total;
+        gg.sfa = reinterpret_cast<const float*>(A->sfa + srow * A->M); gg.sfa_stride_row = 1; gg.sfa_stride_kblk = A->M;
+        gg.sfb = reinterpret_cast<const float*>(A->sfb + srow * A->N);
+        gg.sfb_stride[0] = 0; gg.sfb_stride[1] = 1; gg.sfb_stride[2] = A->N;
+        gg.layout = w.layout0;
+        gg.d = A->d + (int64_t)g * A->M * A->N; gg.ldd = A->N;
+        gg.G = 1; gg.M = A->M; gg.N = A->N; gg.K = k;
+        gg.d_dtype = MOE_DTYPE_F32; gg.accumulate = 1; gg.sf_format = MOE_SF_UE8M0_PACKED;
+        gg.workspace = w.gg_ws; gg.workspace_bytes = w.gg_ws_bytes;
+        int rc = launch_gg<false>(&gg, stream);
+        if (rc != MOE_OK) return rc;
+        koff += k;
+        srow += (k + 511) / 512;
+    }
     return MOE_OK;
 }
 

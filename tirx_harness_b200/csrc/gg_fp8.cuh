@@ -84,6 +84,7 @@ struct GGParams {
     void* d;                     // bf16 (or fp32 when d_f32 != 0)
     long long ldd;
     int d_f32;
+    int d_accumulate;            // fp32 output only: add to d instead of overwriting it
     int G, M, N, K;              // M: total rows (contiguous) / rows per group (masked)
     int rows_total;              // rows of the flattened A / D (M or G*M)
     int num_n_blocks;            // ceil(N / BN)

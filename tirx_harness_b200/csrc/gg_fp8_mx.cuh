@@ -351,10 +351,15 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
                 for (int j = 0; j < 128; j += 4) {
-                    if (n0 + j + 4 <= p.N)
-                        *reinterpret_cast<float4*>(drow + j) =
-                            make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
-                                        __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
+                    if (n0 + j + 4 <= p.N) {
+                        float4 o = make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
+                                               __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
+                        if (p.d_accumulate) {
+                            const float4 old = *reinterpret_cast<const float4*>(drow + j);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(drow + j) = o;
+                    }
                 }
             } else if (row_valid) {
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
@@ -585,10 +590,15 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
                 for (int j = 0; j < 128; j += 4) {
-                    if (n0 + j + 4 <= p.N)
-                        *reinterpret_cast<float4*>(drow + j) =
-                            make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
-                                        __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
+                    if (n0 + j + 4 <= p.N) {
+                        float4 o = make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
+                                               __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
+                        if (p.d_accumulate) {
+                            const float4 old = *reinterpret_cast<const float4*>(drow + j);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(drow + j) = o;
+                    }
                 }
             } else if (row_valid) {
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;

@@ -187,6 +187,52 @@ def bind_contiguous_packed(a, sfa_words, b, sfb_words, d, grouped_layout) -> _Bo
     return bound
 
 
+class _BoundKGrouped:
+    """k-grouped (weight-gradient) GEMM bound to its tensors: ``d[g] += a[ks_g rows].T @ b[ks_g rows]``."""
+
+    def __init__(self, a, sfa_words, b, sfb_words, d, ks):
+        _check_fp8(a, "a"); _check_fp8(b, "b")
+        K_total, M = a.shape
+        N = b.shape[1]
+        ks = [int(k) for k in ks]
+        G = len(ks)
+        scale_rows = sum((k + 511) // 512 for k in ks)
+        if b.shape[0] != K_total or sum(ks) != K_total:
+            raise ValueError("a is [K_total, M], b is [K_total, N] and sum(ks) must equal K_total")
+        if sfa_words.dtype != torch.int32 or tuple(sfa_words.shape) != (scale_rows, M) or not sfa_words.is_contiguous():
+            raise ValueError(f"packed SFA must be contiguous int32 [{scale_rows}, {M}]")
+        if sfb_words.dtype != torch.int32 or tuple(sfb_words.shape) != (scale_rows, N) or not sfb_words.is_contiguous():
+            raise ValueError(f"packed SFB must be contiguous int32 [{scale_rows}, {N}]")
+        if d.dtype != torch.float32 or tuple(d.shape) != (G, M, N) or not d.is_contiguous():
+            raise ValueError(f"d must be contiguous float32 [{G}, {M}, {N}]")
+        L = _lib.lib()
+        self.device = a.device
+        ws_bytes = L.moe_kg_workspace_bytes(M, N, ctypes.c_int64(K_total))
+        if ws_bytes == 0:
+            raise ValueError("unsupported k-grouped shape (K_total must be a positive multiple of 128)")
+        self._ws = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
+        self._ks = (ctypes.c_int32 * G)(*ks)
+        self._keep = (a, sfa_words, b, sfb_words, d)
+        self._args = _lib.KgArgs(a=a.data_ptr(), b=b.data_ptr(), sfa=sfa_words.data_ptr(), sfb=sfb_words.data_ptr(),
+                                 d=d.data_ptr(), ks=self._ks, G=G, M=M, N=N, K_total=K_total,
+                                 workspace=self._ws.data_ptr(), workspace_bytes=ws_bytes)
+        self.d = d
+
+    def __call__(self):
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(_lib.lib().moe_kg_fp8_contiguous(ctypes.byref(self._args), ctypes.c_void_p(stream)))
+        return self.d
+
+
+def bind_k_grouped(a, sfa_words, b, sfb_words, d, ks) -> _BoundKGrouped:
+    """k-grouped FP8 GEMM with fp32 accumulation onto ``d`` (the weight-gradient layout of the reference's kernel
+    family, tools/tests/numsim/corpus/kernels/gemm.py:610-702): ``a`` e4m3 [K_total, M] and ``b`` e4m3 [K_total, N]
+    MN-major, group g owns ``ks[g]`` consecutive K rows (multiples of 128), packed UE8M0 scales int32
+    [sum(ceil(ks/512)), M] / [.., N], ``d`` f32 [G, M, N].  Returns the zero-argument callable."""
+    return _BoundKGrouped(a, sfa_words, b, sfb_words, d, ks)
+
+
 def m_grouped_fp8_gemm_nt_contiguous(a, sfa, b, sfb, d, grouped_layout):
     """One-shot form (argument order of the kernel the reference baselines against: (a, sfa), (b, sfb), d, layout)."""
     return bind_contiguous(a, sfa, b, sfb, d, grouped_layout)()
