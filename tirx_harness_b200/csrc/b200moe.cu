@@ -465,29 +465,45 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-// out[c * R + r] = in[r * C + c] for a byte matrix in [R, C]; 64 x 64 tiles through shared memory, 16-byte accesses.
-// R % 64 == 0 and C % 16 == 0.
-__global__ void transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, long long R, int C) {
-    __shared__ __align__(16) uint8_t t[64][80];
-    const long long r0 = (long long)blockIdx.y * 64;
-    const int c0 = blockIdx.x * 64;
-    const int row = threadIdx.x >> 2, seg = threadIdx.x & 3;
-    if (c0 + seg * 16 < C) {
-        const uint4 v = *reinterpret_cast<const uint4*>(in + (r0 + row) * C + c0 + seg * 16);
-        *reinterpret_cast<uint4*>(&t[row][seg * 16]) = v;
+// out[c * R + r] = in[r * C + c] for a byte matrix in [R, C]; 128 x 128 tiles, full 128-byte lines in and out.
+// Phase 1: the tile lands in shared memory as 32-bit words (row pitch 33 words); phase 2: thread (segment, column)
+// gathers the 16 bytes of its column from 16 consecutive rows (a warp = 32 columns of one segment: 8 distinct
+// banks, broadcast) into a second, transposed tile; phase 3: that tile leaves as 16-byte pieces of full lines.
+// R % 128 == 0 and C % 16 == 0.
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
+                                                             long long R, int C) {
+    __shared__ uint32_t t[128][33];
+    __shared__ __align__(16) uint32_t tt[128][36];
+    const long long r0 = (long long)blockIdx.y * 128;
+    const int c0 = blockIdx.x * 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + 256 * i, row = idx >> 3, seg = idx & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (c0 + seg * 16 < C) v = __ldg(reinterpret_cast<const uint4*>(in + (r0 + row) * C + c0 + seg * 16));
+        t[row][seg * 4 + 0] = v.x; t[row][seg * 4 + 1] = v.y; t[row][seg * 4 + 2] = v.z; t[row][seg * 4 + 3] = v.w;
     }
     __syncthreads();
-    const int crow = row;                  // output row = input column c0 + crow
-    if (c0 + crow < C) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + 256 * i, seg = idx >> 7, c = idx & 127;
+        const int sh = (c & 3) * 8;
         uint32_t w[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             uint32_t x = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) x |= (uint32_t)t[seg * 16 + q * 4 + i][crow] << (8 * i);
+            for (int k = 0; k < 4; ++k) x |= ((t[seg * 16 + q * 4 + k][c >> 2] >> sh) & 0xFFu) << (8 * k);
             w[q] = x;
         }
-        *reinterpret_cast<uint4*>(out + (long long)(c0 + crow) * R + r0 + seg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(&tt[c][seg * 4]) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = threadIdx.x + 256 * i, c = idx >> 3, seg = idx & 7;
+        if (c0 + c < C)
+            *reinterpret_cast<uint4*>(out + (long long)(c0 + c) * R + r0 + seg * 16) = *reinterpret_cast<const uint4*>(&tt[c][seg * 4]);
     }
 }
 
@@ -805,10 +821,10 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     KgWorkspace w = carve_kg(A->workspace, A->M, A->N, A->K_total);
     CUDA_TRY(cudaMemsetAsync(w.layout0, 0, (size_t)A->M * 4, st));        // every row belongs to group 0 of its launch
-    transpose_u8_kernel<<<dim3((A->M + 63) / 64, (unsigned)(A->K_total / 64)), 256, 0, st>>>(
+    transpose_u8_kernel<<<dim3((A->M + 127) / 128, (unsigned)(A->K_total / 128)), 256, 0, st>>>(
         static_cast<const uint8_t*>(A->a), w.at, A->K_total, A->M);
     CUDA_TRY(cudaGetLastError());
-    transpose_u8_kernel<<<dim3((A->N + 63) / 64, (unsigned)(A->K_total / 64)), 256, 0, st>>>(
+    transpose_u8_kernel<<<dim3((A->N + 127) / 128, (unsigned)(A->K_total / 128)), 256, 0, st>>>(
         static_cast<const uint8_t*>(A->b), w.bt, A->K_total, A->N);
     CUDA_TRY(cudaGetLastError());
     int64_t koff = 0, srow = 0;

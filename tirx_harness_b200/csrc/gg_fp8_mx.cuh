@@ -354,11 +354,8 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (n0 + j + 4 <= p.N) {
                         float4 o = make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
                                                __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
-                        if (p.d_accumulate) {
-                            const float4 old = *reinterpret_cast<const float4*>(drow + j);
-                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                        }
-                        *reinterpret_cast<float4*>(drow + j) = o;
+                        if (p.d_accumulate) red_add_f32x4(drow + j, o);      // one contributor per element: same as load+add+store
+                        else *reinterpret_cast<float4*>(drow + j) = o;
                     }
                 }
             } else if (row_valid) {
@@ -593,11 +590,8 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     if (n0 + j + 4 <= p.N) {
                         float4 o = make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
                                                __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
-                        if (p.d_accumulate) {
-                            const float4 old = *reinterpret_cast<const float4*>(drow + j);
-                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                        }
-                        *reinterpret_cast<float4*>(drow + j) = o;
+                        if (p.d_accumulate) red_add_f32x4(drow + j, o);      // one contributor per element: same as load+add+store
+                        else *reinterpret_cast<float4*>(drow + j) = o;
                     }
                 }
             } else if (row_valid) {

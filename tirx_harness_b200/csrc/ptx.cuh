@@ -90,6 +90,11 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, ok);
 }
 
+// d[0..3] += v, performed by the L2 (no read back into the SM); 16-byte aligned
+__device__ __forceinline__ void red_add_f32x4(float* d, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
 // ---- cp.async (LDGSTS): 4-byte global -> shared copies whose completion arrives on an mbarrier
 __device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(gsrc) : "memory");
