@@ -183,7 +183,7 @@ def test_layer_stagewise_parity(ops):
                          host["gemm1_weights_scale"].numpy(), u8(host["gemm2_weights"]),
                          host["gemm2_weights_scale"].numpy(), top_k=top_k, gate_first=False)
     got, ref = dev["output"].float().cpu().numpy(), orc.bf16_to_f32(full["out"])
-    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean())
+    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean()) + 1e-30
 
 
 def test_layer_with_given_routes_and_mn_major_input_scales(ops):
@@ -251,7 +251,7 @@ def test_layer_fused_activation_matches_oracle(ops):
     _codes_close(u8(v["a2"])[:n][valid], full["a2"][valid], max_mismatch=5e-3)
     got, ref = dev["output"].float().cpu().numpy(), orc.bf16_to_f32(full["out"])
     assert np.isfinite(got).all()
-    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean())
+    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean()) + 1e-30
 
 
 def test_deepseek_routing_ids_exact(ops, golden_dir):
@@ -271,11 +271,12 @@ def test_deepseek_routing_ids_exact(ops, golden_dir):
     np.testing.assert_allclose(npf(w0), 0.125, rtol=1e-6)
 
 
-def test_layer_with_registered_moe_task_keys(ops):
+@pytest.mark.parametrize("T", [1, 7, 59, 200])          # the task's trace rows start at T = 1, 7, 14, 15, ...
+def test_layer_with_registered_moe_task_keys(ops, T):
     """The `moe` task's data dict (DeepSeek routing, MN-major input scales, local_expert_offset): only the local
     experts' contributions are summed, as in tasks/moe/definition.json."""
     from tirx_harness_b200 import moe_layer
-    T, H, I, E_loc, E_glob, top_k = 200, 256, 128, 32, 256, 8
+    H, I, E_loc, E_glob, top_k = 256, 128, 32, 256, 8
     dev, host = _make_layer(T, H, I, E_loc, top_k, seed=33)
     gen = torch.Generator().manual_seed(7)
     logits = torch.randn((T, E_glob), generator=gen) * 2
@@ -296,4 +297,4 @@ def test_layer_with_registered_moe_task_keys(ops):
     np.testing.assert_array_equal(v["counts"].cpu().numpy(), full["plan"]["counts"])
     got, ref = data["output"].float().cpu().numpy(), orc.bf16_to_f32(full["out"])
     assert np.isfinite(got).all()
-    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean())
+    assert np.sqrt(((got - ref) ** 2).mean()) <= 5e-3 * np.sqrt((ref**2).mean()) + 1e-30

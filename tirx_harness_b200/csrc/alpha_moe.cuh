@@ -95,6 +95,60 @@ __global__ void alpha_quant_scatter_kernel(const __nv_bfloat16* __restrict__ x, 
     if (lane == 0) s[(long long)b * rows_total + row] = sc;
 }
 
+// Plan and quantisation in one launch, for the decode regime (a few thousand routes at most): one warp per
+// (route, 128-block) finds its route's slot itself by scanning the route list (slot = number of earlier routes
+// to the same expert; the route list is a few KB and stays in L1/L2) instead of waiting for a separate plan
+// kernel; the warp of block 0 also publishes rowpos and, if no later route goes to the same expert, the
+// expert's count.  `counts` must be zero on entry (experts without routes keep 0).  Same results as
+// alpha_plan_kernel + alpha_quant_scatter_kernel, bit for bit.
+__global__ void alpha_plan_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids, int n_pairs, int top_k,
+                                        int E, int max_m, int H, long long rows_total, int* __restrict__ counts,
+                                        int* __restrict__ rowpos, uint8_t* __restrict__ q, float* __restrict__ s, int* status) {
+    const int nb = H >> 7;
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    if (w >= n_pairs * nb) return;
+    const int p = w / nb, b = w - p * nb;
+    // the token's values do not depend on the previous kernels of the stream: fetch them before waiting
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(x + (long long)(p / top_k) * H + b * 128 + lane * 4));
+    const int e = __ldg(ids + p);
+    int before = 0, after = 0;
+    if (e >= 0 && e < E) {
+        for (int base = 0; base < n_pairs; base += 32) {
+            const int i = base + lane;
+            const bool same = i < n_pairs && __ldg(ids + i) == e;
+            before += same && i < p;
+            after += same && i > p;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+        after += __shfl_xor_sync(0xffffffffu, after, o);
+    }
+    const bool valid = e >= 0 && e < E && before < max_m;
+    const int row = valid ? e * max_m + before : -1;
+    pdl_wait();              // counts / rowpos / a1 may still be in use by the previous call's kernels
+    if (b == 0 && lane == 0) {
+        rowpos[p] = row;
+        if (e >= 0 && e < E && after == 0) {
+            int c = before + 1;
+            if (c > max_m) {
+                atomicOr(status, STATUS_ALPHA_OVERFLOW);
+                c = max_m;
+            }
+            counts[e] = c;
+        }
+    }
+    if (!valid) return;
+    float v[4], sc;
+    bf16x4_to_float(raw, v);
+    const uint32_t packed = quant_block_4(v, &sc);
+    *reinterpret_cast<uint32_t*>(q + (long long)row * H + b * 128 + lane * 4) = packed;
+    if (lane == 0) s[(long long)b * rows_total + row] = sc;
+}
+
 // One warp per route.  gu fp32 [rows_total, 2I] with gate = columns [0, I) when gate_first, else [I, 2I).
 __global__ void alpha_silu_requant_kernel(const float* __restrict__ gu, const int* __restrict__ rowpos, int n_pairs,
                                           int inter, int gate_first, long long rows_total, uint8_t* __restrict__ q,

@@ -147,6 +147,9 @@ int device_info(DeviceInfo** out) {
                                       mx1::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx1::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(alpha_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * asw::MAX_E * 4));
+        CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<1>::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<2>::SMEM_BYTES));
         {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(2 * di.num_sms, 1, 1);
@@ -447,6 +450,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     return MOE_OK;
 }
 
+constexpr int ALPHA_FUSED_PLAN_MAX_ROUTES = 2048;   // above this a route list scan per warp costs more than a plan launch
 constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
 constexpr bool ALPHA_SWAP_DOWN_DEFAULT = true;
 
@@ -885,20 +889,26 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     AlphaWorkspace w = carve_alpha(A->workspace, A->M, A->H, A->I, A->E, A->top_k);
     const int n_pairs = A->M * A->top_k;
     const size_t hist_bytes = (size_t)32 * A->E * 4;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
-        CUDA_TRY(cudaFuncSetAttribute(alpha_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * gg::MAX_MASKED_GROUPS * 4));
-        attr_set[dev] = true;
-    }
-    CUDA_TRY(launch_pdl(alpha_plan_kernel, dim3(1), dim3(ALPHA_PLAN_THREADS), hist_bytes, st, A->topk_ids, n_pairs, A->E,
-                        (int)w.max_m, w.counts, w.rowpos, status_ptr()));
+    DeviceInfo* di = nullptr;      // also raises the kernels' dynamic shared-memory limits, once per device
+    rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
     const int wpb = 8;
     const int route_blocks = (n_pairs + wpb - 1) / wpb;
     const int quant_blocks = (n_pairs * (A->H / 128) + wpb - 1) / wpb;
-    CUDA_TRY(launch_pdl(alpha_quant_scatter_kernel, dim3(quant_blocks), dim3(wpb * 32), 0, st,
-                        static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs, A->top_k, A->H, w.rows_total, w.a1, w.s1));
+    if (n_pairs <= ALPHA_FUSED_PLAN_MAX_ROUTES) {
+        // decode regime: every quantisation warp finds its route's slot itself, no separate plan launch
+        CUDA_TRY(cudaMemsetAsync(w.counts, 0, (size_t)A->E * 4, st));
+        alpha_plan_quant_kernel<<<quant_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), A->topk_ids, n_pairs,
+                                                                 A->top_k, A->E, (int)w.max_m, A->H, w.rows_total, w.counts, w.rowpos,
+                                                                 w.a1, w.s1, status_ptr());
+        CUDA_TRY(cudaGetLastError());
+    } else {
+        CUDA_TRY(launch_pdl(alpha_plan_kernel, dim3(1), dim3(ALPHA_PLAN_THREADS), hist_bytes, st, A->topk_ids, n_pairs, A->E,
+                            (int)w.max_m, w.counts, w.rowpos, status_ptr()));
+        CUDA_TRY(launch_pdl(alpha_quant_scatter_kernel, dim3(quant_blocks), dim3(wpb * 32), 0, st,
+                            static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs, A->top_k, A->H, w.rows_total, w.a1, w.s1));
+    }
+    (void)route_blocks;
     // The two projections run either as swapped-operand decode kernels (weights = MMA rows, 32 routed rows = MMA
     // columns) or as row-major masked-layout grouped GEMMs (128 x 256 tiles); the intermediates have the same layout
     // either way.  Developer switch B200MOE_ALPHA_PATH = swap | masked | mixed (masked gate_up, swapped down).
@@ -907,15 +917,6 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     if (env_path) {
         swap1 = strcmp(env_path, "swap") == 0;
         swap2 = strcmp(env_path, "swap") == 0 || strcmp(env_path, "mixed") == 0;
-    }
-    DeviceInfo* di = nullptr;
-    rc = device_info(&di);
-    if (rc != MOE_OK) return rc;
-    static bool swap_attr_set[64] = {};
-    if (dev < 64 && !swap_attr_set[dev]) {
-        CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<1>::SMEM_BYTES));
-        CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<2>::SMEM_BYTES));
-        swap_attr_set[dev] = true;
     }
     // (expert, chunk) units: at most one per expert that has rows plus one per further 32 rows
     const long long unit_bound = (n_pairs < A->E ? n_pairs : A->E) + n_pairs / asw::NT;
