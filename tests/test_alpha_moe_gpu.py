@@ -103,7 +103,7 @@ def _check_against_oracle(c, op, data, M):
 
 @pytest.mark.parametrize("M,H,E,top_k,skew", [(1, 256, 8, 3, 0.0), (5, 512, 16, 4, 0.0), (16, 256, 64, 6, 3.0),
                                                 (33, 2048, 48, 10, 0.0),
-                                                (256, 256, 64, 10, 0.0)])      # > 2048 routes: separate plan kernel
+                                                (256, 256, 64, 10, 0.0)])      # above 512 routes: separate plan kernel
 def test_alpha_layer_matches_oracle(M, H, E, top_k, skew):
     c = _case(M, H, E, top_k, seed=100 + M, rsf=1.0 if M % 2 else 2.5, skew=skew)
     op, data = _run_gpu(c, M)

@@ -450,7 +450,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     return MOE_OK;
 }
 
-constexpr int ALPHA_FUSED_PLAN_MAX_ROUTES = 2048;   // above this a route list scan per warp costs more than a plan launch
+constexpr int ALPHA_FUSED_PLAN_MAX_ROUTES = 512;    // measured: the per-warp scan of the route list wins up to a few hundred routes
 constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
 constexpr bool ALPHA_SWAP_DOWN_DEFAULT = true;
 
