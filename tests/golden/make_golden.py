@@ -1,6 +1,7 @@
 """Regenerates the golden fixtures in this folder from the reference checkout.
 
-Run once in a container that has the reference at REF (default /root/reference):
+Run once on a machine that has a checkout of the reference; pass its path as the first argument
+(or set TIRX_HARNESS_REF):
 
     python tests/golden/make_golden.py [REF]
 
@@ -21,7 +22,7 @@ import types
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TIRX_HARNESS_REF", "reference")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
