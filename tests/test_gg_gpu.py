@@ -189,6 +189,21 @@ def test_masked_random_small(gg):
     _check_masked(gg, make_masked_case(5, 96, 384, 256, seed=12))       # max_m not a multiple of 128
 
 
+def test_masked_decode_shapes_many_groups_few_rows(gg):
+    """Decode regime: many groups with a handful of rows each.  Tiles with at most 16 valid rows fetch a 16-row box
+    of A, the schedule comes from the shared-memory tables; checked for the promotion kernel (continuous scales,
+    max_m not a multiple of 128) and the block-scaled single-CTA kernel (power-of-two scales, max_m = 128)."""
+    from tirx_harness_b200.workloads import make_masked_case
+    rng = np.random.default_rng(5)
+    G = 96
+    mm = rng.integers(0, 13, size=G)
+    mm[[3, 40, 95]] = [40, 17, 16]                       # a full group, one just above and one at the small-box limit
+    _check_masked(gg, make_masked_case(G, 40, 256, 512, seed=21, law="uniform_exp", masked_m=mm.tolist()))
+    mm2 = rng.integers(0, 20, size=G)
+    mm2[[0, 50]] = [128, 0]
+    _check_masked(gg, make_masked_case(G, 128, 384, 512, seed=22, masked_m=mm2.tolist()))
+
+
 def test_full_size_properties_config1(gg):
     """Full DeepSeek-V3 gate_up shape: checked through size-independent properties and a row sample."""
     from tirx_harness_b200.workloads import make_operand_b
