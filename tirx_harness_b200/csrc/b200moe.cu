@@ -252,6 +252,10 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
     p.d_accumulate = a->accumulate ? 1 : 0;
+    {
+        const char* env_trace = getenv("B200MOE_GG_TRACE");      // developer aid: device address of int64 [grid][8]
+        p.trace = env_trace ? reinterpret_cast<long long*>(strtoull(env_trace, nullptr, 10)) : nullptr;
+    }
     p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
     p.rows_total = (int)rows_total;
     p.num_n_blocks = (a->N + gg::BN - 1) / gg::BN;
@@ -429,7 +433,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     GGParams p = {};
     p.sfa = a->sfa; p.sfa_sr = a->sfa_stride_row; p.sfa_sk = a->sfa_stride_kblk;
     p.sfb = a->sfb; p.layout = a->layout; p.rows_used = a->rows_used; p.mode_flag = nullptr;
-    p.d = nullptr; p.ldd = 0; p.d_f32 = 0; p.d_accumulate = 0;
+    p.d = nullptr; p.ldd = 0; p.d_f32 = 0; p.d_accumulate = 0; p.trace = nullptr;
     p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
     p.rows_total = a->M;
     p.inter = a->N / 2;

@@ -85,6 +85,7 @@ struct GGParams {
     long long ldd;
     int d_f32;
     int d_accumulate;            // fp32 output only: add to d instead of overwriting it
+    long long* trace;            // developer aid: per-CTA wait-cycle counters [grid][8], or nullptr
     int G, M, N, K;              // M: total rows (contiguous) / rows per group (masked)
     int rows_total;              // rows of the flattened A / D (M or G*M)
     int num_n_blocks;            // ceil(N / BN)

@@ -235,6 +235,8 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             PairScheduler<MASKED> sched(p, prefix, lane, rank);
             Tile tile;
             uint32_t stage = 0, phase = 0, qcount = 0;
+            long long tr_wait = 0;
+            const long long tr_t0 = clock64();
             bool ok = true;
             while (ok && sched.next(tile)) {
                 const int b_row = tile.g * p.N + tile.n_blk * BN + (int)rank * (BN / 2);
@@ -242,8 +244,10 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int sfb_chunk = (tile.g * p.nb128 + tile.n_blk * 2) * quads;  // first of the two column blocks
                 const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
                 for (int kb = 0; kb < KB; ++kb) {
+                    const long long c0 = p.trace ? clock64() : 0;
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
                                         STATUS_TIMEOUT_SMEM_EMPTY);
+                    if (p.trace) tr_wait += clock64() - c0;
                     if (!ok) break;
                     if (lane == 0) {
                         const uint32_t fb = leader_full_bar + 8 * stage;
@@ -265,6 +269,10 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
+            if (p.trace && lane == 0) {
+                p.trace[blockIdx.x * 8 + 0] = tr_wait;
+                p.trace[blockIdx.x * 8 + 1] = clock64() - tr_t0;
+            }
         } else if (warp == 1 && rank == 0) {
             // ------------------------------------------------ MMA issuer (leader)
             // The tile sequence is computed by the whole warp; a tile's K loop is run by lane 0 alone with
@@ -277,12 +285,18 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem_a));
             const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
             const uint32_t idesc0 = make_idesc_mxf8(2 * BM, BN, 0);
+            long long tr_te = 0, tr_full = 0, tr_issue = 0;
             while (ok && sched.next(tile)) {
                 if (lane == 0) {
                     // the single accumulator must have been drained by both CTAs' epilogues
+                    const long long c0 = p.trace ? clock64() : 0;
                     ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                    if (p.trace) tr_te += clock64() - c0;
                     for (int kb = 0; ok && kb < KB; ++kb) {
+                        const long long c1 = p.trace ? clock64() : 0;
                         ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                        const long long c2 = p.trace ? clock64() : 0;
+                        tr_full += c2 - c1;
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t sub = kb & 3;
@@ -305,6 +319,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         umma_mxf8_pair(tmem_base, adesc + 6, bdesc + 6, idesc, tsfa, tsfb, 1u);
                         umma_commit_pair(empty_bar + 8 * stage, 3);
                         if (kb == KB - 1) umma_commit_pair(tfull_bar, 3);
+                        if (p.trace) tr_issue += clock64() - c2;
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
                     tile_phase ^= 1;
@@ -314,6 +329,11 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 phase = __shfl_sync(0xffffffffu, phase, 0);
                 tile_phase = __shfl_sync(0xffffffffu, tile_phase, 0);
                 qcount = __shfl_sync(0xffffffffu, qcount, 0);
+            }
+            if (p.trace && lane == 0) {
+                p.trace[blockIdx.x * 8 + 2] = tr_te;
+                p.trace[blockIdx.x * 8 + 3] = tr_full;
+                p.trace[blockIdx.x * 8 + 4] = tr_issue;
             }
         }
     } else {
