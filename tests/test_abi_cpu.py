@@ -63,3 +63,7 @@ def test_workspace_size_is_monotonic_and_cpu_callable():
     small, big = L.moe_alpha_workspace_bytes(1, 2048, 128, 512, 10), L.moe_alpha_workspace_bytes(128, 2048, 128, 512, 10)
     assert 0 < small < big < (1 << 30)
     assert L.moe_alpha_workspace_bytes(8, 0, 128, 512, 10) == 0
+    # k-grouped layout: K-major copies of both operands plus the scale tiles of the largest possible group
+    kg = L.moe_kg_workspace_bytes(256, 384, ctypes.c_int64(1024))
+    assert kg >= (256 + 384) * 1024
+    assert L.moe_kg_workspace_bytes(256, 384, ctypes.c_int64(1000)) == 0          # K_total must be a multiple of 128
