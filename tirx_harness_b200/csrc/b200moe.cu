@@ -143,6 +143,8 @@ int device_info(DeviceInfo** out) {
                                       mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx1::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -313,7 +315,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
             int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
             if (pairs < 1) pairs = 1;
             gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
-                                                                                   ws.flag, ml.quads, status_ptr());
+                                                                                   ws.flag, ml.quads, status_ptr(), KgNone{});
         }
         CUDA_TRY(cudaGetLastError());
         p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
@@ -519,6 +521,8 @@ struct KgWorkspace {
     uint8_t *at, *bt;
     int32_t* layout0;
     void* gg_ws;
+    int* flag;
+    uint32_t *sfa_tiles, *sfb_tiles;
     size_t gg_ws_bytes, bytes;
 };
 
@@ -532,6 +536,12 @@ KgWorkspace carve_kg(void* base, int64_t M, int64_t N, int64_t K_total) {
     w.layout0 = reinterpret_cast<int32_t*>(take((size_t)M * 4));
     w.gg_ws_bytes = mx_layout(1, M, (int)N, (int)K_total).bytes;
     w.gg_ws = take(w.gg_ws_bytes);
+    // single launch over all groups: scale tiles of every (128 rows or columns, scale word row); at most one word row
+    // per 128 K rows
+    const size_t max_quads = (size_t)(K_total / 128);
+    w.flag = reinterpret_cast<int*>(take(256));
+    w.sfa_tiles = reinterpret_cast<uint32_t*>(take((size_t)((M + 127) / 128) * max_quads * 512));
+    w.sfb_tiles = reinterpret_cast<uint32_t*>(take((size_t)((N + 127) / 128) * max_quads * 512));
     w.bytes = off;
     return w;
 }
@@ -835,6 +845,54 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
     transpose_u8_kernel<<<dim3((A->N + 127) / 128, (unsigned)(A->K_total / 128)), 256, 0, st>>>(
         static_cast<const uint8_t*>(A->b), w.bt, A->K_total, A->N);
     CUDA_TRY(cudaGetLastError());
+    if (A->G <= 64 && getenv("B200MOE_KG_PER_GROUP") == nullptr) {
+        // one launch over all groups (per-group launches round 6.05 waves of tiles up to 7, eight times)
+        DeviceInfo* di = nullptr;
+        int rc = device_info(&di);
+        if (rc != MOE_OK) return rc;
+        KgTable kg = {};
+        kg.n = A->G;
+        int64_t ko = 0, qo = 0;
+        for (int g = 0; g < A->G; ++g) {
+            kg.koff[g] = (int)ko; kg.kb[g] = A->ks[g] / 128; kg.qoff[g] = (int)qo;
+            ko += A->ks[g];
+            qo += (A->ks[g] + 511) / 512;
+        }
+        const int quads = (int)qo;
+        GGParams p = {};
+        p.d = A->d; p.ldd = A->N; p.d_f32 = 1; p.d_accumulate = 1;
+        p.G = A->G; p.M = A->M; p.N = A->N; p.K = (int)A->K_total;
+        p.rows_total = A->M;
+        p.num_n_blocks = (A->N + mx::BN - 1) / mx::BN;
+        p.num_k_blocks = 0;
+        p.nb128 = (A->N + 127) / 128;
+        p.num_m_blocks = (A->M + 127) / 128;
+        kg.per_group = ((A->M + 255) / 256) * p.num_n_blocks;
+        MxWorkspace ws;
+        ws.flag = w.flag; ws.sfa_packed = w.sfa_tiles; ws.sfb_packed = w.sfb_tiles;
+        ws.row_blocks = (A->M + 127) / 128; ws.quads = quads;
+        CUDA_TRY(cudaMemsetAsync(ws.flag, 0, sizeof(int), st));
+        dim3 pgrid(ws.row_blocks + p.nb128, quads, 1);
+        mx_prep_packed_kernel<<<pgrid, 128, 0, st>>>(reinterpret_cast<const uint32_t*>(A->sfa), 1, A->M,
+                                                     reinterpret_cast<const uint32_t*>(A->sfb), 0, 1, A->N, A->M, A->N, 1, p.nb128, ws);
+        CUDA_TRY(cudaGetLastError());
+        CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+        rc = encode_fp8_kmajor(&tm_a, w.at, (uint64_t)A->M, (uint64_t)A->K_total, 128);
+        if (rc != MOE_OK) return rc;
+        rc = encode_fp8_kmajor(&tm_b, w.bt, (uint64_t)A->N, (uint64_t)A->K_total, mx::BN / 2);
+        if (rc != MOE_OK) return rc;
+        rc = encode_words_1d(&tm_sfa, ws.sfa_packed, (uint64_t)ws.row_blocks * quads * 128);
+        if (rc != MOE_OK) return rc;
+        rc = encode_words_1d(&tm_sfb, ws.sfb_packed, (uint64_t)p.nb128 * quads * 128);
+        if (rc != MOE_OK) return rc;
+        const long long tiles = (long long)kg.n * kg.per_group;
+        int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
+        if (pairs < 1) pairs = 1;
+        gg_fp8_mx_kernel<false, true><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, p, ws.flag, quads,
+                                                                                    status_ptr(), kg);
+        CUDA_TRY(cudaGetLastError());
+        return MOE_OK;
+    }
     int64_t koff = 0, srow = 0;
     for (int g = 0; g < A->G; ++g) {
         const int32_t k = A->ks[g];

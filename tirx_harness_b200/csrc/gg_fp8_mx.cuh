@@ -151,12 +151,62 @@ __device__ __forceinline__ uint32_t make_idesc_mxf8(int m, int n, uint32_t sf_id
            | (sf_id << 29);                               // A scale id
 }
 
+// ---- k-grouped schedule of the pair kernel: G groups share the rows of A ([M, K_total], K-major copy) and of B
+// ([N, K_total]); group g multiplies them over its K window and owns d[g].  Passed by value (up to 64 groups).
+struct KgTable {
+    int n;                 // groups
+    int per_group;         // pair tiles per group: ceil(M/256) * column blocks
+    int koff[64];          // first K element of each group
+    int kb[64];            // K blocks (128) of each group
+    int qoff[64];          // first scale word row (4 K blocks per word) of each group
+};
+struct KgNone {};
+template <bool KG> struct KgArg { using type = KgNone; };
+template <> struct KgArg<true> { using type = KgTable; };
+
+template <bool MASKED, bool KG> struct MxSched;
 template <bool MASKED>
+struct MxSched<MASKED, false> : PairScheduler<MASKED> {
+    __device__ __forceinline__ MxSched(const GGParams& p_, const int* prefix_, int lane_, int rank_, const KgNone&)
+        : PairScheduler<MASKED>(p_, prefix_, lane_, rank_) {}
+    static __device__ __forceinline__ int k_offset(const KgNone&, int) { return 0; }
+    static __device__ __forceinline__ int k_blocks(const KgNone&, int, int KB) { return KB; }
+    static __device__ __forceinline__ int quad_offset(const KgNone&, int) { return 0; }
+};
+template <>
+struct MxSched<false, true> {
+    const GGParams& p;
+    const KgTable& kg;
+    int t, stride, rank, total;
+    __device__ __forceinline__ MxSched(const GGParams& p_, const int*, int, int rank_, const KgTable& kg_)
+        : p(p_), kg(kg_), t(blockIdx.x >> 1), stride(gridDim.x >> 1), rank(rank_), total(kg_.n * kg_.per_group) {}
+    __device__ __forceinline__ bool next(Tile& tile) {
+        while (t < total) {
+            const int g = t / kg.per_group, rem = t - g * kg.per_group;
+            t += stride;
+            if (kg.kb[g] == 0) continue;          // a group without K rows leaves its d untouched
+            tile.g = g;
+            tile.m0 = (rem / p.num_n_blocks) * 256 + rank * 128;
+            tile.n_blk = rem % p.num_n_blocks;
+            tile.rows = 128;
+            return true;
+        }
+        return false;
+    }
+    static __device__ __forceinline__ int k_offset(const KgTable& k, int g) { return k.koff[g]; }
+    static __device__ __forceinline__ int k_blocks(const KgTable& k, int g, int) { return k.kb[g]; }
+    static __device__ __forceinline__ int quad_offset(const KgTable& k, int g) { return k.qoff[g]; }
+};
+
+template <bool MASKED, bool KG = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(mx::THREADS, 1)
 gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                 const GGParams p, const int* __restrict__ flag, int quads, int* status) {
+                 const GGParams p, const int* __restrict__ flag, int quads, int* status,
+                 const __grid_constant__ typename KgArg<KG>::type kg) {
     using namespace mx;
+    static_assert(!(MASKED && KG), "the k-grouped schedule is a contiguous-layout mode");
+    using Sched = MxSched<MASKED, KG>;
     if (*flag != 0) return;          // some scale is not a power of two: the promotion kernel handles this call
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -232,18 +282,22 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         setmaxnreg_dec<72>();
         if (warp == 0) {
             // ------------------------------------------------ TMA producer (both CTAs)
-            PairScheduler<MASKED> sched(p, prefix, lane, rank);
+            Sched sched(p, prefix, lane, rank, kg);
             Tile tile;
             uint32_t stage = 0, phase = 0, qcount = 0;
             long long tr_wait = 0;
             const long long tr_t0 = clock64();
             bool ok = true;
             while (ok && sched.next(tile)) {
-                const int b_row = tile.g * p.N + tile.n_blk * BN + (int)rank * (BN / 2);
-                const int sfa_chunk = (tile.m0 >> 7) * quads;                       // this CTA's 128 rows
-                const int sfb_chunk = (tile.g * p.nb128 + tile.n_blk * 2) * quads;  // first of the two column blocks
+                // k-grouped: every group multiplies the same rows of A and B over its own K window
+                const int b_row = (KG ? 0 : tile.g * p.N) + tile.n_blk * BN + (int)rank * (BN / 2);
+                const int k0 = Sched::k_offset(kg, tile.g);
+                const int KBt = Sched::k_blocks(kg, tile.g, KB);
+                const int q0 = Sched::quad_offset(kg, tile.g);
+                const int sfa_chunk = (tile.m0 >> 7) * quads + q0;                  // this CTA's 128 rows
+                const int sfb_chunk = ((KG ? 0 : tile.g * p.nb128) + tile.n_blk * 2) * quads + q0;  // first of the two column blocks
                 const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
-                for (int kb = 0; kb < KB; ++kb) {
+                for (int kb = 0; kb < KBt; ++kb) {
                     const long long c0 = p.trace ? clock64() : 0;
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
                                         STATUS_TIMEOUT_SMEM_EMPTY);
@@ -253,8 +307,8 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         const uint32_t fb = leader_full_bar + 8 * stage;
                         const bool with_sf = (kb & 3) == 0;
                         if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * (A_STAGE_BYTES + B_STAGE_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0)));
-                        tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, kb * BK, tile.m0);
-                        tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
+                        tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, k0 + kb * BK, tile.m0);
+                        tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, k0 + kb * BK, b_row);
                         if (with_sf) {
                             const int q = kb >> 2;
                             const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
@@ -278,7 +332,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // The tile sequence is computed by the whole warp; a tile's K loop is run by lane 0 alone with
             // single-thread waits and incrementally updated descriptors.  The tensor pipe only queues a
             // couple of MMAs, so every instruction this thread spends between two K blocks is a bubble.
-            PairScheduler<MASKED> sched(p, prefix, lane, rank);
+            Sched sched(p, prefix, lane, rank, kg);
             Tile tile;
             uint32_t stage = 0, phase = 0, tile_phase = 0, qcount = 0;
             bool ok = true;
@@ -292,7 +346,8 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const long long c0 = p.trace ? clock64() : 0;
                     ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
                     if (p.trace) tr_te += clock64() - c0;
-                    for (int kb = 0; ok && kb < KB; ++kb) {
+                    const int KBt = Sched::k_blocks(kg, tile.g, KB);
+                    for (int kb = 0; ok && kb < KBt; ++kb) {
                         const long long c1 = p.trace ? clock64() : 0;
                         ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
                         const long long c2 = p.trace ? clock64() : 0;
@@ -318,7 +373,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         umma_mxf8_pair(tmem_base, adesc + 4, bdesc + 4, idesc, tsfa, tsfb, 1u);
                         umma_mxf8_pair(tmem_base, adesc + 6, bdesc + 6, idesc, tsfa, tsfb, 1u);
                         umma_commit_pair(empty_bar + 8 * stage, 3);
-                        if (kb == KB - 1) umma_commit_pair(tfull_bar, 3);
+                        if (kb == KBt - 1) umma_commit_pair(tfull_bar, 3);
                         if (p.trace) tr_issue += clock64() - c2;
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
@@ -343,16 +398,18 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int quarter = warp & 3;
         const int half = ew >> 2;
         const int row_in_tile = quarter * 32 + lane;
-        PairScheduler<MASKED> sched(p, prefix, lane, rank);
+        Sched sched(p, prefix, lane, rank, kg);
         Tile tile;
         uint32_t tile_phase = 0;
         bool ok = true;
         while (ok && sched.next(tile)) {
             const int n0 = tile.n_blk * BN + half * 128;
-            const int row = tile.m0 + row_in_tile;
+            int row = tile.m0 + row_in_tile;
             bool row_valid;
             if (MASKED) row_valid = row_in_tile < tile.rows;
+            else if (KG) row_valid = row < p.M;
             else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
+            if (KG) row += tile.g * p.M;          // d is [G, M, N]
             ok = mbar_wait_warp(tfull_bar, tile_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tile_phase ^= 1;
