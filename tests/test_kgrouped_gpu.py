@@ -57,11 +57,14 @@ def _random_case(M, N, ks, seed):
     return A, B, pack(SFA), pack(SFB), D
 
 
-@pytest.mark.parametrize("per_group", [False, True])
+@pytest.mark.parametrize("mode", ["mn_major", "transposed", "per_group"])
 @pytest.mark.parametrize("M,N,ks", [(128, 256, [128, 384]), (256, 208, [640, 0, 128, 1024]), (384, 512, [512, 512, 256])])
-def test_k_grouped_matches_oracle(M, N, ks, per_group, monkeypatch):
-    """Both host strategies: one launch over all groups (up to 64 groups) and one launch per group."""
-    if per_group:
+def test_k_grouped_matches_oracle(M, N, ks, mode, monkeypatch):
+    """The three host strategies: MN-major operands fed to the tensor core as they are in one launch over all groups
+    (default), K-major copies made by a transposing pre-pass, and one launch per group (more than 64 groups)."""
+    if mode == "transposed":
+        monkeypatch.setenv("B200MOE_KG_MN", "0")
+    elif mode == "per_group":
         monkeypatch.setenv("B200MOE_KG_PER_GROUP", "1")
     A, B, SFA, SFB, D = _random_case(M, N, ks, seed=M + N)
     want = orc.kg_contiguous(A, B, SFA, SFB, ks, D)

@@ -198,7 +198,7 @@ struct MxSched<false, true> {
     static __device__ __forceinline__ int quad_offset(const KgTable& k, int g) { return k.qoff[g]; }
 };
 
-template <bool MASKED, bool KG = false>
+template <bool MASKED, bool KG = false, bool MNMAJOR = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(mx::THREADS, 1)
 gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -206,6 +206,10 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const __grid_constant__ typename KgArg<KG>::type kg) {
     using namespace mx;
     static_assert(!(MASKED && KG), "the k-grouped schedule is a contiguous-layout mode");
+    static_assert(!MNMAJOR || KG, "MN-major operands are the k-grouped layout's");
+    // MNMAJOR: the operands stay as the caller has them, a [K_total, M] and b [K_total, N] (M / N contiguous); a stage
+    // holds 128 K rows x 128 bytes of M (or N), the MMAs read it as an MN-major operand (instruction descriptor bits
+    // 15 and 16) and step 32 K rows = 4096 bytes per instruction.
     using Sched = MxSched<MASKED, KG>;
     if (*flag != 0) return;          // some scale is not a power of two: the promotion kernel handles this call
     extern __shared__ uint8_t smem_raw[];
@@ -307,8 +311,13 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         const uint32_t fb = leader_full_bar + 8 * stage;
                         const bool with_sf = (kb & 3) == 0;
                         if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * (A_STAGE_BYTES + B_STAGE_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0)));
-                        tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, k0 + kb * BK, tile.m0);
-                        tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, k0 + kb * BK, b_row);
+                        if (MNMAJOR) {
+                            tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, tile.m0, k0 + kb * BK);
+                            tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, b_row, k0 + kb * BK);
+                        } else {
+                            tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, k0 + kb * BK, tile.m0);
+                            tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, k0 + kb * BK, b_row);
+                        }
                         if (with_sf) {
                             const int q = kb >> 2;
                             const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
@@ -338,7 +347,8 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bool ok = true;
             const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem_a));
             const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
-            const uint32_t idesc0 = make_idesc_mxf8(2 * BM, BN, 0);
+            const uint32_t idesc0 = make_idesc_mxf8(2 * BM, BN, 0) | (MNMAJOR ? (1u << 15) | (1u << 16) : 0u);
+            constexpr uint64_t KSTEP = MNMAJOR ? (32 * 128) >> 4 : 2;      // descriptor units (16 bytes) per K = 32
             long long tr_te = 0, tr_full = 0, tr_issue = 0;
             while (ok && sched.next(tile)) {
                 if (lane == 0) {
@@ -369,9 +379,9 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
                         const uint64_t bdesc = bdesc0 + stage * (B_STAGE_BYTES >> 4);
                         umma_mxf8_pair(tmem_base, adesc, bdesc, idesc, tsfa, tsfb, kb > 0 ? 1u : 0u);
-                        umma_mxf8_pair(tmem_base, adesc + 2, bdesc + 2, idesc, tsfa, tsfb, 1u);
-                        umma_mxf8_pair(tmem_base, adesc + 4, bdesc + 4, idesc, tsfa, tsfb, 1u);
-                        umma_mxf8_pair(tmem_base, adesc + 6, bdesc + 6, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_base, adesc + KSTEP, bdesc + KSTEP, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_base, adesc + 2 * KSTEP, bdesc + 2 * KSTEP, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_base, adesc + 3 * KSTEP, bdesc + 3 * KSTEP, idesc, tsfa, tsfb, 1u);
                         umma_commit_pair(empty_bar + 8 * stage, 3);
                         if (kb == KBt - 1) umma_commit_pair(tfull_bar, 3);
                         if (p.trace) tr_issue += clock64() - c2;
