@@ -121,9 +121,9 @@ int moe_gg_fp8_masked(const moe_gg_args* args, void* stream);
  * reference's DeepGEMM kernel family (deepgemm_sm100_k_grouped_fp8_gemm_contiguous as exercised by
  * tools/tests/numsim/corpus/kernels/gemm.py:610-702: per-group K cursors, MN-major operands, fp32 accumulation
  * onto the existing D).  `ks` is a HOST array (the shapes of a weight gradient are known on the host);
- * every ks[g] must be a multiple of 128, M % 128 == 0, N % 8 == 0.  This version transposes the operands
- * into K-major scratch (one pass over a and b) and runs the block-scaled kernel once per group on its K
- * window.  workspace: moe_kg_workspace_bytes, 256-byte aligned.                                      */
+ * every ks[g] must be a multiple of 128, M % 128 == 0, N % 16 == 0.  Up to 64 groups run as ONE launch of the
+ * block-scaled kernel that reads a and b as MN-major operands where they are; more groups run one launch per
+ * group on K-major copies made in the workspace.  workspace: moe_kg_workspace_bytes, 256-byte aligned. */
 typedef struct moe_kg_args {
     const void* a;                /* e4m3 [K_total, M] */
     const void* b;                /* e4m3 [K_total, N] */
