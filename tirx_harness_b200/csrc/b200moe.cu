@@ -18,6 +18,7 @@
 #include "moe_ops.cuh"
 #include "alpha_moe.cuh"
 #include "alpha_gemm.cuh"
+#include "alpha_gemv.cuh"
 
 namespace {
 
@@ -458,6 +459,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     return MOE_OK;
 }
 
+constexpr int ALPHA_GEMV_MAX_ROUTES = 160;       // up to 16 tokens x top-10: the CUDA-core pair of kernels
 constexpr bool KG_MN_MAJOR_DEFAULT = true;      // measured 0.96 ms against 1.11 ms with the transposing pre-pass
 constexpr int ALPHA_FUSED_PLAN_MAX_ROUTES = 512;    // measured: the per-warp scan of the route list wins up to a few hundred routes
 constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
@@ -974,6 +976,23 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     DeviceInfo* di = nullptr;      // also raises the kernels' dynamic shared-memory limits, once per device
     rc = device_info(&di);
     if (rc != MOE_OK) return rc;
+    // A handful of tokens: two CUDA-core kernels that stream each routed expert's weights once (alpha_gemv.cuh).
+    // Developer switches: B200MOE_ALPHA_GEMV_MAX_ROUTES=n moves the threshold (0 = never); any B200MOE_ALPHA_PATH
+    // value selects the tensor-core pipeline below.
+    {
+        const char* env_gemv = getenv("B200MOE_ALPHA_GEMV_MAX_ROUTES");
+        const int gemv_max = env_gemv ? atoi(env_gemv) : ALPHA_GEMV_MAX_ROUTES;
+        if (n_pairs <= gemv_max && A->H <= AGV_MAX_H && getenv("B200MOE_ALPHA_PATH") == nullptr) {
+            float* act = w.d2;                  // [n_pairs, 128] fp32, indexed by route
+            CUDA_TRY(launch_pdl(alpha_gemv_gate_up_kernel, dim3(n_pairs * AGV_SLICES), dim3(256), 0, st,
+                                static_cast<const __nv_bfloat16*>(A->hidden), A->topk_ids, static_cast<const uint8_t*>(A->w13),
+                                A->w13_scale, A->top_k, A->E, A->H, act, w.g1));
+            CUDA_TRY(launch_pdl(alpha_gemv_down_kernel, dim3(A->M * (A->H / 32)), dim3(128), 0, st, (const float*)act, A->topk_ids,
+                                A->topk_weights, static_cast<const uint8_t*>(A->w2), A->w2_scale, A->routed_scaling_factor,
+                                A->top_k, A->E, A->H, static_cast<__nv_bfloat16*>(A->out)));
+            return MOE_OK;
+        }
+    }
     const int wpb = 8;
     const int route_blocks = (n_pairs + wpb - 1) / wpb;
     const int quant_blocks = (n_pairs * (A->H / 128) + wpb - 1) / wpb;
