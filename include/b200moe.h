@@ -338,7 +338,8 @@ typedef struct moe_ep_peers {
 } moe_ep_peers;
 
 /* Cross-GPU barrier on `stream`: publishes `epoch` (strictly increasing per call) to every peer and
- * waits, at most 2 s, for theirs; a wait that runs out sets the device status word instead of hanging. */
+ * waits, at most MOE_OPT_EP_WAIT_LIMIT_MS (2 s by default), for theirs; a wait that runs out sets bit 16 of the
+ * device status word (moe_device_status) instead of hanging, and the kernel returns. */
 int moe_ep_barrier(const moe_ep_peers* peers, int32_t rank, int32_t world, int32_t epoch, void* stream);
 
 size_t moe_ep_workspace_bytes(int64_t n_pairs, int32_t E_total);
@@ -376,6 +377,34 @@ int moe_ep_combine(const moe_ep_peers* peers, const int32_t* ids, const int32_t*
  * gate_first as there.  Requires N % 256 == 0. */
 int moe_gg_fp8_gate_up_act(const moe_gg_args* args, void* act_q, float* act_scales, int64_t ss_row, int64_t ss_blk,
                            int32_t gate_first, void* stream);
+
+/* ---- process-wide modes ----------------------------------------------------------------------- */
+/* None is needed for normal use: the defaults are the measured-fastest choices.  Each mode exists because a
+ * test or a measurement selects it; they replace nothing in the reference (its candidates are single kernels).
+ * Values are read once per call, so a change applies from the next call of any thread. */
+#define MOE_OPT_GG_BLOCK_SCALED 0        /* 1 (default): power-of-two scales take the block-scaled-MMA kernels when
+                                          * workspace is given; 0: always the promotion kernel */
+#define MOE_OPT_MX_TILE 1                /* block-scaled kernel: AUTO = CTA pairs for the contiguous layout, one CTA
+                                          * per tile for the masked layout */
+#define MOE_MX_TILE_AUTO 0
+#define MOE_MX_TILE_PAIR 1
+#define MOE_MX_TILE_SINGLE 2
+#define MOE_OPT_ALPHA_PATH 2             /* decode-regime layer: AUTO = two CUDA-core kernels up to the route
+                                          * threshold, else swapped-operand tensor-core kernels; the others force
+                                          * the tensor-core pipeline and choose the tiling of its two projections */
+#define MOE_ALPHA_PATH_AUTO 0
+#define MOE_ALPHA_PATH_SWAP 1
+#define MOE_ALPHA_PATH_MASKED 2          /* both projections as masked-layout grouped GEMMs */
+#define MOE_ALPHA_PATH_MIXED 3           /* masked gate_up, swapped down */
+#define MOE_OPT_ALPHA_GEMV_MAX_ROUTES 3  /* largest M*top_k that takes the CUDA-core kernels (default 160, 0 = never) */
+#define MOE_OPT_KG_MODE 4                /* k-grouped GEMM */
+#define MOE_KG_MODE_MN_MAJOR 0           /* default: one launch, operands read MN-major as the caller has them */
+#define MOE_KG_MODE_TRANSPOSE 1          /* one launch on K-major copies made by a transposing pre-pass */
+#define MOE_KG_MODE_PER_GROUP 2          /* one launch per group (what more than 64 groups always get) */
+#define MOE_OPT_EP_WAIT_LIMIT_MS 5       /* bound of the cross-GPU flag waits of moe_ep_barrier, 1..60000 ms (default 2000) */
+#define MOE_OPT_COUNT_ 6
+int moe_set_option(int32_t option, int32_t value);
+int moe_get_option(int32_t option, int32_t* value);
 
 /* Reads (and clears) the device-side status word of the current device; synchronises the
  * stream first.  0 = no kernel reported a problem.  Non-zero: a bounded wait inside a kernel ran

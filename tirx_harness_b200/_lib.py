@@ -116,11 +116,26 @@ EXPORTS = (
     "moe_kg_workspace_bytes", "moe_kg_fp8_contiguous",
     "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",
     "moe_ep_barrier", "moe_ep_workspace_bytes", "moe_ep_count_publish", "moe_ep_plan", "moe_ep_dispatch",
-    "moe_ep_combine",
+    "moe_ep_combine", "moe_set_option", "moe_get_option",
     "moe_last_error", "moe_version",
 )
 _SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes",
                   "moe_alpha_workspace_bytes", "moe_kg_workspace_bytes")
+
+
+# moe_set_option keys and values (include/b200moe.h)
+OPT_GG_BLOCK_SCALED, OPT_MX_TILE, OPT_ALPHA_PATH, OPT_ALPHA_GEMV_MAX_ROUTES, OPT_KG_MODE, OPT_EP_WAIT_LIMIT_MS = range(6)
+MX_TILE_AUTO, MX_TILE_PAIR, MX_TILE_SINGLE = range(3)
+ALPHA_PATH_AUTO, ALPHA_PATH_SWAP, ALPHA_PATH_MASKED, ALPHA_PATH_MIXED = range(4)
+KG_MODE_MN_MAJOR, KG_MODE_TRANSPOSE, KG_MODE_PER_GROUP = range(3)
+
+
+def set_option(option: int, value: int) -> int:
+    """Sets a process-wide mode and returns the previous value (so a caller can restore it)."""
+    old = ctypes.c_int32(0)
+    check(lib().moe_get_option(ctypes.c_int32(option), ctypes.byref(old)))
+    check(lib().moe_set_option(ctypes.c_int32(option), ctypes.c_int32(value)))
+    return old.value
 
 
 def check(rc: int) -> None:

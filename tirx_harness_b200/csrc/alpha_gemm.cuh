@@ -155,18 +155,18 @@ struct AlphaEpilogue {
         for (int kb = 0; kb < p.KB; ++kb, ++step) {
             const uint32_t acc = step % ACC_BUFS, acc_phase = (step / ACC_BUFS) & 1u;
             const uint32_t slot = step % SF_SLOTS, sphase = (step / SF_SLOTS) & 1u;
-            const long long c0 = p.trace ? clock64() : 0;
+            const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
             ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
-            if (p.trace) tr_tf += clock64() - c0;
+            if (B200_TRACE(p.trace)) tr_tf += clock64() - c0;
             if (!ok) return false;
             tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t(ew * 32) << 16) + acc * ACC_STRIDE;
             uint32_t v0[NC], v1[NC];
             TmemCols<NC>::load(taddr, v0);
             if (PHASE == 1) TmemCols<NC>::load(taddr + NT, v1);
-            const long long c1 = p.trace ? clock64() : 0;
+            const long long c1 = B200_TRACE(p.trace) ? clock64() : 0;
             ok = mbar_wait_warp(sffull_bar + 8 * slot, sphase, abort_flag, status, STATUS_TIMEOUT_SF_FULL);
-            if (p.trace) tr_sf += clock64() - c1;
+            if (B200_TRACE(p.trace)) tr_sf += clock64() - c1;
             if (!ok) {                          // unwinding: the loads above must land before TMEM is freed
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 return false;
@@ -317,7 +317,7 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (p.trace && lane == 0) {
+        if (B200_TRACE(p.trace) && lane == 0) {
             p.trace[blockIdx.x * 8 + 0] = tr_wait;
             p.trace[blockIdx.x * 8 + 1] = clock64() - tr_t0;
         }
@@ -376,7 +376,7 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             acc = __shfl_sync(0xffffffffu, acc, 0);
             acc_phase = __shfl_sync(0xffffffffu, acc_phase, 0);
         }
-        if (p.trace && lane == 0) {
+        if (B200_TRACE(p.trace) && lane == 0) {
             p.trace[blockIdx.x * 8 + 2] = tr_te;
             p.trace[blockIdx.x * 8 + 3] = tr_full;
             p.trace[blockIdx.x * 8 + 4] = tr_issue;
@@ -421,7 +421,7 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             // most decode units hold a handful of rows: drain and promote 16 accumulator columns instead of 32
             ok = u.n_valid <= 16 ? epi.template unit<16>(u) : epi.template unit<32>(u);
         }
-        if (p.trace && warp == 4 && lane == 0) {
+        if (B200_TRACE(p.trace) && warp == 4 && lane == 0) {
             p.trace[blockIdx.x * 8 + 5] = epi.tr_tf;
             p.trace[blockIdx.x * 8 + 6] = epi.tr_sf;
             p.trace[blockIdx.x * 8 + 7] = clock64() - tr_e0;

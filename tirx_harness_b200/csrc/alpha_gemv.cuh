@@ -53,9 +53,14 @@ alpha_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const int* __rest
     const int p = blockIdx.x / AGV_SLICES, slice = blockIdx.x % AGV_SLICES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = H >> 7;
+    // First kernel of a call: its inputs (ids, the token rows) may be the output of whatever ran before it in
+    // the stream -- the previous call's `out`, a router or norm kernel -- so nothing is read before the wait.
+    // Dependents are released only after it: the second kernel reads ids and weights ahead of its own wait,
+    // which is safe exactly because it cannot start before everything older than this kernel has completed.
+    pdl_wait();
     pdl_launch_dependents();
     const int e = __ldg(ids + p);
-    // 1x128 quantisation of the token's row (inputs of the call: no dependence on earlier kernels of the stream)
+    // 1x128 quantisation of the token's row
     const __nv_bfloat16* xrow = x + (long long)(p / top_k) * H;
     for (int b = warp; b < KB; b += 8) {
         float v[4], sc;
@@ -68,7 +73,6 @@ alpha_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const int* __rest
         if (lane == 0) xs[b] = sc;
     }
     __syncthreads();
-    pdl_wait();                                 // act / g1 may still be read by the previous call's second kernel
     if (e < 0 || e >= E) return;
     // warp w: activation features i0, i0+1 of this slice -> 4 rows of W13 (gate i0, up i0, gate i0+1, up i0+1).
     // A 128-K block is 8 consecutive 16-byte chunks = 8 consecutive lanes; 32 lanes cover 4 blocks per round; the
@@ -145,6 +149,8 @@ alpha_gemv_down_kernel(const float* __restrict__ act, const int* __restrict__ id
     const int t = blockIdx.x / tiles, h0 = (blockIdx.x % tiles) * 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
+    // ids / weights are read before the wait below: the gate_up kernel in front of this one releases its dependents
+    // only after everything older in the stream has completed, so they are final by the time this CTA exists.
     if (warp == 0) {
         // lane j owns route j: its place in the order is the number of live routes with a smaller (expert, j)
         const bool have = lane < top_k;

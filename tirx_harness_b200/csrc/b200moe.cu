@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -13,7 +14,7 @@
 #include <mutex>
 
 #include "gg_fp8.cuh"
-#include "gg_fp8_2cta.cuh"
+#include "pair_common.cuh"
 #include "gg_fp8_mx.cuh"
 #include "moe_ops.cuh"
 #include "alpha_moe.cuh"
@@ -26,6 +27,17 @@ using namespace b200;
 
 // Device status word: kernels OR a code into it when a bounded wait runs out.
 __device__ int g_status_word = 0;
+
+// Process-wide modes (moe_set_option).  Plain atomics: a call reads each option once.
+std::atomic<int> g_options[MOE_OPT_COUNT_] = {
+    /* MOE_OPT_GG_BLOCK_SCALED */ {1},
+    /* MOE_OPT_MX_TILE */ {MOE_MX_TILE_AUTO},
+    /* MOE_OPT_ALPHA_PATH */ {MOE_ALPHA_PATH_AUTO},
+    /* MOE_OPT_ALPHA_GEMV_MAX_ROUTES */ {160},
+    /* MOE_OPT_KG_MODE */ {MOE_KG_MODE_MN_MAJOR},
+    /* MOE_OPT_EP_WAIT_LIMIT_MS */ {2000},
+};
+inline int opt(int which) { return g_options[which].load(std::memory_order_relaxed); }
 
 thread_local char g_err[512] = "";
 
@@ -110,6 +122,7 @@ MxLayout mx_layout(int G, long long rows_total, int N, int K) {
 struct DeviceInfo {
     int num_sms = 0;
     int max_pairs = 0;       // CTA pairs (clusters of 2) of the pair kernel that can be resident at once
+    int* status = nullptr;   // device address of g_status_word on this device
     bool attr_set = false;
 };
 
@@ -136,10 +149,6 @@ int device_info(DeviceInfo** out) {
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES_SCATTER));
-        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      gg2::SMEM_BYTES));
-        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      gg2::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -152,14 +161,15 @@ int device_info(DeviceInfo** out) {
                                       mx1::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx1::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute(ep_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, EP_DISPATCH_MAX_SMEM));
         CUDA_TRY(cudaFuncSetAttribute(alpha_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * asw::MAX_E * 4));
         CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<1>::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(alpha_swap_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, asw::Cfg<2>::SMEM_BYTES));
         {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(2 * di.num_sms, 1, 1);
-            cfg.blockDim = dim3(gg2::THREADS, 1, 1);
-            cfg.dynamicSmemBytes = gg2::SMEM_BYTES;
+            cfg.blockDim = dim3(mx::THREADS, 1, 1);
+            cfg.dynamicSmemBytes = mx::SMEM_BYTES;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2;
@@ -168,24 +178,20 @@ int device_info(DeviceInfo** out) {
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, gg_fp8_2cta_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
+            if (cudaOccupancyMaxActiveClusters(&n, gg_fp8_mx_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
                 (void)cudaGetLastError();
                 n = di.num_sms / 2;
             }
             di.max_pairs = n < di.num_sms / 2 ? n : di.num_sms / 2;
-            if (const char* e = getenv("B200MOE_PAIRS")) di.max_pairs = atoi(e);
-            if (getenv("B200MOE_VERBOSE")) fprintf(stderr, "b200moe: %d SMs, occupancy query %d clusters, using %d\n", di.num_sms, n, di.max_pairs);
         }
+        int* sp = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&sp), g_status_word));
+        if (sp == nullptr) return fail(MOE_ERR_CUDA, "cudaGetSymbolAddress returned NULL for the status word");
+        di.status = sp;
         di.attr_set = true;
     }
     *out = &di;
     return MOE_OK;
-}
-
-int* status_ptr() {
-    int* p = nullptr;
-    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word);
-    return p;
 }
 
 template <bool MASKED>
@@ -223,12 +229,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     int rc = device_info(&di);
     if (rc != MOE_OK) return rc;
 
-    // developer switches, read on every call: B200MOE_GG_KERNEL=2cta selects the CTA-pair promotion
-    // kernel (slower: its per-K-block hand-off crosses SMs); B200MOE_GG_MX=0 disables the power-of-two path
-    const char* env_kernel = getenv("B200MOE_GG_KERNEL");
-    const char* env_mx = getenv("B200MOE_GG_MX");
-    const bool use_pair_kernel = env_kernel && strcmp(env_kernel, "2cta") == 0;
-    const bool allow_mx = !(env_mx && strcmp(env_mx, "0") == 0);
+    const bool allow_mx = opt(MOE_OPT_GG_BLOCK_SCALED) != 0;
     CUtensorMap tmap_a, tmap_b;
     if (a->lda != 0 && (a->lda < a->K || a->lda % 16)) return fail(MOE_ERR_INVALID, "lda must be 0 or >= K and a multiple of 16");
     if (a->ldb != 0 && (a->ldb < a->K || a->ldb % 16)) return fail(MOE_ERR_INVALID, "ldb must be 0 or >= K and a multiple of 16");
@@ -236,8 +237,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         return fail(MOE_ERR_UNSUPPORTED, "accumulate needs fp32 output, packed UE8M0 scales and no scattered output");
     rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)rows_total, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
     if (rc != MOE_OK) return rc;
-    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, use_pair_kernel ? gg2::BN / 2 : gg::BN,
-                           (uint64_t)a->ldb);
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, gg::BN, (uint64_t)a->ldb);
     if (rc != MOE_OK) return rc;
 
     GGParams p;
@@ -257,10 +257,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.ldd = a->ldd;
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
     p.d_accumulate = a->accumulate ? 1 : 0;
-    {
-        const char* env_trace = getenv("B200MOE_GG_TRACE");      // developer aid: device address of int64 [grid][8]
-        p.trace = env_trace ? reinterpret_cast<long long*>(strtoull(env_trace, nullptr, 10)) : nullptr;
-    }
+    p.trace = nullptr;
     p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
     p.rows_total = (int)rows_total;
     p.num_n_blocks = (a->N + gg::BN - 1) / gg::BN;
@@ -292,12 +289,13 @@ int launch_gg(const moe_gg_args* a, void* stream) {
                 (int)rows_total, a->N, a->G, p.nb128, ws);
         else
             mx_prep_kernel<<<pgrid, 128, 0, st>>>(a->sfa, a->sfa_stride_row, a->sfa_stride_kblk, a->sfb, (int)rows_total,
-                                                  p.num_k_blocks, a->G, p.nb128, ws);
+                                                  p.num_k_blocks, a->G, p.nb128, ws, a->layout, MASKED ? a->M : 0,
+                                                  p.rows_used);
         CUDA_TRY(cudaGetLastError());
-        const char* env_mxk = getenv("B200MOE_MX_KERNEL");        // "pair" or "single"
         // measured: CTA pairs win on full 256-row blocks (contiguous layout), single CTAs on the masked
         // layout, where a pair multiplies up to 255 empty rows per group
-        const bool mx_single = env_mxk ? strcmp(env_mxk, "single") == 0 : MASKED;
+        const int mx_tile = opt(MOE_OPT_MX_TILE);
+        const bool mx_single = mx_tile == MOE_MX_TILE_AUTO ? MASKED : mx_tile == MOE_MX_TILE_SINGLE;
         CUtensorMap tmap_b2, tmap_sfa, tmap_sfb;
         rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx_single ? mx1::BN : mx::BN / 2,
                                (uint64_t)a->ldb);
@@ -311,28 +309,18 @@ int launch_gg(const moe_gg_args* a, void* stream) {
             int grid1 = (int)(tiles1 < di->num_sms ? tiles1 : di->num_sms);
             if (grid1 < 1) grid1 = 1;
             gg_fp8_mx1_kernel<MASKED><<<grid1, mx1::THREADS, mx1::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
-                                                                                   ws.flag, ml.quads, status_ptr());
+                                                                                   ws.flag, ml.quads, di->status);
         } else {
             const long long row_blocks256 = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
             const long long tiles = row_blocks256 * p.num_n_blocks;
             int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
             if (pairs < 1) pairs = 1;
             gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
-                                                                                   ws.flag, ml.quads, status_ptr(), KgNone{});
+                                                                                   ws.flag, ml.quads, di->status, KgNone{});
         }
         CUDA_TRY(cudaGetLastError());
         p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
         if (packed_sf) return MOE_OK;    // UE8M0 bytes are powers of two by construction: nothing else to run
-    }
-    if (use_pair_kernel && p.scatter_meta == nullptr) {
-        const long long row_blocks = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
-        const long long tiles = row_blocks * p.num_n_blocks;
-        int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
-        if (pairs < 1) pairs = 1;
-        gg_fp8_2cta_kernel<MASKED><<<2 * pairs, gg2::THREADS, gg2::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-            tmap_a, tmap_b, p, status_ptr());
-        CUDA_TRY(cudaGetLastError());
-        return MOE_OK;
     }
     long long max_tiles = MASKED ? (long long)a->G * p.num_m_blocks * p.num_n_blocks
                                  : (long long)p.num_m_blocks * p.num_n_blocks;
@@ -340,9 +328,9 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     if (grid < 1) grid = 1;
     if constexpr (!MASKED) {
         if (p.scatter_meta != nullptr) {
-            if (a->N % 128 != 0) return fail(MOE_ERR_INVALID, "scattered output needs N %% 128 == 0");
+            if (a->N % gg::BN != 0) return fail(MOE_ERR_INVALID, "scattered output needs N %% 256 == 0 (rows leave as 512-byte pieces)");
             gg_fp8_kernel<false, false, true><<<grid, gg::THREADS, gg::SMEM_BYTES_SCATTER, static_cast<cudaStream_t>(stream)>>>(
-                tmap_a, tmap_b, tmap_a, p, status_ptr());
+                tmap_a, tmap_b, tmap_a, p, di->status);
             CUDA_TRY(cudaGetLastError());
             return MOE_OK;
         }
@@ -353,7 +341,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         if (rc != MOE_OK) return rc;
     }
     gg_fp8_kernel<MASKED><<<grid, gg::THREADS, MASKED ? gg::SMEM_BYTES_MASKED : gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-        tmap_a, tmap_b, tmap_a_small, p, status_ptr());
+        tmap_a, tmap_b, tmap_a_small, p, di->status);
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
@@ -433,7 +421,7 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     if (a->ldb != 0 || a->accumulate) return fail(MOE_ERR_UNSUPPORTED, "ldb and accumulate are not supported by the fused-activation GEMM");
     rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)a->M, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
     if (rc != MOE_OK) return rc;
-    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, 64);
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, gg::FUSE_B_BOX_ROWS);
     if (rc != MOE_OK) return rc;
     GGParams p = {};
     p.sfa = a->sfa; p.sfa_sr = a->sfa_stride_row; p.sfa_sk = a->sfa_stride_kblk;
@@ -454,29 +442,26 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
     int grid = (int)(max_tiles < di->num_sms ? max_tiles : di->num_sms);
     if (grid < 1) grid = 1;
     gg_fp8_kernel<false, true><<<grid, gg::THREADS, gg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-        tmap_a, tmap_b, tmap_a, p, status_ptr());
+        tmap_a, tmap_b, tmap_a, p, di->status);
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
 
-constexpr int ALPHA_GEMV_MAX_ROUTES = 160;       // up to 16 tokens x top-10: the CUDA-core pair of kernels
-constexpr bool KG_MN_MAJOR_DEFAULT = true;      // measured 0.96 ms against 1.11 ms with the transposing pre-pass
 constexpr int ALPHA_FUSED_PLAN_MAX_ROUTES = 512;    // measured: the per-warp scan of the route list wins up to a few hundred routes
 constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
 constexpr bool ALPHA_SWAP_DOWN_DEFAULT = true;
 
 // Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream
-// still runs and orders itself with pdl_wait() (ptx.cuh).  B200MOE_PDL=0 falls back to plain launches.
+// still runs and orders itself with pdl_wait() (ptx.cuh).
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    static const bool enabled = [] { const char* e = getenv("B200MOE_PDL"); return !(e && strcmp(e, "0") == 0); }();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = enabled ? 1 : 0;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -843,10 +828,10 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
     if (A->workspace_bytes < need) return fail(MOE_ERR_INVALID, "workspace too small: %zu < %zu bytes", (size_t)A->workspace_bytes, need);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     KgWorkspace w = carve_kg(A->workspace, A->M, A->N, A->K_total);
-    // default: the MN-major operands go to the tensor core as they are; B200MOE_KG_MN=0 selects the transposing pre-pass
-    const bool single_launch = A->G <= 64 && getenv("B200MOE_KG_PER_GROUP") == nullptr;
-    const char* env_mn = getenv("B200MOE_KG_MN");
-    const bool mn_major = single_launch && (env_mn ? strcmp(env_mn, "1") == 0 : KG_MN_MAJOR_DEFAULT) && A->M % 16 == 0;
+    // default: the MN-major operands go to the tensor core as they are (MOE_OPT_KG_MODE selects the other two forms)
+    const int kg_mode = opt(MOE_OPT_KG_MODE);
+    const bool single_launch = A->G <= 64 && kg_mode != MOE_KG_MODE_PER_GROUP;
+    const bool mn_major = single_launch && kg_mode == MOE_KG_MODE_MN_MAJOR && A->M % 16 == 0;
     CUDA_TRY(cudaMemsetAsync(w.layout0, 0, (size_t)A->M * 4, st));        // every row belongs to group 0 of its launch
     if (!mn_major) {
     transpose_u8_kernel<<<dim3((A->M + 127) / 128, (unsigned)(A->K_total / 128)), 256, 0, st>>>(
@@ -908,10 +893,10 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
         if (pairs < 1) pairs = 1;
         if (mn_major)
             gg_fp8_mx_kernel<false, true, true><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, p, ws.flag,
-                                                                                              quads, status_ptr(), kg);
+                                                                                              quads, di->status, kg);
         else
             gg_fp8_mx_kernel<false, true><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tm_a, tm_b, tm_sfa, tm_sfb, p, ws.flag, quads,
-                                                                                        status_ptr(), kg);
+                                                                                        di->status, kg);
         CUDA_TRY(cudaGetLastError());
         return MOE_OK;
     }
@@ -976,13 +961,13 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
     DeviceInfo* di = nullptr;      // also raises the kernels' dynamic shared-memory limits, once per device
     rc = device_info(&di);
     if (rc != MOE_OK) return rc;
-    // A handful of tokens: two CUDA-core kernels that stream each routed expert's weights once (alpha_gemv.cuh).
-    // Developer switches: B200MOE_ALPHA_GEMV_MAX_ROUTES=n moves the threshold (0 = never); any B200MOE_ALPHA_PATH
-    // value selects the tensor-core pipeline below.
+    // A handful of tokens (default: up to 160 routes = 16 tokens x top-10): two CUDA-core kernels that stream each
+    // routed expert's weights once (alpha_gemv.cuh).  MOE_OPT_ALPHA_GEMV_MAX_ROUTES moves the threshold (0 = never);
+    // any MOE_OPT_ALPHA_PATH other than AUTO selects the tensor-core pipeline below.
+    const int alpha_path = opt(MOE_OPT_ALPHA_PATH);
     {
-        const char* env_gemv = getenv("B200MOE_ALPHA_GEMV_MAX_ROUTES");
-        const int gemv_max = env_gemv ? atoi(env_gemv) : ALPHA_GEMV_MAX_ROUTES;
-        if (n_pairs <= gemv_max && A->H <= AGV_MAX_H && getenv("B200MOE_ALPHA_PATH") == nullptr) {
+        const int gemv_max = opt(MOE_OPT_ALPHA_GEMV_MAX_ROUTES);
+        if (n_pairs <= gemv_max && A->H <= AGV_MAX_H && alpha_path == MOE_ALPHA_PATH_AUTO) {
             float* act = w.d2;                  // [n_pairs, 128] fp32, indexed by route
             CUDA_TRY(launch_pdl(alpha_gemv_gate_up_kernel, dim3(n_pairs * AGV_SLICES), dim3(256), 0, st,
                                 static_cast<const __nv_bfloat16*>(A->hidden), A->topk_ids, static_cast<const uint8_t*>(A->w13),
@@ -1001,28 +986,26 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         CUDA_TRY(cudaMemsetAsync(w.counts, 0, (size_t)A->E * 4, st));
         alpha_plan_quant_kernel<<<quant_blocks, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(A->hidden), A->topk_ids, n_pairs,
                                                                  A->top_k, A->E, (int)w.max_m, A->H, w.rows_total, w.counts, w.rowpos,
-                                                                 w.a1, w.s1, status_ptr());
+                                                                 w.a1, w.s1, di->status);
         CUDA_TRY(cudaGetLastError());
     } else {
         CUDA_TRY(launch_pdl(alpha_plan_kernel, dim3(1), dim3(ALPHA_PLAN_THREADS), hist_bytes, st, A->topk_ids, n_pairs, A->E,
-                            (int)w.max_m, w.counts, w.rowpos, status_ptr()));
+                            (int)w.max_m, w.counts, w.rowpos, di->status));
         CUDA_TRY(launch_pdl(alpha_quant_scatter_kernel, dim3(quant_blocks), dim3(wpb * 32), 0, st,
                             static_cast<const __nv_bfloat16*>(A->hidden), w.rowpos, n_pairs, A->top_k, A->H, w.rows_total, w.a1, w.s1));
     }
     (void)route_blocks;
     // The two projections run either as swapped-operand decode kernels (weights = MMA rows, 32 routed rows = MMA
     // columns) or as row-major masked-layout grouped GEMMs (128 x 256 tiles); the intermediates have the same layout
-    // either way.  Developer switch B200MOE_ALPHA_PATH = swap | masked | mixed (masked gate_up, swapped down).
-    const char* env_path = getenv("B200MOE_ALPHA_PATH");
+    // either way.  MOE_OPT_ALPHA_PATH = SWAP | MASKED | MIXED (masked gate_up, swapped down).
     bool swap1 = ALPHA_SWAP_GATE_UP_DEFAULT, swap2 = ALPHA_SWAP_DOWN_DEFAULT;
-    if (env_path) {
-        swap1 = strcmp(env_path, "swap") == 0;
-        swap2 = strcmp(env_path, "swap") == 0 || strcmp(env_path, "mixed") == 0;
+    if (alpha_path != MOE_ALPHA_PATH_AUTO) {
+        swap1 = alpha_path == MOE_ALPHA_PATH_SWAP;
+        swap2 = alpha_path == MOE_ALPHA_PATH_SWAP || alpha_path == MOE_ALPHA_PATH_MIXED;
     }
     // (expert, chunk) units: at most one per expert that has rows plus one per further 32 rows
     const long long unit_bound = (n_pairs < A->E ? n_pairs : A->E) + n_pairs / asw::NT;
-    const char* env_trace = getenv("B200MOE_ALPHA_TRACE");      // developer aid: device address of int64 [2][148][8]
-    long long* trace = env_trace ? reinterpret_cast<long long*>(strtoull(env_trace, nullptr, 10)) : nullptr;
+    long long* trace = nullptr;
     AlphaGemmParams gp{};
     gp.counts = w.counts; gp.E = A->E; gp.max_m = (int)w.max_m; gp.rows_total = w.rows_total;
     gp.a2 = w.a2; gp.s2 = w.s2; gp.g1 = w.g1; gp.d2 = w.d2; gp.H = A->H;
@@ -1036,7 +1019,7 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         gp.s_rows = w.s1; gp.sfb = A->w13_scale; gp.KB = A->H / 128; gp.NF = 1;
         int grid1 = (int)(unit_bound < di->num_sms ? unit_bound : di->num_sms);
         CUDA_TRY(launch_pdl(alpha_swap_kernel<1>, dim3(grid1), dim3(asw::Cfg<1>::THREADS), asw::Cfg<1>::SMEM_BYTES, st, tm_w13, tm_x1,
-                            gp, status_ptr()));
+                            gp, di->status));
     } else {
         moe_gg_args g1 = {};
         g1.a = w.a1; g1.b = A->w13; g1.sfa = w.s1; g1.sfa_stride_row = 1; g1.sfa_stride_kblk = w.rows_total;
@@ -1058,7 +1041,7 @@ int moe_alpha_forward(const moe_alpha_args* A, void* stream) {
         const long long units2 = unit_bound * gp.NF;
         int grid2 = (int)(units2 < di->num_sms ? units2 : di->num_sms);
         CUDA_TRY(launch_pdl(alpha_swap_kernel<2>, dim3(grid2), dim3(asw::Cfg<2>::THREADS), asw::Cfg<2>::SMEM_BYTES, st, tm_w2, tm_x2,
-                            gp, status_ptr()));
+                            gp, di->status));
     } else {
         moe_gg_args g2 = {};
         g2.a = w.a2; g2.b = A->w2; g2.sfa = w.s2; g2.sfa_stride_row = 1; g2.sfa_stride_kblk = w.rows_total;
@@ -1130,7 +1113,11 @@ static EpPeers ep_convert(const moe_ep_peers* P) {
 int moe_ep_barrier(const moe_ep_peers* P, int32_t rank, int32_t world, int32_t epoch, void* stream) {
     int rc = ep_check(P, rank, world);
     if (rc != MOE_OK) return rc;
-    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ep_convert(P), rank, world, epoch, status_ptr());
+    DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
+    const unsigned long long limit_ns = (unsigned long long)opt(MOE_OPT_EP_WAIT_LIMIT_MS) * 1000000ull;
+    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ep_convert(P), rank, world, epoch, limit_ns, di->status);
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
@@ -1174,10 +1161,13 @@ int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int3
     if (!ids || !counts_local || !offsets || !grouped_layout || !dst_base || !pos || !workspace)
         return fail(MOE_ERR_INVALID, "plan pointers must be non-NULL");
     if (workspace_bytes < moe_ep_workspace_bytes(n_pairs, E_total)) return fail(MOE_ERR_INVALID, "EP workspace too small");
+    DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int* chunk_offsets = static_cast<const int*>(workspace);      // left by moe_ep_count_publish
     ep_plan_kernel<<<1, 256, (size_t)2 * E_total * 4, st>>>(P->counts[rank], rank, world, E_total, E_local, align,
-                                                          counts_local, offsets, dst_base);
+                                                          cap_rows, counts_local, offsets, dst_base, di->status);
     CUDA_TRY(cudaGetLastError());
     ep_layout_kernel<<<(cap_rows + 1023) / 1024, 1024, 0, st>>>(offsets, counts_local, E_local, grouped_layout, cap_rows);
     CUDA_TRY(cudaGetLastError());
@@ -1202,23 +1192,20 @@ int moe_ep_dispatch(const moe_ep_peers* P, const void* x_q, const float* x_scale
     if (n_pairs <= 0) return n_pairs == 0 ? MOE_OK : fail(MOE_ERR_INVALID, "n_pairs must be non-negative");
     if (n_pairs % top_k) return fail(MOE_ERR_INVALID, "n_pairs must be a multiple of top_k");
     if (top_k > 32) return fail(MOE_ERR_INVALID, "top_k must be at most 32");
+    if (n_pairs > (1ll << 24)) return fail(MOE_ERR_INVALID, "n_pairs must be at most 2^24 (a row's return address packs the pair index into 24 bits)");
     const long long rec = ((long long)H + H / 32 + 15) & ~15ll;
     if (pitch < rec || pitch % 16) return fail(MOE_ERR_INVALID, "pitch must be >= H + H/32 (rounded up to 16) and a multiple of 16");
     if ((reinterpret_cast<uintptr_t>(x_q) & 15)) return fail(MOE_ERR_INVALID, "x_q must be 16-byte aligned");
     const long long tokens = n_pairs / top_k;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
+    DeviceInfo* di = nullptr;      // also raises the dispatch kernel's dynamic shared-memory limit, once per device
+    rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
     const size_t smem = (size_t)DISPATCH_WARPS * rec;
-    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        CUDA_TRY(cudaFuncSetAttribute(ep_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        attr_done[dev] = true;
-    }
-    if (smem > 64 * 1024) return fail(MOE_ERR_INVALID, "H too large for the dispatch staging buffer");
+    if (smem > (size_t)EP_DISPATCH_MAX_SMEM) return fail(MOE_ERR_INVALID, "H too large for the dispatch staging buffer");
     ep_dispatch_kernel<<<(unsigned)((tokens + DISPATCH_WARPS - 1) / DISPATCH_WARPS), DISPATCH_WARPS * 32, smem,
                          static_cast<cudaStream_t>(stream)>>>(
         ep_convert(P), static_cast<const uint8_t*>(x_q), x_scale, xs_row, xs_blk, ids, pos, n_pairs, top_k, E_local, H,
-        cap_rows, rank, pitch, status_ptr());
+        cap_rows, rank, pitch, di->status);
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }
@@ -1293,6 +1280,28 @@ int moe_permute_plan_static(const int32_t* ids, int64_t n_pairs, int32_t e_lo, i
     plan_place_kernel<<<n_chunks > 0 ? n_chunks : 1, PLAN_CHUNK, hist_bytes, st>>>(
         ids, n_pairs, e_lo, E_local, chunk_counts, counts, offsets, pos, src_pair, grouped_layout, cap_rows);
     CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_set_option(int32_t option, int32_t value) {
+    if (option < 0 || option >= MOE_OPT_COUNT_) return fail(MOE_ERR_INVALID, "unknown option %d", option);
+    bool ok = true;
+    switch (option) {
+        case MOE_OPT_GG_BLOCK_SCALED: ok = value == 0 || value == 1; break;
+        case MOE_OPT_MX_TILE: ok = value >= MOE_MX_TILE_AUTO && value <= MOE_MX_TILE_SINGLE; break;
+        case MOE_OPT_ALPHA_PATH: ok = value >= MOE_ALPHA_PATH_AUTO && value <= MOE_ALPHA_PATH_MIXED; break;
+        case MOE_OPT_ALPHA_GEMV_MAX_ROUTES: ok = value >= 0 && value <= 32768; break;
+        case MOE_OPT_KG_MODE: ok = value >= MOE_KG_MODE_MN_MAJOR && value <= MOE_KG_MODE_PER_GROUP; break;
+        case MOE_OPT_EP_WAIT_LIMIT_MS: ok = value >= 1 && value <= 60000; break;
+    }
+    if (!ok) return fail(MOE_ERR_INVALID, "value %d is out of range for option %d", value, option);
+    g_options[option].store(value, std::memory_order_relaxed);
+    return MOE_OK;
+}
+
+int moe_get_option(int32_t option, int32_t* value) {
+    if (option < 0 || option >= MOE_OPT_COUNT_ || !value) return fail(MOE_ERR_INVALID, "unknown option %d or NULL value", option);
+    *value = opt(option);
     return MOE_OK;
 }
 

@@ -3,7 +3,7 @@
 //   D_g[rows, N] (bf16) = sum over 128-wide K blocks kb of
 //        (A_g[rows, kb] . B_g[N, kb]^T  in e4m3 x e4m3 -> fp32 on tcgen05)  *  sfa[row, kb] * sfb[g, n/128, kb]
 //
-// One persistent CTA per SM, 384 threads, three roles:
+// One persistent CTA per SM, 640 threads (20 warps), four roles:
 //   warp 0        TMA producer: A tile 128 x 128 B and B tile 256 x 128 B per K block into a
 //                 4-stage shared-memory ring (SWIZZLE_128B), completion on mbarriers
 //   warp 1        MMA issuer: four tcgen05.mma (128 x 256 x 32) per K block into one of two
@@ -12,14 +12,17 @@
 //   warp 2        scale loader: per K block the 128 row scales of the tile and the two 128x128
 //                 block scales go from global memory into an 8-slot shared-memory ring, several
 //                 blocks ahead of their use, so the promotion never waits on L2 latency
-//   warps 4..11   two promotion/epilogue warpgroups (128 columns each): per K block they drain
-//                 the TMEM accumulator (tcgen05.ld), apply the block scales
-//                 acc += partial * (sfa * sfb) in registers, hand the TMEM buffer back, and after
-//                 the last K block convert to bf16 and store the valid rows
+//   warps 4..19   sixteen promotion/epilogue warps = four column groups (64 columns each) x the four
+//                 TMEM lane quarters: per K block they drain the TMEM accumulator (tcgen05.ld),
+//                 apply the block scales acc += partial * (sfa * sfb) in registers, hand the TMEM
+//                 buffer back, and after the last K block convert to bf16 and store the valid rows.
+//                 The drain is the step that bounds this kernel (128 KB of TMEM per K block against
+//                 512 tensor-pipe cycles); sixteen warps keep twice as many TMEM loads in flight as
+//                 eight and halve each thread's share.
 // The MMA of K block i+1 runs while block i is being promoted (double-buffered TMEM).
-// FUSE_ACT (gate_up GEMM of a MoE layer): a tile's 256 columns are [up 64 | gate 64] for each of the two
-// warpgroups, so every epilogue thread ends up holding matching gate/up values; it forms silu(gate)*up
-// in fp32, the two warpgroups exchange their 64-column amax through shared memory, and the 128-wide block
+// FUSE_ACT (gate_up GEMM of a MoE layer): a tile's 256 columns are [up 32 | gate 32] for each of the four
+// column groups, so every epilogue thread ends up holding matching gate/up values; it forms silu(gate)*up
+// in fp32, the four groups exchange their 32-column amax through shared memory, and the 128-wide block
 // is requantised to e4m3 with its scale and stored -- the gate_up matrix itself is never written.
 // Every wait is bounded (see mbar_wait_warp); on expiry the CTA unwinds and the host sees a status.
 #pragma once
@@ -39,7 +42,11 @@ constexpr int BN = 256;
 constexpr int BK = 128;              // bytes == elements (fp8)
 constexpr int STAGES = 4;
 constexpr int ACC_STAGES = 2;
-constexpr int THREADS = 384;
+constexpr int EPI_WARPS = 16;                      // promotion / epilogue warps: 4 column groups x 4 TMEM lane quarters
+constexpr int EPI_WARP0 = 4;                       // first of them (warps 0..2: TMA, MMA, scale loader; warp 3 idles)
+constexpr int COL_GROUPS = 4;
+constexpr int GROUP_COLS = BN / COL_GROUPS;        // 64 accumulator columns per epilogue thread
+constexpr int THREADS = 32 * (EPI_WARP0 + EPI_WARPS);   // 640
 constexpr int A_STAGE_BYTES = BM * BK;             // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK;             // 32 KB
 constexpr int TMEM_COLS = 512;
@@ -47,14 +54,15 @@ constexpr int MAX_MASKED_GROUPS = 1024;
 constexpr int SMALL_A_ROWS = 16;                   // masked layout: A box for tiles with at most this many valid rows
 constexpr int SCATTER_STAGES = 3;                  // scattered-output variant: one stage fewer ...
 constexpr int STAGING_ROW_BYTES = 528;             // ... and 128 staging rows of 512 B + 16 B pad (bank-conflict free)
+constexpr int FUSE_B_BOX_ROWS = 32;                // fused activation: B arrives as eight 32-row boxes [up 32 | gate 32] x 4
 constexpr int STAGING_BYTES = 128 * STAGING_ROW_BYTES;
 constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int SF_SLOTS = 8;                        // scale ring: per slot 128 row scales + 2 block scales
 constexpr int SF_SLOT_FLOATS = 132;
 constexpr int OFF_BARS = SMEM_TILE_BYTES;          // mbarriers, TMEM base, abort flag
 constexpr int OFF_SF = OFF_BARS + 512;
-constexpr int OFF_AMAX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;     // fused activation: float [2 parity][2 half][128]
-constexpr int OFF_PREFIX = OFF_AMAX + 2 * 2 * 128 * 4;
+constexpr int OFF_AMAX = OFF_SF + SF_SLOTS * SF_SLOT_FLOATS * 4;     // fused activation: float [2 parity][4 groups][128]
+constexpr int OFF_PREFIX = OFF_AMAX + 2 * COL_GROUPS * 128 * 4;
 // + masked-layout prefix table + slack for 1024-byte alignment
 constexpr int SMEM_BYTES = OFF_PREFIX + (MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
 // masked layout: after prefix[G+1] come the clamped masked_m[G] and a direct (group, row block) table of the
@@ -247,13 +255,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     static_assert(!(SCATTER && (MASKED || FUSE_ACT)), "scattered output exists for the plain contiguous GEMM only");
     using namespace gg;
     // SCATTER trades one pipeline stage for a 128 x 528-byte staging area from which finished rows leave
-    // as 256-byte bulk stores (possibly to another GPU) without holding up the promotion warps.
+    // as 512-byte bulk stores (possibly to another GPU) without holding up the promotion warps.
     constexpr int NSTAGES = SCATTER ? gg::SCATTER_STAGES : gg::STAGES;
     constexpr int TILES_END = NSTAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
     constexpr int BARS_AT = TILES_END + (SCATTER ? gg::STAGING_BYTES : 0);
     constexpr int SF_AT = BARS_AT + 512;
     constexpr int AMAX_AT = SF_AT + SF_SLOTS * SF_SLOT_FLOATS * 4;
-    constexpr int PREFIX_AT = AMAX_AT + 2 * 2 * 128 * 4;
+    constexpr int PREFIX_AT = AMAX_AT + 2 * COL_GROUPS * 128 * 4;
     if (p.mode_flag != nullptr && *p.mode_flag == 0) return;   // the power-of-two-scale path took this call
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms the MMA descriptors address
@@ -263,7 +271,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS_AT);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty,
     // then SF_SLOTS scale-full and SF_SLOTS scale-empty barriers
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1);
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1 + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     float* sf_ring = reinterpret_cast<float*>(smem + SF_AT);
     int* prefix = reinterpret_cast<int*>(smem + PREFIX_AT);
@@ -278,6 +286,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const uint32_t sffull_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES);
     const uint32_t sfempty_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES + SF_SLOTS);
     const uint32_t amax_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
+    const uint32_t stg_bar = amax_bar + 8;            // SCATTER: 4 "row free" + 4 "row filled" barriers, one pair per lane quarter
     float* amax_x = reinterpret_cast<float*>(smem + AMAX_AT);
 
     if (threadIdx.x == 0) {
@@ -287,13 +296,17 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
         for (int s = 0; s < ACC_STAGES; ++s) {
             mbar_init(tfull_bar + 8 * s, 1);
-            mbar_init(tempty_bar + 8 * s, 8);     // one arrival per epilogue warp
+            mbar_init(tempty_bar + 8 * s, EPI_WARPS);     // one arrival per epilogue warp
         }
         for (int s = 0; s < SF_SLOTS; ++s) {
-            mbar_init(sffull_bar + 8 * s, 32);    // every lane of the loader warp arrives
-            mbar_init(sfempty_bar + 8 * s, 8);    // one arrival per epilogue warp
+            mbar_init(sffull_bar + 8 * s, 32);            // every lane of the loader warp arrives
+            mbar_init(sfempty_bar + 8 * s, EPI_WARPS);    // one arrival per epilogue warp
         }
-        mbar_init(amax_bar, 256);                 // every epilogue thread, once per tile
+        mbar_init(amax_bar, EPI_WARPS * 32);              // every epilogue thread, once per tile
+        for (int q = 0; q < 4; ++q) {
+            mbar_init(stg_bar + 8 * q, 1);                // the group-0 warp of the quarter
+            mbar_init(stg_bar + 8 * (4 + q), COL_GROUPS); // one arrival per column group of the quarter
+        }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
@@ -311,8 +324,12 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 
     const int KB = p.num_k_blocks;
 
-    if (warp < 4) {
-        setmaxnreg_dec<88>();
+    // Register budget.  Warps sit on the SM's four sub-partitions by warp index modulo 4: each holds one of warps
+    // 0..3 and four epilogue warps.  The launch gives every warp 96 registers per thread (5 x 96 = 480 per lane and
+    // sub-partition); 64 + 4 x 104 = 480 re-divides exactly that, so setmaxnreg.inc never waits for registers
+    // that cannot come.
+    if (warp < EPI_WARP0) {
+        setmaxnreg_dec<64>();
         if (warp == 0) {
             // ------------------------------------------------ TMA producer
             Scheduler<MASKED> sched(p, prefix, lane);
@@ -335,14 +352,15 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         tma_load_2d(smem_u32(smem_a + stage * A_STAGE_BYTES), small_a ? &tmap_a_small : &tmap_a, fb, kb * BK,
                                     tile.m0);
                         if (FUSE_ACT) {
-                            // tmap_b has a 64-row box here: [up 64 | gate 64] for each warpgroup
+                            // tmap_b has a 32-row box here: [up 32 | gate 32] for each of the four column groups
                             const int up0 = tile.g * p.N + (p.gate_first ? p.inter : 0) + tile.n_blk * 128;
                             const int gate0 = tile.g * p.N + (p.gate_first ? 0 : p.inter) + tile.n_blk * 128;
                             const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
-                            tma_load_2d(sb, &tmap_b, fb, kb * BK, up0);
-                            tma_load_2d(sb + 64 * BK, &tmap_b, fb, kb * BK, gate0);
-                            tma_load_2d(sb + 128 * BK, &tmap_b, fb, kb * BK, up0 + 64);
-                            tma_load_2d(sb + 192 * BK, &tmap_b, fb, kb * BK, gate0 + 64);
+#pragma unroll
+                            for (int cg = 0; cg < COL_GROUPS; ++cg) {
+                                tma_load_2d(sb + (2 * cg) * FUSE_B_BOX_ROWS * BK, &tmap_b, fb, kb * BK, up0 + cg * FUSE_B_BOX_ROWS);
+                                tma_load_2d(sb + (2 * cg + 1) * FUSE_B_BOX_ROWS * BK, &tmap_b, fb, kb * BK, gate0 + cg * FUSE_B_BOX_ROWS);
+                            }
                         } else {
                             tma_load_2d(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
                         }
@@ -365,36 +383,43 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
         } else if (warp == 1) {
             // ------------------------------------------------ MMA issuer
+            // The tile sequence is computed by the whole warp; a tile's K loop is run by lane 0 alone with
+            // single-thread waits: every instruction between "accumulator handed back" and "MMA issued" is a
+            // bubble in the tensor pipe, and a warp-wide vote per wait is such a bubble.
             Scheduler<MASKED> sched(p, prefix, lane);
             Tile tile;
             constexpr uint32_t idesc = make_idesc_e4m3_f32(BM, BN);
+            const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem_a));
+            const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             while (ok && sched.next(tile)) {
-                for (int kb = 0; kb < KB; ++kb) {
-                    ok = mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status,
-                                        STATUS_TIMEOUT_TMEM_EMPTY);
-                    if (!ok) break;
-                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status,
-                                        STATUS_TIMEOUT_SMEM_FULL);
-                    if (!ok) break;
-                    tc_fence_after();
-                    if (lane == 0) {
-                        const uint64_t adesc = make_smem_desc_sw128(smem_u32(smem_a + stage * A_STAGE_BYTES));
-                        const uint64_t bdesc = make_smem_desc_sw128(smem_u32(smem_b + stage * B_STAGE_BYTES));
+                if (lane == 0) {
+                    for (int kb = 0; kb < KB; ++kb) {
+                        ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                        if (!ok) break;
+                        ok = mbar_wait_thread(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
+                        const uint64_t bdesc = bdesc0 + stage * (B_STAGE_BYTES >> 4);
                         const uint32_t tmem_d = tmem_base + acc * BN;
-#pragma unroll
-                        for (int k = 0; k < BK / 32; ++k) {
-                            // advance 32 bytes of K inside the 128-byte swizzled row: +2 in 16-byte units
-                            umma_f8f6f4(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
-                        }
+                        // advance 32 bytes of K inside the 128-byte swizzled row: +2 in 16-byte units
+                        umma_f8f6f4(tmem_d, adesc, bdesc, idesc, 0u);
+                        umma_f8f6f4(tmem_d, adesc + 2, bdesc + 2, idesc, 1u);
+                        umma_f8f6f4(tmem_d, adesc + 4, bdesc + 4, idesc, 1u);
+                        umma_f8f6f4(tmem_d, adesc + 6, bdesc + 6, idesc, 1u);
                         umma_commit(empty_bar + 8 * stage);   // stage reusable once the MMAs have read it
                         umma_commit(tfull_bar + 8 * acc);     // accumulator of this K block complete
+                        if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
+                        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                     }
-                    __syncwarp();
-                    if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
-                    if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                 }
+                ok = __all_sync(0xffffffffu, ok);
+                stage = __shfl_sync(0xffffffffu, stage, 0);
+                phase = __shfl_sync(0xffffffffu, phase, 0);
+                acc = __shfl_sync(0xffffffffu, acc, 0);
+                acc_phase = __shfl_sync(0xffffffffu, acc_phase, 0);
             }
         } else if (warp == 2) {
             // ------------------------------------------------ scale loader
@@ -433,56 +458,55 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
         }
     } else {
         // ---------------------------------------------------- promotion + epilogue
-        setmaxnreg_inc<208>();
-        const int ew = warp - 4;
-        const int quarter = warp & 3;                 // TMEM lanes this warp may touch
-        const int half = ew >> 2;                     // which 128 columns of the 256-wide tile
+        setmaxnreg_inc<104>();
+        const int quarter = warp & 3;                       // TMEM lanes this warp may touch: [32 quarter, +32)
+        const int cg = (warp - EPI_WARP0) >> 2;             // which 64 columns of the 256-wide tile
         const int row_in_tile = quarter * 32 + lane;
         Scheduler<MASKED> sched(p, prefix, lane);
         Tile tile;
-        uint32_t acc = 0, acc_phase = 0, slot = 0, sphase = 0, act_phase = 0;
+        uint32_t acc = 0, acc_phase = 0, slot = 0, sphase = 0, act_phase = 0, stg_phase = 0;
         bool ok = true;
         while (ok && sched.next(tile)) {
-            const int n0 = tile.n_blk * BN + half * 128;
+            const int n0 = tile.n_blk * BN + cg * GROUP_COLS;
             const int row = tile.m0 + row_in_tile;
             bool row_valid;
             if (MASKED) row_valid = row_in_tile < tile.rows;
             else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
-            unsigned long long accr[64];          // 128 fp32 accumulators as f32x2 pairs
+            unsigned long long accr[GROUP_COLS / 2];      // 64 fp32 accumulators as f32x2 pairs
 #pragma unroll
-            for (int j = 0; j < 64; ++j) accr[j] = 0ull;
+            for (int j = 0; j < GROUP_COLS / 2; ++j) accr[j] = 0ull;
 
             for (int kb = 0; kb < KB; ++kb) {
                 ok = mbar_wait_warp(sffull_bar + 8 * slot, sphase, abort_flag, status, STATUS_TIMEOUT_SF_FULL);
                 if (!ok) break;
                 const float* sfp = sf_ring + slot * SF_SLOT_FLOATS;
                 const float sa_row = sfp[row_in_tile];
-                const float s = sa_row * sfp[128 + (FUSE_ACT ? 0 : half)];
+                // plain: columns [64 cg, +64) lie in 128-column block cg / 2.  fused: first half up, second half gate.
+                const float s = sa_row * sfp[128 + (FUSE_ACT ? 0 : (cg >> 1))];
                 const float sg = FUSE_ACT ? sa_row * sfp[129] : s;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sfempty_bar + 8 * slot);
                 if (++slot == SF_SLOTS) { slot = 0; sphase ^= 1; }
                 const unsigned long long s2 = pack_f32x2(s, s);
-                const unsigned long long s2g = pack_f32x2(sg, sg);     // columns 64..127 (gate) when fused
+                const unsigned long long s2g = pack_f32x2(sg, sg);     // columns 32..63 (gate) when fused
 
                 ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status,
                                     STATUS_TIMEOUT_TMEM_FULL);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + half * 128;
-                // eight 16-column chunks, double-buffered: chunk c+1 is in flight while chunk c is
+                const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + cg * GROUP_COLS;
+                // four 16-column chunks, double-buffered: chunk c+1 is in flight while chunk c is
                 // multiplied in (two fp32 FMAs per instruction)
                 uint32_t v0[16], v1[16];
                 tmem_ld_32x32b_x16(taddr, v0);
 #pragma unroll
-                for (int c = 0; c < 8; c += 2) {
+                for (int c = 0; c < 4; c += 2) {
                     tmem_ld_wait(v0);
                     tmem_ld_32x32b_x16(taddr + (c + 1) * 16, v1);
 #pragma unroll
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[c * 8 + j], v0[2 * j], v0[2 * j + 1], c < 4 ? s2 : s2g);
+                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[c * 8 + j], v0[2 * j], v0[2 * j + 1], c < 2 ? s2 : s2g);
                     tmem_ld_wait(v1);
-                    if (c + 2 < 8) {
+                    if (c + 2 < 4) {
                         tmem_ld_32x32b_x16(taddr + (c + 2) * 16, v0);
                     } else {
                         // all loads have landed: hand the accumulator back to the MMA warp
@@ -491,36 +515,36 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
                     }
 #pragma unroll
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[(c + 1) * 8 + j], v1[2 * j], v1[2 * j + 1], c + 1 < 4 ? s2 : s2g);
+                    for (int j = 0; j < 8; ++j) fma_f32x2(accr[(c + 1) * 8 + j], v1[2 * j], v1[2 * j + 1], c + 1 < 2 ? s2 : s2g);
                 }
                 if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
             }
             if (!ok) break;
             if (FUSE_ACT) {
-                // accr[0..32) = up columns, accr[32..64) = gate columns of this warpgroup's 64 activations
+                // accr[0..16) = up columns, accr[16..32) = gate columns of this group's 32 activations
                 float amax = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < 16; ++j) {
                     float u0, u1, g0, g1;
                     unpack_f32x2(accr[j], u0, u1);
-                    unpack_f32x2(accr[32 + j], g0, g1);
+                    unpack_f32x2(accr[16 + j], g0, g1);
                     const float a0 = __fmul_rn(silu_f32(g0), u0), a1 = __fmul_rn(silu_f32(g1), u1);
                     amax = fmaxf(amax, fmaxf(fabsf(a0), fabsf(a1)));
                     accr[j] = pack_f32x2(a0, a1);
                 }
-                // the 128-wide quantisation block spans both warpgroups: swap the 64-column maxima
-                amax_x[(act_phase * 2 + half) * 128 + row_in_tile] = amax;
+                // the 128-wide quantisation block spans the four column groups: exchange the 32-column maxima
+                amax_x[(act_phase * COL_GROUPS + cg) * 128 + row_in_tile] = amax;
                 mbar_arrive(amax_bar);
                 ok = mbar_wait_warp(amax_bar, act_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
                 if (!ok) break;
-                amax = fmaxf(amax, amax_x[(act_phase * 2 + (half ^ 1)) * 128 + row_in_tile]);
+#pragma unroll
+                for (int o = 0; o < COL_GROUPS; ++o) amax = fmaxf(amax, amax_x[(act_phase * COL_GROUPS + o) * 128 + row_in_tile]);
                 act_phase ^= 1;
                 const float sc = __fdiv_rn(fmaxf(amax, 1.0e-8f), 448.0f);
                 if (row_valid) {
-                    uint8_t* qrow = p.act_q + (long long)row * p.inter + tile.n_blk * 128 + half * 64;
+                    uint8_t* qrow = p.act_q + (long long)row * p.inter + tile.n_blk * 128 + cg * 32;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
+                    for (int j = 0; j < 16; j += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -532,13 +556,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         }
                         *reinterpret_cast<uint4*>(qrow + j * 2) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    if (half == 0) p.act_s[(long long)row * p.act_ss_r + (long long)tile.n_blk * p.act_ss_b] = sc;
+                    if (cg == 0) p.act_s[(long long)row * p.act_ss_r + (long long)tile.n_blk * p.act_ss_b] = sc;
                 }
             } else
             if (row_valid && p.d_f32) {
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
-                for (int j = 0; j < 128; j += 4) {
+                for (int j = 0; j < GROUP_COLS; j += 4) {
                     if (n0 + j + 4 <= p.N) {
                         float4 o;
                         unpack_f32x2(accr[j / 2], o.x, o.y);
@@ -547,26 +571,43 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     }
                 }
             } else if (SCATTER) {
-                // this thread's 128 columns -> its own 256-byte slice of the staging row -> one bulk store
-                uint8_t* stg = smem + TILES_END + row_in_tile * gg::STAGING_ROW_BYTES + half * 256;
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // previous tile's store has read it
+                // The four column groups of a lane quarter fill one 512-byte staging row per output row (128 bytes
+                // each); the group-0 warp then sends every row with one bulk store.  Two mbarriers per quarter order
+                // "previous store has read the row" -> fill -> send; their waits are bounded like every other.
+                uint8_t* stg_row = smem + TILES_END + row_in_tile * gg::STAGING_ROW_BYTES;
+                const uint32_t free_bar = stg_bar + 8 * quarter, filled_bar = stg_bar + 8 * (4 + quarter);
+                if (cg == 0) {
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // previous tile's store has read it
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(free_bar);
+                } else {
+                    ok = mbar_wait_warp(free_bar, stg_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+                    if (!ok) break;
+                }
 #pragma unroll
-                for (int j = 0; j < 128; j += 8) {
+                for (int j = 0; j < GROUP_COLS; j += 8) {
                     uint4 out;
                     out.x = cvt_bf16x2(accr[j / 2 + 0]);
                     out.y = cvt_bf16x2(accr[j / 2 + 1]);
                     out.z = cvt_bf16x2(accr[j / 2 + 2]);
                     out.w = cvt_bf16x2(accr[j / 2 + 3]);
-                    *reinterpret_cast<uint4*>(stg + j * 2) = out;
+                    *reinterpret_cast<uint4*>(stg_row + cg * (GROUP_COLS * 2) + j * 2) = out;
                 }
                 fence_proxy_async_smem();
-                if (row_valid) {
-                    const int meta = __ldg(p.scatter_meta + row);
-                    __nv_bfloat16* drow = p.scatter_base[(meta >> 24) & 7] + (long long)(meta & 0xFFFFFF) * p.ldd + n0;
-                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;"
-                                 ::"l"(drow), "r"(smem_u32(stg)) : "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(filled_bar);
+                if (cg == 0) {
+                    ok = mbar_wait_warp(filled_bar, stg_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+                    if (!ok) break;
+                    if (row_valid) {
+                        const int meta = __ldg(p.scatter_meta + row);
+                        __nv_bfloat16* drow = p.scatter_base[(meta >> 24) & 7] + (long long)(meta & 0xFFFFFF) * p.ldd + tile.n_blk * BN;
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 512;"
+                                     ::"l"(drow), "r"(smem_u32(stg_row)) : "memory");
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                stg_phase ^= 1;
             } else if (row_valid) {
                 __nv_bfloat16* drow;
                 if (p.scatter_meta != nullptr) {
@@ -576,7 +617,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
                 }
 #pragma unroll
-                for (int j = 0; j < 128; j += 8) {
+                for (int j = 0; j < GROUP_COLS; j += 8) {
                     if (n0 + j + 8 <= p.N) {
                         uint4 out;
                         out.x = cvt_bf16x2(accr[j / 2 + 0]);

@@ -16,7 +16,7 @@
 //                      one accumulator drain per tile by the 8 epilogue warps of each CTA
 #pragma once
 
-#include "gg_fp8_2cta.cuh"
+#include "pair_common.cuh"
 
 namespace b200 {
 
@@ -56,16 +56,27 @@ __device__ __forceinline__ uint32_t ue8m0_of(float s, int* bad) {
 }
 
 // grid.x covers rows_total rounded up to 128, grid.y = quads (SFA); the tail blocks of grid.x beyond
-// that handle SFB.  One thread per (row, quad).
+// that handle SFB.  One thread per (row, quad).  Rows whose output is never stored -- padding rows
+// (negative layout entry), rows past *rows_used, masked-out rows (row >= masked_m[g]) -- usually hold
+// uninitialised scales in real callers: they get the neutral byte and cannot veto the fast path.
 __global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, long long sfa_sk,
                                const float* __restrict__ sfb, int rows_total, int KB, int G, int nb128,
-                               MxWorkspace ws) {
+                               MxWorkspace ws, const int* __restrict__ layout, int masked_max_m,
+                               const int* __restrict__ rows_used) {
     int bad = 0;
     const int q = blockIdx.y;
     if ((int)blockIdx.x < ws.row_blocks) {
         const int r = blockIdx.x * 128 + threadIdx.x;
         uint32_t word = 0x7F7F7F7Fu;
-        if (r < rows_total) {
+        bool live = r < rows_total;
+        if (live) {
+            if (masked_max_m > 0) live = (r % masked_max_m) < __ldg(layout + r / masked_max_m);
+            else {
+                const int g = __ldg(layout + r);
+                live = g >= 0 && g < G && (rows_used == nullptr || r < __ldg(rows_used));
+            }
+        }
+        if (live) {
             word = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -302,10 +313,10 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int sfb_chunk = ((KG ? 0 : tile.g * p.nb128) + tile.n_blk * 2) * quads + q0;  // first of the two column blocks
                 const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
                 for (int kb = 0; kb < KBt; ++kb) {
-                    const long long c0 = p.trace ? clock64() : 0;
+                    const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
                                         STATUS_TIMEOUT_SMEM_EMPTY);
-                    if (p.trace) tr_wait += clock64() - c0;
+                    if (B200_TRACE(p.trace)) tr_wait += clock64() - c0;
                     if (!ok) break;
                     if (lane == 0) {
                         const uint32_t fb = leader_full_bar + 8 * stage;
@@ -332,7 +343,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
-            if (p.trace && lane == 0) {
+            if (B200_TRACE(p.trace) && lane == 0) {
                 p.trace[blockIdx.x * 8 + 0] = tr_wait;
                 p.trace[blockIdx.x * 8 + 1] = clock64() - tr_t0;
             }
@@ -353,14 +364,14 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             while (ok && sched.next(tile)) {
                 if (lane == 0) {
                     // the single accumulator must have been drained by both CTAs' epilogues
-                    const long long c0 = p.trace ? clock64() : 0;
+                    const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
                     ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
-                    if (p.trace) tr_te += clock64() - c0;
+                    if (B200_TRACE(p.trace)) tr_te += clock64() - c0;
                     const int KBt = Sched::k_blocks(kg, tile.g, KB);
                     for (int kb = 0; ok && kb < KBt; ++kb) {
-                        const long long c1 = p.trace ? clock64() : 0;
+                        const long long c1 = B200_TRACE(p.trace) ? clock64() : 0;
                         ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                        const long long c2 = p.trace ? clock64() : 0;
+                        const long long c2 = B200_TRACE(p.trace) ? clock64() : 0;
                         tr_full += c2 - c1;
                         if (!ok) break;
                         tc_fence_after();
@@ -384,7 +395,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         umma_mxf8_pair(tmem_base, adesc + 3 * KSTEP, bdesc + 3 * KSTEP, idesc, tsfa, tsfb, 1u);
                         umma_commit_pair(empty_bar + 8 * stage, 3);
                         if (kb == KBt - 1) umma_commit_pair(tfull_bar, 3);
-                        if (p.trace) tr_issue += clock64() - c2;
+                        if (B200_TRACE(p.trace)) tr_issue += clock64() - c2;
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
                     tile_phase ^= 1;
@@ -395,7 +406,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 tile_phase = __shfl_sync(0xffffffffu, tile_phase, 0);
                 qcount = __shfl_sync(0xffffffffu, qcount, 0);
             }
-            if (p.trace && lane == 0) {
+            if (B200_TRACE(p.trace) && lane == 0) {
                 p.trace[blockIdx.x * 8 + 2] = tr_te;
                 p.trace[blockIdx.x * 8 + 3] = tr_full;
                 p.trace[blockIdx.x * 8 + 4] = tr_issue;

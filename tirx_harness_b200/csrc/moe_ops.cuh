@@ -443,9 +443,11 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 }
 
 // Cross-GPU barrier: thread s publishes `epoch` into peer s's flag slot for this rank, then waits
-// (bounded: 2 s) until peer s's epoch shows up in the local slot.  Launched after the kernel whose
-// peer stores must be visible; __threadfence_system orders them before the flag.
-__global__ void ep_barrier_kernel(EpPeers peers, int rank, int world, int epoch, int* status) {
+// (bounded: `limit_ns` of wall time, 2 s unless the host set another limit) until peer s's epoch shows up
+// in the local slot; a wait that runs out ORs STATUS_TIMEOUT_PEER_FLAG into the status word and returns.
+// Launched after the kernel whose peer stores must be visible; __threadfence_system orders them before the flag.
+__global__ void ep_barrier_kernel(EpPeers peers, int rank, int world, int epoch, unsigned long long limit_ns,
+                                  int* status) {
     const int s = threadIdx.x;
     if (s >= world) return;
     __threadfence_system();
@@ -453,7 +455,7 @@ __global__ void ep_barrier_kernel(EpPeers peers, int rank, int world, int epoch,
     const int* mine = peers.flags[rank] + s;
     const uint64_t t0 = globaltimer_ns();
     while (ld_acquire_sys(mine) < epoch) {
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             atomicOr(status, STATUS_TIMEOUT_PEER_FLAG);
             break;
         }
@@ -473,9 +475,11 @@ __global__ void ep_publish_counts_kernel(EpPeers peers, const int* __restrict__ 
 //   recv side: offsets[E_local+1] of this rank's experts (each padded to `align` rows)
 //   send side: dst_base[E_total] = first destination row, in the owner's buffer, of this rank's
 //              pairs for expert e (owner's expert start + rows of lower-ranked senders)
+// If the rows this rank is about to receive (aligned) exceed its capacity, STATUS_CAPACITY is raised: the
+// dispatch kernels of the senders drop the rows that do not fit.
 __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int rank, int world, int E_total,
-                               int E_local, int align, int* __restrict__ counts_local,
-                               int* __restrict__ offsets, int* __restrict__ dst_base) {
+                               int E_local, int align, int cap_rows, int* __restrict__ counts_local,
+                               int* __restrict__ offsets, int* __restrict__ dst_base, int* status) {
     extern __shared__ int sh[];           // total[E_total], start[E_total]
     int* total = sh;
     int* start = sh + E_total;
@@ -493,7 +497,10 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int rank, int
             start[e] = run;
             run += (total[e] + align - 1) / align * align;
         }
-        if (d == rank) offsets[E_local] = run;
+        if (d == rank) {
+            offsets[E_local] = run;
+            if (run > cap_rows) atomicOr(status, STATUS_CAPACITY);
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E_total; e += blockDim.x) {
@@ -533,6 +540,7 @@ __global__ void ep_layout_kernel(const int* __restrict__ offsets, const int* __r
 // load of the e4m3 row + the scales) and leaves as ONE bulk store of H + H/32 bytes per destination, issued
 // by lane j for destination j.  NVLink then carries large packets instead of 16-byte stores.
 constexpr int DISPATCH_WARPS = 4;
+constexpr int EP_DISPATCH_MAX_SMEM = 64 * 1024;
 __global__ void ep_dispatch_kernel(EpPeers peers, const uint8_t* __restrict__ x, const float* __restrict__ xs,
                                    long long xs_r, long long xs_b, const int* __restrict__ ids,
                                    const int* __restrict__ pos, long long n_pairs, int top_k, int E_local,
@@ -572,6 +580,7 @@ __global__ void ep_dispatch_kernel(EpPeers peers, const uint8_t* __restrict__ x,
     if (lane < top_k) {
         const long long p = t * top_k + lane;
         const int row = __ldg(pos + p);
+        if (row >= cap_rows) atomicOr(status, STATUS_CAPACITY);       // the owner's buffer is too small: row dropped
         if (row >= 0 && row < cap_rows) {
             const int d = __ldg(ids + p) / E_local;
             uint8_t* dst = peers.a[d] + (long long)row * pitch;

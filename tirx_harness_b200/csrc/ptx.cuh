@@ -19,7 +19,16 @@ enum : int {
     STATUS_TIMEOUT_SF_FULL = 1 << 5,      // epilogue: block scales never arrived in shared memory
     STATUS_TIMEOUT_SF_EMPTY = 1 << 6,     // scale loader: ring slot never released
     STATUS_BAD_ARGUMENT = 1 << 8,
+    STATUS_CAPACITY = 1 << 9,             // exchange: more rows were routed to a rank than its receive buffer holds
 };
+
+// Per-role wait-cycle counters (the `trace` pointers of the kernel parameter blocks) are compiled in only by a
+// developer build with -DB200MOE_DEV_TRACE; the library as shipped never reads or writes through them.
+#ifdef B200MOE_DEV_TRACE
+#define B200_TRACE(ptr) ((ptr) != nullptr)
+#else
+#define B200_TRACE(ptr) false
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

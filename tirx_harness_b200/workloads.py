@@ -113,3 +113,70 @@ def zipf_group_sizes(G: int, total_rows: int, s: float = 1.2):
     for i in order[:rem]:
         base[i] += 1
     return base
+
+
+def pack_ue8m0_words(scales: torch.Tensor) -> torch.Tensor:
+    """Power-of-two fp32 scales [..., kb] -> int32 words [..., ceil(kb/4)]: byte j of word q is the biased exponent
+    of K block 4q+j (the packing of tools/tests/numsim/corpus/kernels/gemm.py:252-263); missing blocks hold 2^0."""
+    bits = scales.contiguous().view(torch.int32)
+    if bool((bits & 0x807FFFFF).ne(0).any()):
+        raise ValueError("scales must be positive powers of two")
+    codes = (bits >> 23) & 0xFF
+    pad = -codes.shape[-1] % 4
+    if pad:
+        codes = torch.nn.functional.pad(codes, (0, pad), value=127)
+    c = codes.view(*codes.shape[:-1], -1, 4)
+    return (c[..., 0] | (c[..., 1] << 8) | (c[..., 2] << 16) | (c[..., 3] << 24)).to(torch.int32)
+
+
+def registered_actual_ms(G: int, expected_m: int, seed: int):
+    """Rows per group of a registered grouped_gemm/fp8 row.  The reference draws them with `make_actual_ms` of the
+    un-vendored tirx-kernels package; this stand-in uses the law of the public DeepGEMM generator it was ported
+    from: uniform in [0.7, 1.3] x expected_m per group, seeded."""
+    import random
+    rng = random.Random(seed)
+    return [int(expected_m * rng.uniform(0.7, 1.3)) for _ in range(G)]
+
+
+def make_registered_case(G, expected_m, N, K, seed=0, alignment=224, device="cpu", actual_ms=None):
+    """The registered workload's tensor contract (evolution/tasks/grouped_gemm_fp8.yaml:15-21): K-major A [M,K] and
+    B [G,N,K] in e4m3, UE8M0 scales packed four per int32 and stored MN-major -- SFA [M, K/512] with strides (1, M),
+    SFB [G, N, K/512] with strides (N*K/512, 1, N), one B scale per COLUMN (constant over each 128-column block) --
+    groups padded to `alignment` rows with -1 in grouped_layout, D bf16 [M,N].  The fp32 form of the same scales
+    comes along as SFA_f32 [M,K/128] / SFB_f32 [G,N/128,K/128] for oracles and comparators."""
+    if actual_ms is None:
+        actual_ms = registered_actual_ms(G, expected_m, seed)
+    gl, aligned, M = contiguous_layout(actual_ms, alignment)
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    kb, nb = K // 128, (N + 127) // 128
+    sfa = torch.exp2(torch.randint(-4, 1, (M, kb), generator=gen, device=dev).float())
+    sfb = torch.exp2(torch.randint(-4, 1, (G, nb, kb), generator=gen, device=dev).float())
+    a = torch.empty((M, K), dtype=torch.float8_e4m3fn, device=dev)
+    for r0 in range(0, M, 4096):
+        r1 = min(M, r0 + 4096)
+        x = torch.randn((r1 - r0, K), generator=gen, device=dev)
+        a[r0:r1] = quantize_with_scales(x, sfa[r0:r1].repeat_interleave(128, dim=1))
+    b = torch.empty((G, N, K), dtype=torch.float8_e4m3fn, device=dev)
+    for g in range(G):
+        x = torch.randn((N, K), generator=gen, device=dev)
+        b[g] = quantize_with_scales(x, sfb[g].repeat_interleave(128, dim=0)[:N].repeat_interleave(128, dim=1))
+    gl = gl.to(dev)
+    a.view(torch.uint8)[gl < 0] = 0
+    sfa_words = pack_ue8m0_words(sfa).t().contiguous().t()                              # [M, K/512], MN-major
+    sfb_col = sfb.repeat_interleave(128, dim=1)[:, :N]                                    # [G, N, K/128]
+    sfb_words = pack_ue8m0_words(sfb_col).permute(0, 2, 1).contiguous().permute(0, 2, 1)  # [G, N, K/512], N fastest
+    return dict(A=a, B=b, SFA=sfa_words, SFB=sfb_words, D=torch.zeros((M, N), dtype=torch.bfloat16, device=dev),
+                grouped_layout=gl, actual_ms=tuple(actual_ms), aligned_ms=tuple(aligned), alignment=alignment,
+                SFA_f32=sfa, SFB_f32=sfb, G=G, M=M, N=N, K=K)
+
+
+def output_views(d: torch.Tensor, actual_ms, aligned_ms):
+    """Per-group views of the valid rows of D, as the reference's `output_views` forms them
+    (tasks/grouped_gemm_fp8/baseline.py:21-27): padding rows are outside every view."""
+    views, start = [], 0
+    for actual, aligned in zip(actual_ms, aligned_ms):
+        views.append(d.narrow(0, start, actual))
+        start += aligned
+    return tuple(views)
