@@ -528,6 +528,12 @@ ORC_API void orc_combine(const uint16_t* y, const int32_t* pos, const float* w, 
         }
 }
 
+/* Sets the number of OpenMP threads the following calls use (a launcher such as torchrun exports
+ * OMP_NUM_THREADS=1 to its ranks, which would otherwise time a one-thread baseline). */
+ORC_API void orc_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -60,6 +60,11 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """Number of OpenMP threads of the following oracle calls (launchers export OMP_NUM_THREADS=1 to their ranks)."""
+    lib().orc_set_num_threads(_c.c_int(int(n)))
+
+
 # ---------------------------------------------------------------- codecs
 def e4m3_decode(bits) -> np.ndarray:
     b = _c_arr(bits, np.uint8)

@@ -17,3 +17,16 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return GOLDEN
+
+
+@pytest.fixture
+def moe_option():
+    """set(option, value): a process-wide mode of the CUDA library (moe_set_option) for the length of one test."""
+    from tirx_harness_b200 import _lib
+    saved = []
+
+    def set_(option, value):
+        saved.append((option, _lib.set_option(option, value)))
+    yield set_
+    for option, old in reversed(saved):
+        _lib.set_option(option, old)

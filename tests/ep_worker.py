@@ -77,6 +77,10 @@ def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="push"):
     gf = got.float().cpu().numpy()
     rms = np.sqrt(((gf - r) ** 2).mean()) / np.sqrt((r**2).mean())
     assert rms <= 5e-3, rms
+    # (c) the stage-by-stage check the benchmark runs after its timed region (collective over the ranks)
+    from oracle import checks
+    chk = checks.ep_layer_check(layer, loc, world, rank, tokens=32, rows=32, experts=2)
+    assert chk["ok"] and chk["ok_this_rank"], chk
     layer.close()
     if world > 1:
         dist.barrier()

@@ -232,13 +232,45 @@ def moe_routing():
                         weights_dense=ns["weights"].numpy(), rsf=np.float32(2.5))
 
 
+def moe_task_layer():
+    """Runs the registered `moe` task's own operator (`run` of tasks/moe/definition.json, fixed DeepSeek-V3 geometry)
+    on the seeded inputs of tests/util.py:moe_task_inputs and stores what it returns; the inputs themselves (1.4 GB of
+    weights) are regenerated from the seed by the tests."""
+    import torch
+    sys.path.insert(0, os.path.dirname(os.path.dirname(OUT)))
+    from tests.util import moe_task_inputs
+    d = json.load(open(os.path.join(
+        REF, "evolution/benchmark/flashinfer_bench_evolve/tasks/moe/definition.json")))
+    ns: dict = {}
+    exec(compile(d["reference"], "moe/definition.json:reference", "exec"), ns)
+    T, seed = 16, 2024
+    x = moe_task_inputs(T, seed)
+    fp8 = lambda a: torch.from_numpy(a).view(torch.float8_e4m3fn)
+    out = ns["run"](torch.from_numpy(x["routing_logits"]), torch.from_numpy(x["routing_bias"]).bfloat16(),
+                    fp8(x["hidden_states"]), torch.from_numpy(x["hidden_states_scale"]),
+                    fp8(x["gemm1_weights"]), torch.from_numpy(x["gemm1_weights_scale"]),
+                    fp8(x["gemm2_weights"]), torch.from_numpy(x["gemm2_weights_scale"]),
+                    x["local_expert_offset"], x["routed_scaling_factor"])
+    import hashlib
+    digest = hashlib.sha256(b"".join(np.ascontiguousarray(x[k]).tobytes() for k in (
+        "routing_logits", "routing_bias", "hidden_states", "hidden_states_scale", "gemm1_weights_scale",
+        "gemm2_weights_scale"))).hexdigest()
+    np.savez_compressed(os.path.join(OUT, "moe_task_layer.npz"), T=np.int32(T), seed=np.int32(seed),
+                        out_bits=out.view(torch.int16).numpy().view(np.uint16),
+                        small_inputs_sha256=np.frombuffer(bytes.fromhex(digest), np.uint8))
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 2 and sys.argv[2] == "moe_task_layer":     # 20 GB of host memory, half a minute
+        moe_task_layer()
+        raise SystemExit
     ref = _load_gemm_helpers()
     moe_routing()
     cvt_goldens()
     codec_and_gemm(ref)
     alphamoe_oracle()
     alphamoe_bf16_layer()
+    moe_task_layer()
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(OUT, f)))

@@ -1,5 +1,6 @@
 """Decode-regime MoE layer (the reference's `alphamoe` workload) on the GPU, through the C ABI, against the
 CPU oracle's restatement of the task's definition.json and against the fixture its own `run` produced."""
+import ctypes
 import os
 
 import numpy as np
@@ -8,6 +9,7 @@ import pytest
 import torch
 
 from oracle import oracle as orc
+from tirx_harness_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 
@@ -70,7 +72,9 @@ def _check_against_oracle(c, op, data, M):
                               routed_scaling_factor=c["rsf"])
     it = op.intermediates()
     tok = res["order"] // top_k
-    two_kernel_path = M * top_k <= 160 and os.environ.get("B200MOE_ALPHA_PATH") is None
+    path = ctypes.c_int32(0)
+    _lib.check(_lib.lib().moe_get_option(_lib.OPT_ALPHA_PATH, ctypes.byref(path)))
+    two_kernel_path = M * top_k <= 160 and path.value == _lib.ALPHA_PATH_AUTO
     if two_kernel_path:
         # a handful of tokens: no plan, no gathered rows; the fp32 gate_up rows are stored per route
         g1 = it["g1"].cpu().numpy()[res["order"]]
@@ -110,19 +114,19 @@ def _check_against_oracle(c, op, data, M):
                                                 (33, 2048, 48, 10, 0.0),
                                                 (256, 256, 64, 10, 0.0)])      # above 512 routes: separate plan kernel
 @pytest.mark.parametrize("pipeline", ["default", "tensor"])
-def test_alpha_layer_matches_oracle(M, H, E, top_k, skew, pipeline, monkeypatch):
+def test_alpha_layer_matches_oracle(M, H, E, top_k, skew, pipeline, moe_option):
     """default: two CUDA-core kernels up to 160 routes, the tensor-core pipeline above; tensor: always the latter."""
     if pipeline == "tensor":
-        monkeypatch.setenv("B200MOE_ALPHA_PATH", "swap")
+        moe_option(_lib.OPT_ALPHA_PATH, _lib.ALPHA_PATH_SWAP)
     c = _case(M, H, E, top_k, seed=100 + M, rsf=1.0 if M % 2 else 2.5, skew=skew)
     op, data = _run_gpu(c, M)
     _check_against_oracle(c, op, data, M)
 
 
 @pytest.mark.parametrize("pipeline", ["default", "tensor"])
-def test_alpha_layer_matches_reference_fixture(golden_dir, pipeline, monkeypatch):
+def test_alpha_layer_matches_reference_fixture(golden_dir, pipeline, moe_option):
     if pipeline == "tensor":
-        monkeypatch.setenv("B200MOE_ALPHA_PATH", "swap")
+        moe_option(_lib.OPT_ALPHA_PATH, _lib.ALPHA_PATH_SWAP)
     g = np.load(os.path.join(golden_dir, "alphamoe_bf16_layer.npz"))
     M = g["hidden_bits"].shape[0]
     hs = torch.from_numpy(g["hidden_bits"].view(np.int16).copy()).view(torch.bfloat16)
@@ -186,7 +190,7 @@ def test_alpha_layer_full_size_row_m128_properties():
     assert torch.equal(data2["output"].float(), 2.0 * out1)
 
 
-def test_alpha_small_m_two_kernel_path_agrees_with_tensor_pipeline(monkeypatch):
+def test_alpha_small_m_two_kernel_path_agrees_with_tensor_pipeline(moe_option):
     """Official geometry (K=2048, I=128, E=512, top-10) at M=8: the two-kernel CUDA-core path and the tensor-core
     pipeline compute the same products with different fp32 summation orders: almost all outputs equal to the bit,
     the rest within a bf16 step or two of each other."""
@@ -209,7 +213,7 @@ def test_alpha_small_m_two_kernel_path_agrees_with_tensor_pipeline(monkeypatch):
     c["w2"], c["s2"] = quant(w2)
     _, data = _run_gpu(c, M)
     fast = data["output"].float().clone()
-    monkeypatch.setenv("B200MOE_ALPHA_PATH", "swap")
+    moe_option(_lib.OPT_ALPHA_PATH, _lib.ALPHA_PATH_SWAP)
     _, data2 = _run_gpu(c, M)
     ref = data2["output"].float()
     assert torch.isfinite(fast).all() and fast.abs().max() > 0
@@ -226,3 +230,41 @@ def test_alpha_layer_rejects_unsupported_shapes():
     c["s2"] = np.concatenate([c["s2"], c["s2"]], axis=2)
     with pytest.raises(_lib.B200MoeError):
         _run_gpu(c, 4)
+
+
+@pytest.mark.parametrize("M", [4, 16])
+def test_chained_calls_read_their_predecessors_output(M):
+    """Two layers back to back on one stream, the second one's tokens being the first one's output (what a decoder
+    stack does): the kernels are launched with programmatic stream serialisation, so a kernel that read its inputs
+    before waiting for its predecessor would see stale rows.  Checked over several rounds with changing inputs."""
+    from tirx_harness_b200 import alpha_moe, grouped_gemm
+    dev = torch.device("cuda:0")
+    H, E, top_k = 512, 16, 4
+    c1, c2 = _case(M, H, E, top_k, seed=900 + M, rsf=2.0), _case(M, H, E, top_k, seed=950 + M, rsf=1.0)
+
+    def bind(c, hidden, ids, wts):
+        data = {"hidden_states": hidden, "topk_ids": ids, "topk_weights": wts,
+                "gemm1_weights": _dev(c["w13"], dev).view(torch.float8_e4m3fn), "gemm1_weights_scale": _dev(c["s13"], dev),
+                "gemm2_weights": _dev(c["w2"], dev).view(torch.float8_e4m3fn), "gemm2_weights_scale": _dev(c["s2"], dev),
+                "top_k": top_k, "routed_scaling_factor": c["rsf"],
+                "output": torch.zeros((M, H), dtype=torch.bfloat16, device=dev)}
+        return alpha_moe.setup(data, M), data
+    h0 = c1["hs"].to(dev)
+    op1, d1 = bind(c1, h0, torch.from_numpy(c1["ids"]).to(dev), torch.from_numpy(c1["w"]).to(dev))
+    op2, d2 = bind(c2, d1["output"], torch.from_numpy(c2["ids"]).to(dev), torch.from_numpy(c2["w"]).to(dev))
+    for rnd in range(4):
+        h0.copy_((c1["hs"].float() * (1.0 + 0.5 * rnd)).bfloat16())
+        d1["output"].fill_(7.0)                # stale rows a premature read would pick up
+        d2["output"].fill_(float("nan"))
+        op1()
+        op2()
+        torch.cuda.synchronize()
+        assert grouped_gemm.device_status() == 0
+        mid = _bits(d1["output"])
+        want = orc.alpha_moe_layer(mid, c2["ids"], c2["w"], c2["w13"], c2["s13"], c2["w2"], c2["s2"],
+                                   routed_scaling_factor=c2["rsf"])
+        got = orc.bf16_to_f32(_bits(d2["output"]))
+        ref = orc.bf16_to_f32(want["out"])
+        bound = np.maximum(0.02 + 0.02 * np.abs(ref), 2.0 * want["abs_sum"] * 2.0**-7)
+        assert np.isfinite(got).all() and (np.abs(got - ref) <= bound).all(), rnd
+        assert (_bits(d2["output"]) == want["out"]).mean() > 0.9

@@ -30,3 +30,44 @@ def test_ep_layer_multi_gpu(world, combine):
     r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-4000:]
     assert r.stdout.count("EP layer ok") == world
+
+
+def test_barrier_wait_runs_out_and_reports_instead_of_hanging():
+    """A peer that never publishes its flag: with the wait limit set to a few milliseconds the barrier kernel
+    returns, the device status word carries the peer-flag timeout bit, the status clears, and the device keeps
+    working.  (The failing side is made on the host: rank 1's slot is a buffer of this process that nothing
+    writes; no fault, no trap, no endless loop.)"""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import ctypes
+    import time
+    from tirx_harness_b200 import _lib, grouped_gemm
+    L = _lib.lib()
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")        # this rank's flag slots (slot 1 is never written)
+    other = torch.zeros(64, dtype=torch.int32, device="cuda")       # stands in for the absent peer's buffer
+    dummy = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peers = _lib.EpPeers()
+    for r, flags in enumerate((mine, other)):
+        peers.a[r] = peers.sa[r] = peers.y[r] = peers.counts[r] = peers.meta[r] = dummy.data_ptr()
+        peers.flags[r] = flags.data_ptr()
+    assert grouped_gemm.device_status() == 0
+    old = _lib.set_option(_lib.OPT_EP_WAIT_LIMIT_MS, 5)
+    try:
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        t0 = time.perf_counter()
+        _lib.check(L.moe_ep_barrier(ctypes.byref(peers), 0, 2, 1, st))
+        out = ctypes.c_int32(0)
+        rc = L.moe_device_status(ctypes.byref(out), st)              # synchronises the stream
+        waited = time.perf_counter() - t0
+    finally:
+        _lib.set_option(_lib.OPT_EP_WAIT_LIMIT_MS, old)
+    assert rc == -3 and out.value == 1 << 4, (rc, out.value)          # MOE_ERR_DEVICE, STATUS_TIMEOUT_PEER_FLAG
+    assert waited < 1.0, waited
+    assert int(other[0].item()) == 1                                 # our own epoch was published before the wait
+    assert grouped_gemm.device_status() == 0                         # read-and-clear: the word is clean again
+    # the context is intact: a barrier of a world of one completes at once, and ordinary work runs
+    _lib.check(L.moe_ep_barrier(ctypes.byref(peers), 0, 1, 2, st))
+    assert grouped_gemm.device_status() == 0
+    assert int((torch.arange(8, device="cuda") * 2).sum().item()) == 56
+    with pytest.raises(_lib.B200MoeError):
+        _lib.set_option(_lib.OPT_EP_WAIT_LIMIT_MS, 0)

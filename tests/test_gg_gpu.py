@@ -12,6 +12,7 @@ import pytest
 import torch
 
 from oracle import oracle as orc
+from tirx_harness_b200 import _lib
 from tests.util import assert_bf16_close, bf16_bits, npf, rel_err, u8
 
 pytestmark = pytest.mark.gpu
@@ -247,7 +248,7 @@ def test_full_size_properties_config1(gg):
     assert torch.equal(D2[2 * mpg:], D1[2 * mpg:])
 
 
-def test_power_of_two_scale_path_equals_promotion_path(gg, monkeypatch):
+def test_power_of_two_scale_path_equals_promotion_path(gg):
     """With 2^e scales the block-scaled-MMA path and the promotion path compute the same exact products in
     fp32; both must sit within tolerance of the oracle and agree with each other to fp32 rounding.  With one
     scale that is not a power of two the fast path must stand down (decided on the device, per call)."""
@@ -266,13 +267,13 @@ def test_power_of_two_scale_path_equals_promotion_path(gg, monkeypatch):
         assert np.isnan(outs[name][~valid]).all()
         assert rel_err(outs[name][valid], ref32[valid]) <= TOL
     assert rel_err(outs["mx"][valid], outs["promote"][valid]) <= 1e-4
-    # env switch forces the promotion kernel even with workspace: bit-identical to the no-workspace run
-    monkeypatch.setenv("B200MOE_GG_MX", "0")
+    # MOE_OPT_GG_BLOCK_SCALED = 0 forces the promotion kernel even with workspace: bit-identical to the no-workspace run
+    old = _lib.set_option(_lib.OPT_GG_BLOCK_SCALED, 0)
     d32 = torch.zeros(dev["D"].shape, dtype=torch.float32, device="cuda")
     launch = gg.bind_contiguous(dev["A"], dev["SFA"], dev["B"], dev["SFB"], d32, dev["grouped_layout"])
     launch()
     np.testing.assert_array_equal(d32.cpu().numpy()[valid], outs["promote"][valid])
-    monkeypatch.delenv("B200MOE_GG_MX")
+    _lib.set_option(_lib.OPT_GG_BLOCK_SCALED, old)
     # one non-power-of-two scale: the same bound launch must now give the promotion result for the new scales
     dev["SFA"][5, 3] = 0.3
     launch()

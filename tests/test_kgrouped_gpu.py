@@ -59,13 +59,14 @@ def _random_case(M, N, ks, seed):
 
 @pytest.mark.parametrize("mode", ["mn_major", "transposed", "per_group"])
 @pytest.mark.parametrize("M,N,ks", [(128, 256, [128, 384]), (256, 208, [640, 0, 128, 1024]), (384, 512, [512, 512, 256])])
-def test_k_grouped_matches_oracle(M, N, ks, mode, monkeypatch):
+def test_k_grouped_matches_oracle(M, N, ks, mode, moe_option):
     """The three host strategies: MN-major operands fed to the tensor core as they are in one launch over all groups
     (default), K-major copies made by a transposing pre-pass, and one launch per group (more than 64 groups)."""
+    from tirx_harness_b200 import _lib
     if mode == "transposed":
-        monkeypatch.setenv("B200MOE_KG_MN", "0")
+        moe_option(_lib.OPT_KG_MODE, _lib.KG_MODE_TRANSPOSE)
     elif mode == "per_group":
-        monkeypatch.setenv("B200MOE_KG_PER_GROUP", "1")
+        moe_option(_lib.OPT_KG_MODE, _lib.KG_MODE_PER_GROUP)
     A, B, SFA, SFB, D = _random_case(M, N, ks, seed=M + N)
     want = orc.kg_contiguous(A, B, SFA, SFB, ks, D)
     launch, d = _run(A, B, SFA, SFB, ks, D)

@@ -252,3 +252,28 @@ def test_k_grouped_oracle_matches_the_reference_case_expectation():
     out = orc.kg_contiguous(A, B, SFA, SFB, ks, D)
     np.testing.assert_array_equal(out[0], np.float32(1.25 + ks[0]))
     np.testing.assert_array_equal(out[1], np.float32(-2.5 + 2 * ks[1]))
+
+
+def test_moe_task_layer_against_the_reference_run(golden_dir):
+    """The registered `moe` task's own operator (tasks/moe/definition.json `run`, executed by
+    tests/golden/make_golden.py at the task's fixed geometry, T=16) against this repository's layer oracle on the
+    same seeded inputs.  The reference keeps the intermediate in fp32 where the layer requantises it to e4m3, so
+    the comparison is the task's own gate (compare_moe_outputs) plus the size of that requantisation noise."""
+    from tests.util import moe_output_gate, moe_task_inputs
+    g = np.load(os.path.join(golden_dir, "moe_task_layer.npz"))
+    T = int(g["T"])
+    x = moe_task_inputs(T, int(g["seed"]))
+    rid, rw = orc.route_deepseek(x["routing_logits"], x["routing_bias"], routed_scaling_factor=x["routed_scaling_factor"])
+    full = orc.moe_layer(x["hidden_states"], np.ascontiguousarray(x["hidden_states_scale"].T), None, x["gemm1_weights"],
+                         x["gemm1_weights_scale"], x["gemm2_weights"], x["gemm2_weights_scale"], top_k=8,
+                         e_lo=x["local_expert_offset"], routes=(rid, rw), model=orc.BLOCK_PROMOTE)
+    got = orc.bf16_to_f32(full["out"])
+    ref = orc.bf16_to_f32(g["out_bits"])
+    assert full["plan"]["counts"].sum() > 0          # some routes are local
+    ok, note, stats = moe_output_gate(got, ref)
+    assert ok, note
+    assert stats["rms_ratio"] < 0.05, stats          # e4m3 requantisation of the intermediate: a few percent
+    assert stats["token_matched"] == 1.0
+    # tokens without a local route are exactly zero in both
+    local = ((rid >= x["local_expert_offset"]) & (rid < x["local_expert_offset"] + 32)).any(axis=1)
+    assert (ref[~local] == 0).all() and (got[~local] == 0).all()

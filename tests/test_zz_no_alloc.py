@@ -47,6 +47,13 @@ def test_static_plan_matches_workspace_plan_on_two_calls_in_a_row():
         assert grouped_gemm.device_status() == 0
         for k in ("counts", "offsets", "pos", "src_pair", "grouped_layout"):
             assert torch.equal(got[k], ref[k]), k                  # integer outputs: exact
+    # an empty batch right after a full one: the counters the earlier calls left in the built-in array are never read
+    empty = torch.zeros((0, 8), dtype=torch.int32, device="cuda")
+    rc, got = _plan_static(L, empty, 0, 16, 128, 16 * 128)
+    assert rc == 0, L.moe_last_error().decode()
+    assert grouped_gemm.device_status() == 0
+    assert not got["counts"].any() and not got["offsets"].any()
+    assert (got["grouped_layout"] == -1).all() and (got["src_pair"] == -1).all()
 
 
 def test_static_plan_rejects_requests_beyond_its_built_in_scratch():
