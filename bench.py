@@ -573,7 +573,7 @@ def run_layer(args, world, rank, device, barrier, steps, warmup):
     cfg = LAYER_SMALL if getattr(args, "layer_small", False) else LAYER
     data = _layer_case(world, rank, device, cfg)
     Tl = cfg["T"] // world
-    layer = ep_layer.setup(data, Tl, top_k=cfg["top_k"], combine=args.combine)
+    layer = ep_layer.setup(data, Tl, top_k=cfg["top_k"], combine=args.combine, dispatch=args.dispatch, fuse_act=args.fuse_act)
     timer = Timer(device, world, barrier)
     for _ in range(max(warmup, 3)):
         layer()
@@ -662,7 +662,7 @@ def run_layer(args, world, rank, device, barrier, steps, warmup):
         "config": {"workload": cfg["desc"], "tokens_per_rank": Tl, "experts_per_rank": cfg["E"] // world,
                    "routing": "softmax top-8, ties to lowest index, weights renormalised",
                    "l2": "weights (1.4-11 GB per rank) larger than L2, no flush", "rows_this_rank": int(counts),
-                   "combine": args.combine},
+                   "combine": args.combine, "dispatch": args.dispatch, "fuse_act": bool(args.fuse_act)},
         "clocks": clocks.summary(),
         "e2e": {"value": cfg["T"] / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps, "serial_ms_per_step": serial_ms,
@@ -710,8 +710,10 @@ def _alpha_comparator(data, M, timer_graph):
 
     def launch():
         xq, xs = quant(hs)
+        # the installed flashinfer takes the routes packed: (expert id << 16) | bf16 bits of the weight
+        packed = (ids << 16) | (wts.to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF)
         return trtllm_fp8_block_scale_routed_moe(
-            topk_ids=(ids, wts), routing_bias=None, hidden_states=xq, hidden_states_scale=xs.t().contiguous(),
+            topk_ids=packed, routing_bias=None, hidden_states=xq, hidden_states_scale=xs.t().contiguous(),
             gemm1_weights=w13s, gemm1_weights_scale=s13s, gemm2_weights=w2, gemm2_weights_scale=s2,
             num_experts=w13.shape[0], top_k=top_k, n_group=None, topk_group=None, intermediate_size=w2.shape[2],
             local_expert_offset=0, local_num_experts=w13.shape[0], routed_scaling_factor=1.0, routing_method_type=5,
@@ -1157,6 +1159,9 @@ def main():
     ap.add_argument("--no-comparators", action="store_true", help="do not time the installed DeepGEMM / flashinfer kernels")
     ap.add_argument("--combine", choices=["pull", "push"], default="push",
                     help="layer workload: how expert outputs travel back (see ep_layer.EpMoeLayer)")
+    ap.add_argument("--dispatch", choices=["fused", "kernel"], default="fused",
+                    help="layer workload: dispatch all-to-all inside the gate_up GEMM (default) or as its own kernel + barrier")
+    ap.add_argument("--fuse-act", action="store_true", help="layer workload: SiLU*mul requant inside the gate_up GEMM's epilogue")
     ap.add_argument("--layer-small", action="store_true", help="layer workload at 2048 tokens / 32 experts (profiling)")
     ap.add_argument("--alpha-rows", type=int, nargs="*", default=None,
                     help="alpha workload: row sizes to run instead of the six official ones (profiling)")

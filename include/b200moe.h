@@ -326,7 +326,7 @@ int moe_ipc_close(void* ptr);
  *   sa     = a + H: scales of (row r, block b) at sa[r*pitch/4 + b]
  *   y      bf16 [cap_rows, H]       down-GEMM output rows
  *   counts int32 [world, E_total]   row s = number of pairs rank s routes to each expert
- *   flags  int32 [world]            barrier epochs
+ *   flags  int32 [64 + E_local]     [0, world): barrier epochs; [64, 64 + E_local): arrival counters of the local experts
  *   meta   int32 [cap_rows]         (source rank << 24) | source pair index of each received row           */
 typedef struct moe_ep_peers {
     void* a[8];
@@ -352,17 +352,49 @@ int moe_ep_count_publish(const moe_ep_peers* peers, const int32_t* ids, int64_t 
 /* Step 2 (after that barrier): from the gathered counts derive the receive side (counts_local[E_local],
  * offsets[E_local+1], grouped_layout[cap_rows]) and the send side (dst_base[E_total], pos[n_pairs] =
  * destination row of every pair inside its owner's buffer; rows are ordered by source rank, then by pair
- * order, so the result is independent of timing).  `workspace` must be the one step 1 used. */
+ * order, so the result is independent of timing).  send_order (int32 [n_pairs], may be NULL): this rank's pairs in
+ * the order moe_ep_gate_up_dispatch sends them -- by local expert index first, destination rank second, pair order
+ * inside -- so that every rank's first expert is complete first.  `workspace` must be the one step 1 used. */
 int moe_ep_plan(const moe_ep_peers* peers, const int32_t* ids, int64_t n_pairs, int32_t rank, int32_t world,
                 int32_t E_total, int32_t E_local, int32_t align, int32_t cap_rows, int32_t* counts_local,
-                int32_t* offsets, int32_t* grouped_layout, int32_t* dst_base, int32_t* pos, void* workspace,
-                size_t workspace_bytes, void* stream);
+                int32_t* offsets, int32_t* grouped_layout, int32_t* dst_base, int32_t* pos, int32_t* send_order,
+                void* workspace, size_t workspace_bytes, void* stream);
 
 /* Dispatch all-to-all fused with the permutation: every pair's e4m3 row and scales are stored directly
  * into the owner rank's grouped-layout buffers, together with the row's return address (meta). */
 int moe_ep_dispatch(const moe_ep_peers* peers, const void* x_q, const float* x_scale, int64_t xs_row, int64_t xs_blk,
                     const int32_t* ids, const int32_t* pos, int64_t n_pairs, int32_t top_k, int32_t E_local, int32_t H,
                     int32_t cap_rows, int64_t pitch, int32_t rank, int32_t world, void* stream);
+
+/* gate_up grouped GEMM that carries the dispatch all-to-all itself (ONE kernel: the transfer overlaps the GEMM tile
+ * by tile and needs neither moe_ep_dispatch nor the barrier behind it).  One warp of every CTA stores this rank's
+ * token records into the owners' receive buffers in `send_order`, and counts each row into the owner's arrival
+ * counter of its expert once the store has completed; the GEMM's loader warps wait, per expert and with the usual
+ * 2 s bound, until counts_local[expert] rows have arrived, then multiply them.  The counters live at
+ * peers->flags[r] + 64 (int32 [E_local]); moe_ep_count_publish clears them at the start of every forward.
+ *   gemm   the gate_up GEMM over this rank's receive buffer exactly as moe_gg_fp8_contiguous would get it
+ *          (a = peers->a[rank], lda = pitch, sfa = peers->sa[rank], rows_used = offsets + E_local, G = E_local,
+ *          M = cap_rows, fp32 scales, bf16 d); no workspace: the promotion kernel runs
+ *   act_q  NULL: plain bf16 output to gemm->d.  Non-NULL: SiLU*mul + 1x128 requant in the epilogue, as
+ *          moe_gg_fp8_gate_up_act (then act_scales / ss_row / ss_blk / gate_first as there)
+ * Every rank of the group must call it in the same forward (the waits are for the other ranks' sends).  No peer
+ * memory is ever read: peer traffic is bulk stores, plain stores and reductions.  The reference has no multi-GPU
+ * path; this is the exchange behind its single-GPU `local_expert_offset` emulation. */
+typedef struct moe_ep_send_args {
+    const moe_ep_peers* peers;
+    const void* x_q;                /* e4m3 [T_local, H] */
+    const float* x_scale;           /* scale of (t, block b) at x_scale[t*xs_row + b*xs_blk] */
+    int64_t xs_row, xs_blk;
+    const int32_t* ids;             /* [n_pairs] */
+    const int32_t* pos;             /* [n_pairs], from moe_ep_plan */
+    const int32_t* send_order;      /* [n_pairs], from moe_ep_plan */
+    const int32_t* counts_local;    /* [E_local], from moe_ep_plan */
+    int64_t n_pairs;
+    int64_t pitch;
+    int32_t top_k, E_local, H, cap_rows, rank, world;
+} moe_ep_send_args;
+int moe_ep_gate_up_dispatch(const moe_gg_args* gemm, const moe_ep_send_args* send, void* act_q, float* act_scales,
+                            int64_t ss_row, int64_t ss_blk, int32_t gate_first, void* stream);
 
 /* Combine all-to-all fused with the weighted sum: each token loads its top_k expert rows from the owners'
  * y buffers and accumulates w * row in fp32 (slot order), writing bf16. */

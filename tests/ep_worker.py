@@ -29,7 +29,7 @@ def build_global(T, H, I, E, seed):
                 gemm2_weights_scale=s2 * 0.05)
 
 
-def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="push"):
+def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="push", dispatch="fused"):
     import torch.distributed as dist
     from tirx_harness_b200 import ep_layer, grouped_gemm, moe_layer
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -47,7 +47,7 @@ def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="push"):
                gemm1_weights=g["gemm1_weights"][esl].cuda(), gemm1_weights_scale=g["gemm1_weights_scale"][esl].cuda(),
                gemm2_weights=g["gemm2_weights"][esl].cuda(), gemm2_weights_scale=g["gemm2_weights_scale"][esl].cuda(),
                output=torch.full((Tl, H), float("nan"), dtype=torch.bfloat16, device="cuda"))
-    layer = ep_layer.setup(loc, Tl, top_k=top_k, combine=combine)
+    layer = ep_layer.setup(loc, Tl, top_k=top_k, combine=combine, dispatch=dispatch)
     for _ in range(steps):                      # repeated steps exercise the epoch logic and buffer reuse
         loc["output"].fill_(float("nan"))
         layer()
@@ -89,4 +89,4 @@ def run(T=512, H=512, I=256, E=16, top_k=4, seed=3, steps=3, combine="push"):
 
 
 if __name__ == "__main__":
-    run(combine=os.environ.get("EP_COMBINE", "push"))
+    run(combine=os.environ.get("EP_COMBINE", "push"), dispatch=os.environ.get("EP_DISPATCH", "fused"))

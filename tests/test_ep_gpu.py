@@ -17,14 +17,16 @@ def test_ep_layer_world1_matches_single_gpu_layer():
     from tests import ep_worker
     ep_worker.run(T=384, H=256, I=128, E=8, top_k=2, seed=11, steps=2, combine="push")
     ep_worker.run(T=384, H=256, I=128, E=8, top_k=2, seed=12, steps=2, combine="pull")
+    ep_worker.run(T=384, H=256, I=128, E=8, top_k=2, seed=13, steps=2, combine="push", dispatch="kernel")
+    ep_worker.run(T=1000, H=512, I=256, E=32, top_k=4, seed=14, steps=3, combine="push")      # many experts, ragged tail
 
 
-@pytest.mark.parametrize("combine", ["push", "pull"])
+@pytest.mark.parametrize("combine,dispatch", [("push", "fused"), ("pull", "fused"), ("push", "kernel")])
 @pytest.mark.parametrize("world", [2, 4])
-def test_ep_layer_multi_gpu(world, combine):
+def test_ep_layer_multi_gpu(world, combine, dispatch):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", EP_COMBINE=combine)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", EP_COMBINE=combine, EP_DISPATCH=dispatch)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29511 + world), os.path.join(ROOT, "tests", "ep_worker.py")]
     r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)

@@ -17,14 +17,15 @@ pytestmark = pytest.mark.gpu
 _vp, _i32, _i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
 
 
-def _plan_static(L, ids, e_lo, e_local, align, cap):
+def _plan_static(L, ids, e_lo, e_local, align, cap, n_pairs=None):
     dev = ids.device
+    n_pairs = ids.numel() if n_pairs is None else n_pairs
     out = dict(counts=torch.full((e_local,), -7, dtype=torch.int32, device=dev),
                offsets=torch.full((e_local + 1,), -7, dtype=torch.int32, device=dev),
-               pos=torch.full(ids.shape, -7, dtype=torch.int32, device=dev),
+               pos=torch.full((max(n_pairs, 1),), -7, dtype=torch.int32, device=dev).view(ids.shape if n_pairs else (1,)),
                src_pair=torch.full((cap,), -7, dtype=torch.int32, device=dev),
                grouped_layout=torch.full((cap,), -7, dtype=torch.int32, device=dev))
-    rc = L.moe_permute_plan_static(_vp(ids.data_ptr()), _i64(ids.numel()), _i32(e_lo), _i32(e_local), _i32(align),
+    rc = L.moe_permute_plan_static(_vp(ids.data_ptr()), _i64(n_pairs), _i32(e_lo), _i32(e_local), _i32(align),
                                    _i32(cap), _vp(out["counts"].data_ptr()), _vp(out["offsets"].data_ptr()),
                                    _vp(out["pos"].data_ptr()), _vp(out["src_pair"].data_ptr()),
                                    _vp(out["grouped_layout"].data_ptr()),
@@ -48,8 +49,8 @@ def test_static_plan_matches_workspace_plan_on_two_calls_in_a_row():
         for k in ("counts", "offsets", "pos", "src_pair", "grouped_layout"):
             assert torch.equal(got[k], ref[k]), k                  # integer outputs: exact
     # an empty batch right after a full one: the counters the earlier calls left in the built-in array are never read
-    empty = torch.zeros((0, 8), dtype=torch.int32, device="cuda")
-    rc, got = _plan_static(L, empty, 0, 16, 128, 16 * 128)
+    unused = torch.zeros((1, 8), dtype=torch.int32, device="cuda")           # a valid pointer; no pair is read
+    rc, got = _plan_static(L, unused, 0, 16, 128, 16 * 128, n_pairs=0)
     assert rc == 0, L.moe_last_error().decode()
     assert grouped_gemm.device_status() == 0
     assert not got["counts"].any() and not got["offsets"].any()

@@ -80,6 +80,15 @@ class EpPeers(_c.Structure):
                 ("counts", _c.c_void_p * 8), ("flags", _c.c_void_p * 8), ("meta", _c.c_void_p * 8)]
 
 
+class EpSendArgs(_c.Structure):
+    """``moe_ep_send_args`` of include/b200moe.h."""
+    _fields_ = [("peers", _c.POINTER(EpPeers)), ("x_q", _c.c_void_p), ("x_scale", _c.c_void_p),
+                ("xs_row", _c.c_int64), ("xs_blk", _c.c_int64), ("ids", _c.c_void_p), ("pos", _c.c_void_p),
+                ("send_order", _c.c_void_p), ("counts_local", _c.c_void_p), ("n_pairs", _c.c_int64), ("pitch", _c.c_int64),
+                ("top_k", _c.c_int32), ("E_local", _c.c_int32), ("H", _c.c_int32), ("cap_rows", _c.c_int32),
+                ("rank", _c.c_int32), ("world", _c.c_int32)]
+
+
 class B200MoeError(RuntimeError):
     pass
 
@@ -116,7 +125,7 @@ EXPORTS = (
     "moe_kg_workspace_bytes", "moe_kg_fp8_contiguous",
     "moe_ipc_alloc", "moe_ipc_free", "moe_ipc_get_handle", "moe_ipc_open", "moe_ipc_close",
     "moe_ep_barrier", "moe_ep_workspace_bytes", "moe_ep_count_publish", "moe_ep_plan", "moe_ep_dispatch",
-    "moe_ep_combine", "moe_set_option", "moe_get_option",
+    "moe_ep_combine", "moe_ep_gate_up_dispatch", "moe_set_option", "moe_get_option",
     "moe_last_error", "moe_version",
 )
 _SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_workspace_bytes", "moe_ep_workspace_bytes",

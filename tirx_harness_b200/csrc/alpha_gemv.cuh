@@ -60,6 +60,35 @@ alpha_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const int* __rest
     pdl_wait();
     pdl_launch_dependents();
     const int e = __ldg(ids + p);
+    const bool live = e >= 0 && e < E;
+    // warp w: activation features i0, i0+1 of this slice -> 4 rows of W13 (gate i0, up i0, gate i0+1, up i0+1).
+    // A 128-K block is 8 consecutive 16-byte chunks = 8 consecutive lanes; 32 lanes cover 4 blocks per round; the
+    // 16 loads of four rounds of the four rows, and the expert's block scales, are requested before anything else
+    // (the kernel is a chain of HBM round trips otherwise): they travel while the token row is quantised.
+    const int chunks = H >> 4;
+    const int i0 = slice * 16 + warp * 2;
+    const uint4* wrow[4];
+    uint4 raw[4][4];
+    float sreg[2] = {0.0f, 0.0f};              // lane (half * 16 + kb % 16), register kb / 16: scale of (half, kb)
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int half = r & 1, i = i0 + (r >> 1);
+            wrow[r] = reinterpret_cast<const uint4*>(w13 + ((long long)e * 256 + half * 128 + i) * H);
+        }
+#pragma unroll
+        for (int rd = 0; rd < 4; ++rd) {
+            const int c = rd * 32 + lane;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) raw[rd][r] = c < chunks ? __ldg(wrow[r] + c) : make_uint4(0, 0, 0, 0);
+        }
+        const float* sbase = s13 + ((long long)e * 2 + (lane >> 4)) * KB;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int kb = (lane & 15) + 16 * j;
+            if (kb < KB) sreg[j] = __ldg(sbase + kb);
+        }
+    }
     // 1x128 quantisation of the token's row
     const __nv_bfloat16* xrow = x + (long long)(p / top_k) * H;
     for (int b = warp; b < KB; b += 8) {
@@ -73,30 +102,18 @@ alpha_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const int* __rest
         if (lane == 0) xs[b] = sc;
     }
     __syncthreads();
-    if (e < 0 || e >= E) return;
-    // warp w: activation features i0, i0+1 of this slice -> 4 rows of W13 (gate i0, up i0, gate i0+1, up i0+1).
-    // A 128-K block is 8 consecutive 16-byte chunks = 8 consecutive lanes; 32 lanes cover 4 blocks per round; the
-    // 16 loads of four rounds of the four rows are issued before the first is used (the kernel is a latency chain
-    // otherwise: one HBM round trip per load).
-    const int chunks = H >> 4;
-    const int i0 = slice * 16 + warp * 2;
-    const uint4* wrow[4];
-    const float* sb[4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const int half = r & 1, i = i0 + (r >> 1);
-        wrow[r] = reinterpret_cast<const uint4*>(w13 + ((long long)e * 256 + half * 128 + i) * H);
-        sb[r] = s13 + ((long long)e * 2 + half) * KB;
-    }
+    if (!live) return;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (int c0 = 0; c0 < chunks; c0 += 128) {
-        uint4 raw[4][4];
+        if (c0 > 0) {
 #pragma unroll
-        for (int rd = 0; rd < 4; ++rd) {
-            const int c = c0 + rd * 32 + lane;
+            for (int rd = 0; rd < 4; ++rd) {
+                const int c = c0 + rd * 32 + lane;
 #pragma unroll
-            for (int r = 0; r < 4; ++r) raw[rd][r] = c < chunks ? __ldg(wrow[r] + c) : make_uint4(0, 0, 0, 0);
+                for (int r = 0; r < 4; ++r) raw[rd][r] = c < chunks ? __ldg(wrow[r] + c) : make_uint4(0, 0, 0, 0);
+            }
         }
+        const float sv = c0 == 0 ? sreg[0] : sreg[1];          // 128 chunks = 16 K blocks per pass
 #pragma unroll
         for (int rd = 0; rd < 4; ++rd) {
             const int c = c0 + rd * 32 + lane;
@@ -118,11 +135,13 @@ alpha_gemv_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const int* __rest
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 const int kb = ((c0 + rd * 32) >> 3) + g;
-                if (kb < KB) {
+                if (kb < KB) {                                   // warp-uniform
                     const float sx = xs[kb];
+                    const float sw_gate = __shfl_sync(0xffffffffu, sv, kb & 15);
+                    const float sw_up = __shfl_sync(0xffffffffu, sv, 16 + (kb & 15));
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
-                        acc[r] = fmaf(__shfl_sync(0xffffffffu, part[r], g * 8), __fmul_rn(sx, __ldg(sb[r] + kb)), acc[r]);
+                        acc[r] = fmaf(__shfl_sync(0xffffffffu, part[r], g * 8), __fmul_rn(sx, (r & 1) ? sw_up : sw_gate), acc[r]);
                 }
             }
         }
@@ -143,7 +162,7 @@ alpha_gemv_down_kernel(const float* __restrict__ act, const int* __restrict__ id
                        const uint8_t* __restrict__ w2, const float* __restrict__ s2w, float rsf, int top_k, int E, int H,
                        __nv_bfloat16* __restrict__ out) {
     __shared__ int s_pair[32], s_exp[32];
-    __shared__ float s_scale[32];
+    __shared__ float s_scale[32], s_wsc[32];
     __shared__ int s_n;
     const int tiles = H >> 5;
     const int t = blockIdx.x / tiles, h0 = (blockIdx.x % tiles) * 32;
@@ -157,6 +176,7 @@ alpha_gemv_down_kernel(const float* __restrict__ act, const int* __restrict__ id
         const int e = have ? __ldg(ids + t * top_k + lane) : -1;
         const float wt = have ? __ldg(wts + t * top_k + lane) : 0.0f;
         const bool live = have && e >= 0 && e < E;
+        const float wsc = live ? __ldg(s2w + (long long)e * (H >> 7) + (h0 >> 7)) : 0.0f;    // this tile's W2 block scale
         const unsigned live_mask = __ballot_sync(0xffffffffu, live);
         int rank = 0;
         for (int o = 0; o < top_k; ++o) {
@@ -167,33 +187,39 @@ alpha_gemv_down_kernel(const float* __restrict__ act, const int* __restrict__ id
             s_pair[rank] = t * top_k + lane;
             s_exp[rank] = e;
             s_scale[rank] = __fmul_rn(wt, rsf);
+            s_wsc[rank] = wsc;
         }
         if (lane == 0) s_n = __popc(live_mask);
     }
     __syncthreads();
-    pdl_wait();                                 // act is written by the gate_up kernel just before this one
     const int n = s_n;
+    const int hw = h0 + warp * 8;
+    constexpr int R = 10;          // routes in flight per pass: the task's top-10 in one
     float accv[8];
 #pragma unroll
     for (int f = 0; f < 8; ++f) accv[f] = 0.0f;
-    const int hw = h0 + warp * 8;
-    for (int k0 = 0; k0 < n; k0 += 4) {
-        // four routes at a time: their activations and this warp's eight W2 rows are all requested before any is used
-        float4 a[4];
-        uint32_t wraw[4][8];
+    for (int k0 = 0; k0 < n; k0 += R) {
+        // W2 rows of all routes of the pass are requested before the wait (weights do not depend on the kernel in
+        // front), the activations right after it: one HBM round trip per pass instead of one per four routes
+        uint32_t wraw[R][8];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < R; ++r) {
             const int k = k0 + r < n ? k0 + r : n - 1;
-            a[r] = __ldcg(reinterpret_cast<const float4*>(act + (long long)s_pair[k] * 128) + lane);
             const uint8_t* wbase = w2 + ((long long)s_exp[k] * H + hw) * 128;
 #pragma unroll
             for (int f = 0; f < 8; ++f) wraw[r][f] = __ldg(reinterpret_cast<const uint32_t*>(wbase + f * 128) + lane);
         }
+        if (k0 == 0) pdl_wait();                                 // act is written by the gate_up kernel just before this one
+        float4 a[R];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < R; ++r) {
+            const int k = k0 + r < n ? k0 + r : n - 1;
+            a[r] = __ldcg(reinterpret_cast<const float4*>(act + (long long)s_pair[k] * 128) + lane);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
             if (k0 + r < n) {                                   // warp-uniform
                 const int k = k0 + r;
-                const int e = s_exp[k];
                 // requantise the route's 128 activations (lane holds 4): s = max(amax,1e-8)/448, code = e4m3(clamp(a/s))
                 float amax = warp_max(fmaxf(fmaxf(fabsf(a[r].x), fabsf(a[r].y)), fmaxf(fabsf(a[r].z), fabsf(a[r].w))));
                 const float sc = __fdiv_rn(fmaxf(amax, 1.0e-8f), 448.0f);
@@ -201,7 +227,7 @@ alpha_gemv_down_kernel(const float* __restrict__ act, const int* __restrict__ id
                 const float q1 = e4m3_round_trip(clamp448(__fdiv_rn(a[r].y, sc)));
                 const float q2 = e4m3_round_trip(clamp448(__fdiv_rn(a[r].z, sc)));
                 const float q3 = e4m3_round_trip(clamp448(__fdiv_rn(a[r].w, sc)));
-                const float sab = __fmul_rn(sc, __ldg(s2w + (long long)e * (H >> 7) + (h0 >> 7)));
+                const float sab = __fmul_rn(sc, s_wsc[k]);
                 const float ws = s_scale[k];
 #pragma unroll
                 for (int f = 0; f < 8; ++f) {
@@ -218,6 +244,7 @@ alpha_gemv_down_kernel(const float* __restrict__ act, const int* __restrict__ id
             }
         }
     }
+    if (n == 0) pdl_wait();
     if (lane < 8) {
         float v = accv[0];
 #pragma unroll

@@ -39,6 +39,14 @@ std::atomic<int> g_options[MOE_OPT_COUNT_] = {
 };
 inline int opt(int which) { return g_options[which].load(std::memory_order_relaxed); }
 
+// Generation number of a call that takes the block-scaled path: the scale check marks "not all powers of two" by
+// storing this number into the workspace flag, so nothing has to be cleared between calls.
+std::atomic<unsigned> g_call_gen{1};
+inline int next_gen() {
+    unsigned g = g_call_gen.fetch_add(1, std::memory_order_relaxed);
+    return (int)(g == 0 ? g_call_gen.fetch_add(1, std::memory_order_relaxed) : g);
+}
+
 thread_local char g_err[512] = "";
 
 int fail(int code, const char* fmt, ...) {
@@ -149,6 +157,10 @@ int device_info(DeviceInfo** out) {
                                       gg::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       gg::SMEM_BYTES_SCATTER));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg::SMEM_BYTES_DISPATCH));
+        CUDA_TRY(cudaFuncSetAttribute(gg_fp8_kernel<false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      gg::SMEM_BYTES_DISPATCH));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -248,6 +260,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.layout = a->layout;
     p.rows_used = MASKED ? nullptr : a->rows_used;
     p.mode_flag = nullptr;
+    p.mode_gen = 0;
     p.act_q = nullptr; p.act_s = nullptr; p.act_ss_r = 0; p.act_ss_b = 0; p.inter = 0; p.gate_first = 0;
     p.scatter_meta = MASKED ? nullptr : a->scatter_meta;
     for (int i = 0; i < 8; ++i) p.scatter_base[i] = static_cast<__nv_bfloat16*>(a->scatter_base[i]);
@@ -280,7 +293,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         ws.row_blocks = ml.row_blocks;
         ws.quads = ml.quads;
         cudaStream_t st = static_cast<cudaStream_t>(stream);
-        CUDA_TRY(cudaMemsetAsync(ws.flag, 0, sizeof(int), st));
+        ws.gen = p.mode_gen = next_gen();
         dim3 pgrid(ml.row_blocks + a->G * p.nb128, ml.quads, 1);
         if (packed_sf)
             mx_prep_packed_kernel<<<pgrid, 128, 0, st>>>(
@@ -867,7 +880,7 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
         MxWorkspace ws;
         ws.flag = w.flag; ws.sfa_packed = w.sfa_tiles; ws.sfb_packed = w.sfb_tiles;
         ws.row_blocks = (A->M + 127) / 128; ws.quads = quads;
-        CUDA_TRY(cudaMemsetAsync(ws.flag, 0, sizeof(int), st));
+        ws.gen = p.mode_gen = next_gen();
         dim3 pgrid(ws.row_blocks + p.nb128, quads, 1);
         mx_prep_packed_kernel<<<pgrid, 128, 0, st>>>(reinterpret_cast<const uint32_t*>(A->sfa), 1, A->M,
                                                      reinterpret_cast<const uint32_t*>(A->sfb), 0, 1, A->N, A->M, A->N, 1, p.nb128, ws);
@@ -1151,8 +1164,8 @@ int moe_ep_count_publish(const moe_ep_peers* P, const int32_t* ids, int64_t n_pa
 
 int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int32_t rank, int32_t world,
                 int32_t E_total, int32_t E_local, int32_t align, int32_t cap_rows, int32_t* counts_local,
-                int32_t* offsets, int32_t* grouped_layout, int32_t* dst_base, int32_t* pos, void* workspace,
-                size_t workspace_bytes, void* stream) {
+                int32_t* offsets, int32_t* grouped_layout, int32_t* dst_base, int32_t* pos, int32_t* send_order,
+                void* workspace, size_t workspace_bytes, void* stream) {
     int rc = ep_check(P, rank, world);
     if (rc != MOE_OK) return rc;
     rc = check_plan_args(n_pairs, E_total, align, cap_rows);
@@ -1166,8 +1179,11 @@ int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int3
     if (rc != MOE_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int* chunk_offsets = static_cast<const int*>(workspace);      // left by moe_ep_count_publish
+    // first slot of every global expert in this rank's sending order: the scratch behind the chunk counters
+    int* send_base = send_order ? reinterpret_cast<int*>(static_cast<char*>(workspace) + moe_permute_workspace_bytes(n_pairs, E_total))
+                                : nullptr;
     ep_plan_kernel<<<1, 256, (size_t)2 * E_total * 4, st>>>(P->counts[rank], rank, world, E_total, E_local, align,
-                                                          cap_rows, counts_local, offsets, dst_base, di->status);
+                                                          cap_rows, counts_local, offsets, dst_base, send_base, di->status);
     CUDA_TRY(cudaGetLastError());
     ep_layout_kernel<<<(cap_rows + 1023) / 1024, 1024, 0, st>>>(offsets, counts_local, E_local, grouped_layout, cap_rows);
     CUDA_TRY(cudaGetLastError());
@@ -1175,7 +1191,7 @@ int moe_ep_plan(const moe_ep_peers* P, const int32_t* ids, int64_t n_pairs, int3
     if (n_chunks > 0) {
         // cap = INT_MAX: destination rows live in the owners' buffers; the owner bounds them by its own capacity
         plan_place_kernel<<<n_chunks, PLAN_CHUNK, (size_t)32 * E_total * 4, st>>>(
-            ids, n_pairs, 0, E_total, chunk_offsets, nullptr, dst_base, pos, nullptr, nullptr, 0x7FFFFFFF);
+            ids, n_pairs, 0, E_total, chunk_offsets, nullptr, dst_base, pos, nullptr, nullptr, 0x7FFFFFFF, send_base, send_order);
         CUDA_TRY(cudaGetLastError());
     }
     return MOE_OK;
@@ -1206,6 +1222,79 @@ int moe_ep_dispatch(const moe_ep_peers* P, const void* x_q, const float* x_scale
                          static_cast<cudaStream_t>(stream)>>>(
         ep_convert(P), static_cast<const uint8_t*>(x_q), x_scale, xs_row, xs_blk, ids, pos, n_pairs, top_k, E_local, H,
         cap_rows, rank, pitch, di->status);
+    CUDA_TRY(cudaGetLastError());
+    return MOE_OK;
+}
+
+int moe_ep_gate_up_dispatch(const moe_gg_args* a, const moe_ep_send_args* S, void* act_q, float* act_scales, int64_t ss_row,
+                            int64_t ss_blk, int32_t gate_first, void* stream) {
+    if (!a || !S) return fail(MOE_ERR_INVALID, "args is NULL");
+    int rc = ep_check(S->peers, S->rank, S->world);
+    if (rc != MOE_OK) return rc;
+    const bool fused = act_q != nullptr;
+    if (!a->a || !a->b || !a->sfa || !a->sfb || !a->layout || !a->rows_used || (fused ? !act_scales : !a->d))
+        return fail(MOE_ERR_INVALID, "a, b, sfa, sfb, layout, rows_used and the output must be non-NULL");
+    if (!S->x_q || !S->x_scale || !S->ids || !S->pos || !S->send_order || !S->counts_local)
+        return fail(MOE_ERR_INVALID, "send pointers must be non-NULL");
+    if (a->G <= 0 || a->G != S->E_local || a->N <= 0 || a->K <= 0 || a->M <= 0 || a->K != S->H)
+        return fail(MOE_ERR_INVALID, "G must equal E_local, K must equal H, M (capacity) positive");
+    if (a->K % 128 || a->N % (fused ? 256 : 8)) return fail(MOE_ERR_INVALID, "K must be a multiple of 128, N of %d", fused ? 256 : 8);
+    if (a->sf_format != MOE_SF_F32 || a->scatter_meta || a->accumulate || a->ldb)
+        return fail(MOE_ERR_UNSUPPORTED, "the dispatching GEMM takes fp32 scales and writes plain output");
+    if (!fused && (a->d_dtype != MOE_DTYPE_BF16 || a->ldd < a->N || a->ldd % 8)) return fail(MOE_ERR_INVALID, "d must be bf16 with ldd >= N, ldd %% 8 == 0");
+    if (S->n_pairs < 0 || S->n_pairs > (1ll << 24) || S->top_k <= 0 || S->n_pairs % S->top_k)
+        return fail(MOE_ERR_INVALID, "n_pairs must be a multiple of top_k and at most 2^24");
+    const long long rec = ((long long)S->H + S->H / 32 + 15) & ~15ll;
+    if (rec > EP_SEND_RECORD_MAX) return fail(MOE_ERR_UNSUPPORTED, "H=%d: a token record must fit %d bytes", S->H, EP_SEND_RECORD_MAX);
+    if (S->pitch < rec || S->pitch % 16 || a->lda != S->pitch) return fail(MOE_ERR_INVALID, "pitch must be >= H + H/32, a multiple of 16, and equal to lda");
+    if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->b) & 15) || (reinterpret_cast<uintptr_t>(S->x_q) & 15) ||
+        (reinterpret_cast<uintptr_t>(fused ? act_q : a->d) & 15))
+        return fail(MOE_ERR_INVALID, "a, b, x_q and the output must be 16-byte aligned");
+    if ((long long)a->G * a->N > 0x7FFFFFFFll) return fail(MOE_ERR_INVALID, "row counts exceed 2^31-1");
+    DeviceInfo* di = nullptr;
+    rc = device_info(&di);
+    if (rc != MOE_OK) return rc;
+    CUtensorMap tmap_a, tmap_b;
+    rc = encode_fp8_kmajor(&tmap_a, a->a, (uint64_t)a->M, (uint64_t)a->K, gg::BM, (uint64_t)a->lda);
+    if (rc != MOE_OK) return rc;
+    rc = encode_fp8_kmajor(&tmap_b, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, fused ? gg::FUSE_B_BOX_ROWS : gg::BN);
+    if (rc != MOE_OK) return rc;
+    GGParams p = {};
+    p.sfa = a->sfa; p.sfa_sr = a->sfa_stride_row; p.sfa_sk = a->sfa_stride_kblk;
+    p.sfb = a->sfb; p.layout = a->layout; p.rows_used = a->rows_used;
+    p.d = a->d; p.ldd = a->ldd;
+    p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
+    p.rows_total = a->M;
+    p.num_k_blocks = a->K / 128;
+    p.nb128 = (a->N + 127) / 128;
+    p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
+    if (fused) {
+        p.inter = a->N / 2;
+        p.num_n_blocks = p.inter / 128;
+        p.act_q = static_cast<uint8_t*>(act_q);
+        p.act_s = act_scales;
+        p.act_ss_r = ss_row; p.act_ss_b = ss_blk;
+        p.gate_first = gate_first ? 1 : 0;
+    } else {
+        p.num_n_blocks = (a->N + gg::BN - 1) / gg::BN;
+    }
+    EpSend& e = p.ep;
+    for (int i = 0; i < EP_MAX_WORLD; ++i) {
+        e.a[i] = static_cast<uint8_t*>(S->peers->a[i]);
+        e.meta[i] = S->peers->meta[i];
+        e.arrive[i] = S->peers->flags[i] ? S->peers->flags[i] + EP_ARRIVE_OFFSET : nullptr;
+    }
+    e.x = static_cast<const uint8_t*>(S->x_q); e.xs = S->x_scale; e.xs_r = S->xs_row; e.xs_b = S->xs_blk; e.pitch = S->pitch;
+    e.ids = S->ids; e.pos = S->pos; e.order = S->send_order; e.expected = S->counts_local;
+    e.n_pairs = (int)S->n_pairs; e.top_k = S->top_k; e.E_local = S->E_local; e.H = S->H; e.cap_rows = S->cap_rows; e.rank = S->rank;
+    // every CTA must be resident (its sending warp's rows are awaited by other GPUs): a persistent grid of one CTA
+    // per SM; CTAs beyond the tile count only send
+    const int grid = di->num_sms;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (fused)
+        gg_fp8_kernel<false, true, false, true><<<grid, gg::THREADS, gg::SMEM_BYTES_DISPATCH, st>>>(tmap_a, tmap_b, tmap_a, p, di->status);
+    else
+        gg_fp8_kernel<false, false, false, true><<<grid, gg::THREADS, gg::SMEM_BYTES_DISPATCH, st>>>(tmap_a, tmap_b, tmap_a, p, di->status);
     CUDA_TRY(cudaGetLastError());
     return MOE_OK;
 }

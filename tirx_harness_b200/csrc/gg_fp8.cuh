@@ -71,6 +71,8 @@ constexpr int MASKED_LIST_CAP = 2048;
 constexpr int MASKED_TABLE_INTS = (MAX_MASKED_GROUPS + 1) + MAX_MASKED_GROUPS + MASKED_LIST_CAP;
 constexpr int SMEM_BYTES_MASKED = OFF_PREFIX + MASKED_TABLE_INTS * 4 + 12 + 1024;
 constexpr int SMEM_BYTES_SCATTER = SMEM_BYTES - (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES;
+// dispatching variant (contiguous layout: no prefix table): the sending warp's record buffers take that place
+constexpr int SMEM_BYTES_DISPATCH = OFF_PREFIX + EP_SEND_BUFFERS * EP_SEND_RECORD_MAX + 1024;
 }  // namespace gg
 
 struct GGParams {
@@ -79,7 +81,8 @@ struct GGParams {
     const float* sfb;            // [G][nb128][KB]
     const int* layout;           // grouped_layout[M] or masked_m[G]
     const int* rows_used;        // contiguous, optional: device count of leading rows in use (<= M)
-    const int* mode_flag;        // optional: this kernel runs only if *mode_flag != 0 (see gg_fp8_mx.cuh)
+    const int* mode_flag;        // optional: this kernel runs only if *mode_flag == mode_gen (see gg_fp8_mx.cuh)
+    int mode_gen;                // generation number of the call (block-scaled path)
     // scattered output (expert-parallel down GEMM): row r is stored at scatter_base[meta >> 24] + (meta & 0xFFFFFF) * ldd
     // with meta = scatter_meta[r]; the bases may be other GPUs' memory (plain stores only)
     const int* scatter_meta;
@@ -94,6 +97,7 @@ struct GGParams {
     int d_f32;
     int d_accumulate;            // fp32 output only: add to d instead of overwriting it
     long long* trace;            // developer aid: per-CTA wait-cycle counters [grid][8], or nullptr
+    EpSend ep;                   // DISPATCH kernels only: the all-to-all this GEMM carries (moe_ops.cuh)
     int G, M, N, K;              // M: total rows (contiguous) / rows per group (masked)
     int rows_total;              // rows of the flattened A / D (M or G*M)
     int num_n_blocks;            // ceil(N / BN)
@@ -247,12 +251,45 @@ struct Scheduler {
     }
 };
 
-template <bool MASKED, bool FUSE_ACT = false, bool SCATTER = false>
+// Bounded wait (2 s) of one warp until every row of local expert g has arrived in this rank's receive buffer:
+// lane 0 polls the arrival counter with acquire semantics at system scope (the rows were stored by other GPUs).
+__device__ __forceinline__ bool wait_expert_arrived(const EpSend& ep, int g, volatile int* abort_flag, int* status) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        const int want = __ldg(ep.expected + g);
+        const int* ctr = ep.arrive[ep.rank] + g;
+        if (ld_acquire_sys(ctr) < want) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_sys(ctr) < want) {
+                if ((++spins & 63u) == 0) {
+                    if (*abort_flag) { ok = false; break; }
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        *abort_flag = 1;
+                        atomicOr(status, STATUS_TIMEOUT_PEER_FLAG);
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+
+// DISPATCH: the gate_up GEMM of an expert-parallel layer that carries the dispatch all-to-all itself.  Warp 3 of
+// every CTA sends this rank's token records (e4m3 row + scales) straight into the owners' receive buffers, local
+// expert 0 of every rank first; the TMA producer and the scale loader wait, per expert, until that expert's rows
+// have all arrived (arrival counters incremented by the senders after their stores completed).  The transfer thus
+// overlaps the GEMM tile by tile and needs no barrier of its own.  Senders never wait for anything remote, and
+// every CTA of the grid is resident (persistent grid <= SM count), so the waits cannot form a cycle.
+template <bool MASKED, bool FUSE_ACT = false, bool SCATTER = false, bool DISPATCH = false>
 __global__ void __launch_bounds__(gg::THREADS, 1)
 gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const __grid_constant__ CUtensorMap tmap_a_small, const GGParams p, int* status) {
     static_assert(!(MASKED && FUSE_ACT), "the fused activation epilogue exists for the contiguous layout only");
     static_assert(!(SCATTER && (MASKED || FUSE_ACT)), "scattered output exists for the plain contiguous GEMM only");
+    static_assert(!(DISPATCH && (MASKED || SCATTER)), "the dispatching variant is a contiguous-layout gate_up GEMM");
     using namespace gg;
     // SCATTER trades one pipeline stage for a 128 x 528-byte staging area from which finished rows leave
     // as 512-byte bulk stores (possibly to another GPU) without holding up the promotion warps.
@@ -262,7 +299,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     constexpr int SF_AT = BARS_AT + 512;
     constexpr int AMAX_AT = SF_AT + SF_SLOTS * SF_SLOT_FLOATS * 4;
     constexpr int PREFIX_AT = AMAX_AT + 2 * COL_GROUPS * 128 * 4;
-    if (p.mode_flag != nullptr && *p.mode_flag == 0) return;   // the power-of-two-scale path took this call
+    if (p.mode_flag != nullptr && *p.mode_flag != p.mode_gen) return;   // the power-of-two-scale path took this call
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms the MMA descriptors address
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -271,7 +308,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BARS_AT);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty,
     // then SF_SLOTS scale-full and SF_SLOTS scale-empty barriers
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1 + 8);
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS + 1 + 8 + EP_SEND_BUFFERS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     float* sf_ring = reinterpret_cast<float*>(smem + SF_AT);
     int* prefix = reinterpret_cast<int*>(smem + PREFIX_AT);
@@ -287,6 +324,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     const uint32_t sfempty_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES + SF_SLOTS);
     const uint32_t amax_bar = smem_u32(bars + 2 * NSTAGES + 2 * ACC_STAGES + 2 * SF_SLOTS);
     const uint32_t stg_bar = amax_bar + 8;            // SCATTER: 4 "row free" + 4 "row filled" barriers, one pair per lane quarter
+    const uint32_t send_bar = stg_bar + 64;           // DISPATCH: one "record loaded" barrier per send buffer
     float* amax_x = reinterpret_cast<float*>(smem + AMAX_AT);
 
     if (threadIdx.x == 0) {
@@ -307,6 +345,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             mbar_init(stg_bar + 8 * q, 1);                // the group-0 warp of the quarter
             mbar_init(stg_bar + 8 * (4 + q), COL_GROUPS); // one arrival per column group of the quarter
         }
+        for (int b = 0; b < EP_SEND_BUFFERS; ++b) mbar_init(send_bar + 8 * b, 1);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
@@ -337,8 +376,16 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             uint32_t stage = 0, phase = 0;
             uint32_t issued = 0, issued_parity = 0;   // per-stage: a load was issued / its phase parity
             bool ok = true;
+            int arrived_g = -1;
             while (ok && sched.next(tile)) {
                 const int b_row = tile.g * p.N + tile.n_blk * BN;
+                if (DISPATCH && tile.g != arrived_g) {
+                    ok = wait_expert_arrived(p.ep, tile.g, abort_flag, status);
+                    if (!ok) break;
+                    arrived_g = tile.g;
+                    // the rows were written through NVLink; the TMA loads below read them through the async proxy
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                }
                 for (int kb = 0; kb < KB; ++kb) {
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
                                         STATUS_TIMEOUT_SMEM_EMPTY);
@@ -427,7 +474,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             Tile tile;
             uint32_t slot = 0, sphase = 0;
             bool ok = true;
+            int arrived_g = -1;
             while (ok && sched.next(tile)) {
+                if (DISPATCH && tile.g != arrived_g) {      // the row scales travel inside the records
+                    ok = wait_expert_arrived(p.ep, tile.g, abort_flag, status);
+                    if (!ok) break;
+                    arrived_g = tile.g;
+                }
                 const float* rp[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -455,6 +508,79 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 }
             }
             cp_async_wait_all();      // nothing may still be writing this CTA's shared memory at exit
+        } else if (DISPATCH) {
+            // ------------------------------------------------ sender of the dispatch all-to-all (warp 3)
+            // Per pair: the token's record (e4m3 row by a bulk load, scales by the lanes) is assembled in one of
+            // EP_SEND_BUFFERS shared-memory buffers and leaves as ONE bulk store into the owner's receive buffer.
+            // Lane 0 issues all bulk operations, so its bulk groups complete in order: once at most
+            // EP_SEND_BUFFERS - 1 groups are pending, the store issued EP_SEND_BUFFERS iterations ago has completed
+            // -- its buffer is free again and its row can be counted as arrived (release at system scope).
+            const EpSend& ep = p.ep;
+            uint8_t* stage_base = smem + PREFIX_AT;
+            const int rec = (ep.H + (ep.H >> 5) + 15) & ~15;
+            int* pending[EP_SEND_BUFFERS];
+#pragma unroll
+            for (int b = 0; b < EP_SEND_BUFFERS; ++b) pending[b] = nullptr;
+            bool ok = true;
+            int it = 0;
+            for (int slot = blockIdx.x; ok && slot < ep.n_pairs; slot += gridDim.x, ++it) {
+                const int b = it % EP_SEND_BUFFERS;
+                const uint32_t par = (it / EP_SEND_BUFFERS) & 1;
+                int* done = nullptr;
+#pragma unroll
+                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (i == b) done = pending[i];
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(EP_SEND_BUFFERS - 1) : "memory");
+                    if (done != nullptr) {
+                        __threadfence_system();
+                        red_release_sys_add(done, 1);
+                    }
+                }
+                __syncwarp();
+                int pr = 0, row = -1, e = 0;
+                if (lane == 0) {
+                    pr = __ldg(ep.order + slot);
+                    row = __ldg(ep.pos + pr);
+                    e = __ldg(ep.ids + pr);
+                }
+                pr = __shfl_sync(0xffffffffu, pr, 0);
+                row = __shfl_sync(0xffffffffu, row, 0);
+                e = __shfl_sync(0xffffffffu, e, 0);
+                const int d = e / ep.E_local, j = e - d * ep.E_local;
+                const long long t = pr / ep.top_k;
+                int* next_pending = nullptr;
+                if (row >= 0 && row < ep.cap_rows) {
+                    uint8_t* buf = stage_base + b * EP_SEND_RECORD_MAX;
+                    const uint32_t bar = send_bar + 8 * b;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(bar, (uint32_t)ep.H);
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(smem_u32(buf)), "l"(ep.x + t * ep.H), "r"(ep.H), "r"(bar) : "memory");
+                    }
+                    float* sbuf = reinterpret_cast<float*>(buf + ep.H);
+                    for (int bk = lane; bk < (ep.H >> 7); bk += 32) sbuf[bk] = __ldg(ep.xs + t * ep.xs_r + (long long)bk * ep.xs_b);
+                    fence_proxy_async_smem();
+                    ok = mbar_wait_warp(bar, par, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                    if (ok && lane == 0) {
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                     ::"l"(ep.a[d] + (long long)row * ep.pitch), "r"(smem_u32(buf)), "r"(rec) : "memory");
+                        ep.meta[d][row] = (ep.rank << 24) | pr;      // where the row's result has to go back to
+                    }
+                    if (ok) next_pending = ep.arrive[d] + j;
+                } else if (row >= ep.cap_rows && lane == 0) {
+                    atomicOr(status, STATUS_CAPACITY);               // the owner's buffer is too small: row dropped
+                }
+                if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (i == b) pending[i] = next_pending;
+            }
+            // drain: every store complete (also on the failure path), then the last rows are counted
+            if (lane == 0) {
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                __threadfence_system();
+#pragma unroll
+                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (pending[i] != nullptr) red_release_sys_add(pending[i], 1);
+            }
         }
     } else {
         // ---------------------------------------------------- promotion + epilogue

@@ -8,8 +8,9 @@
 // sum of exactly-scaled e4m3 products accumulated in fp32.
 //
 //   mx_prep_kernel     checks every scale and writes the UE8M0 bytes, four K blocks per 32-bit word,
-//                      in the 32x16-byte tile order tcgen05.cp expects; sets a flag if any scale is not a
-//                      power of two (then this path stands down and the promotion kernel runs instead)
+//                      in the 32x16-byte tile order tcgen05.cp expects; stores the call's generation number
+//                      into a flag if any scale is not a power of two (then this path stands down and the
+//                      promotion kernel runs instead)
 //   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256 x 256 tiles, 6-stage TMA ring; the scale words of
 //                      four K blocks travel with the first of their stages; the leader issues
 //                      tcgen05.cp (smem -> TMEM) and 16 block-scaled MMAs per group of four K blocks;
@@ -39,7 +40,9 @@ constexpr int TMEM_SF_STRIDE = 12;                    // per buffer: 4 columns S
 }  // namespace mx
 
 struct MxWorkspace {
-    int* flag;                 // 0 after mx_prep_kernel = every scale is a power of two
+    int* flag;                 // == gen after mx_prep_kernel: some scale of THIS call is not a power of two
+    int gen;                   // the call's generation number (host counter): no memset between calls, a value left
+                               // by an earlier call can never equal it
     uint32_t* sfa_packed;      // [row_blocks128][quads][128]
     uint32_t* sfb_packed;      // [G][nb128][quads][128]
     int row_blocks, quads;
@@ -99,7 +102,7 @@ __global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, 
             ws.sfb_packed[((long long)idx * ws.quads + q) * 128 + threadIdx.x] = word;
         }
     }
-    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(ws.flag, 1);
+    if (__syncthreads_or(bad) && threadIdx.x == 0) *reinterpret_cast<volatile int*>(ws.flag) = ws.gen;
 }
 
 // Same outputs from scales that already ARE UE8M0 bytes packed four to an int32 (the registered
@@ -222,7 +225,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // holds 128 K rows x 128 bytes of M (or N), the MMAs read it as an MN-major operand (instruction descriptor bits
     // 15 and 16) and step 32 K rows = 4096 bytes per instruction.
     using Sched = MxSched<MASKED, KG>;
-    if (*flag != 0) return;          // some scale is not a power of two: the promotion kernel handles this call
+    if (*flag == p.mode_gen) return;      // some scale is not a power of two: the promotion kernel handles this call
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
@@ -526,7 +529,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                   const GGParams p, const int* __restrict__ flag, int quads, int* status) {
     using namespace mx1;
-    if (*flag != 0) return;
+    if (*flag == p.mode_gen) return;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;

@@ -309,7 +309,10 @@ __global__ void plan_place_kernel(const int* __restrict__ ids, long long n_pairs
                                   const int* __restrict__ chunk_offsets, const int* __restrict__ counts,
                                   const int* __restrict__ offsets, int* __restrict__ pos,
                                   int* __restrict__ src_pair, int* __restrict__ grouped_layout,
-                                  int cap_rows) {
+                                  int cap_rows, const int* __restrict__ offsets2 = nullptr,
+                                  int* __restrict__ order2 = nullptr) {
+    // offsets2 / order2 (optional): a second stable ordering of the same pairs, order2[offsets2[e] + rank of the
+    // pair among the pairs of expert e] = pair; dense (no padding rows)
     extern __shared__ int hist[];
     int rank;
     const int e = plan_warp_hist(ids, n_pairs, e_lo, E, hist, &rank);
@@ -327,7 +330,9 @@ __global__ void plan_place_kernel(const int* __restrict__ ids, long long n_pairs
     if (p < n_pairs) {
         int row = -1;
         if (e >= 0) {
-            row = offsets[e] + chunk_offsets[(long long)blockIdx.x * E + e] + hist[(threadIdx.x >> 5) * E + e] + rank;
+            const int within = chunk_offsets[(long long)blockIdx.x * E + e] + hist[(threadIdx.x >> 5) * E + e] + rank;
+            if (order2 != nullptr) order2[offsets2[e] + within] = (int)p;
+            row = offsets[e] + within;
             if (row >= cap_rows) row = -1;
             else if (src_pair != nullptr) src_pair[row] = (int)p;
         }
@@ -442,6 +447,33 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     return v;
 }
 
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+    asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Arrival counters live behind the barrier flags of each rank's symmetric region: flags[EP_ARRIVE_OFFSET + j] counts
+// the rows that have landed for local expert j in the current forward.
+constexpr int EP_ARRIVE_OFFSET = 64;
+constexpr int EP_SEND_BUFFERS = 3;                 // token records in flight per sending warp
+constexpr int EP_SEND_RECORD_MAX = 7424;           // bytes: H + H/32 for H <= 7168, rounded up to 128
+
+// What the gate_up GEMM needs to carry the dispatch all-to-all itself (one sending warp per CTA): this rank's
+// tokens and routes, where every pair goes (pos, from the exchange plan), the order to send them in (local
+// expert index first, so that every rank's first expert is complete first), and both sides' arrival counters.
+struct EpSend {
+    uint8_t* a[EP_MAX_WORLD];            // receive buffers of all ranks (records of `pitch` bytes)
+    int* meta[EP_MAX_WORLD];             // return address of every received row
+    int* arrive[EP_MAX_WORLD];           // arrival counters of all ranks, [E_local] each
+    const uint8_t* x;                    // this rank's tokens, e4m3 [T, H]
+    const float* xs;                     // their scales at [t * xs_r + b * xs_b]
+    long long xs_r, xs_b, pitch;
+    const int* ids;                      // [n_pairs] global expert of every pair
+    const int* pos;                      // [n_pairs] destination row inside the owner's buffer
+    const int* order;                    // [n_pairs] pairs in sending order
+    const int* expected;                 // [E_local] rows this rank receives per local expert
+    int n_pairs, top_k, E_local, H, cap_rows, rank;
+};
+
 // Cross-GPU barrier: thread s publishes `epoch` into peer s's flag slot for this rank, then waits
 // (bounded: `limit_ns` of wall time, 2 s unless the host set another limit) until peer s's epoch shows up
 // in the local slot; a wait that runs out ORs STATUS_TIMEOUT_PEER_FLAG into the status word and returns.
@@ -462,9 +494,12 @@ __global__ void ep_barrier_kernel(EpPeers peers, int rank, int world, int epoch,
     }
 }
 
-// Publishes this rank's per-expert pair counts (E_total ints) into row `rank` of every peer's table.
+// Publishes this rank's per-expert pair counts (E_total ints) into row `rank` of every peer's table, and clears this
+// rank's arrival counters for the forward that begins: no peer can send a row of it before the barrier that follows
+// this kernel, and every row of the previous forward was counted before that forward's gate_up GEMM finished.
 __global__ void ep_publish_counts_kernel(EpPeers peers, const int* __restrict__ my_counts, int rank,
                                          int world, int E_total) {
+    for (int j = threadIdx.x; j < E_total / world; j += blockDim.x) peers.flags[rank][EP_ARRIVE_OFFSET + j] = 0;
     for (int i = threadIdx.x; i < world * E_total; i += blockDim.x) {
         const int d = i / E_total, e = i % E_total;
         peers.counts[d][rank * E_total + e] = my_counts[e];
@@ -479,7 +514,8 @@ __global__ void ep_publish_counts_kernel(EpPeers peers, const int* __restrict__ 
 // dispatch kernels of the senders drop the rows that do not fit.
 __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int rank, int world, int E_total,
                                int E_local, int align, int cap_rows, int* __restrict__ counts_local,
-                               int* __restrict__ offsets, int* __restrict__ dst_base, int* status) {
+                               int* __restrict__ offsets, int* __restrict__ dst_base, int* __restrict__ send_base,
+                               int* status) {
     extern __shared__ int sh[];           // total[E_total], start[E_total]
     int* total = sh;
     int* start = sh + E_total;
@@ -503,6 +539,17 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_all, int rank, int
         }
     }
     __syncthreads();
+    // sending order of this rank's pairs: local expert index first, destination rank second, so that expert 0 of
+    // every rank is complete first; send_base[e] = first slot of the pairs for global expert e (may be NULL)
+    if (send_base != nullptr && threadIdx.x == 0) {
+        int run = 0;
+        for (int j = 0; j < E_local; ++j)
+            for (int d = 0; d < world; ++d) {
+                const int e = d * E_local + j;
+                send_base[e] = run;
+                run += counts_all[rank * E_total + e];
+            }
+    }
     for (int e = threadIdx.x; e < E_total; e += blockDim.x) {
         int before = 0;
         for (int s = 0; s < rank; ++s) before += counts_all[s * E_total + e];

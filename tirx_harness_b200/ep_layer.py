@@ -4,9 +4,11 @@
     layer()                                          # one forward on the current stream
 
 Rank r owns experts [r*E_local, (r+1)*E_local) with their weights resident and T_local tokens.
-Per forward: route -> publish per-expert counts to all peers -> barrier -> plan -> dispatch (rows are
-stored straight into the owner's grouped-layout buffer over NVLink, with their return address) -> barrier
--> gate_up grouped GEMM -> SiLU*mul requant -> down grouped GEMM whose epilogue sends every finished
+Per forward: route -> publish per-expert counts to all peers -> barrier -> plan -> gate_up grouped GEMM that
+carries the dispatch all-to-all itself (one warp of every CTA stores this rank's token records straight into the
+owners' grouped-layout buffers over NVLink, first experts first; the GEMM's loaders start on an expert as soon as
+its rows have all arrived, so the transfer hides behind the GEMM and needs no barrier; ``dispatch="kernel"`` runs
+the older separate dispatch kernel + barrier instead) -> SiLU*mul requant -> down grouped GEMM whose epilogue sends every finished
 output row straight to the slot of the rank that owns the token (256-byte bulk stores from a shared-memory
 staging area, so the combine all-to-all rides on the GEMM and costs it nothing measurable) -> barrier ->
 local weighted sum.  ``combine="pull"`` keeps the expert outputs local instead and lets the combine kernel
@@ -74,7 +76,7 @@ class SymmetricBuffer:
 
 class EpMoeLayer:
     def __init__(self, data: dict, T_local: int, top_k: int = 8, align: int = 128, gate_first: bool = False,
-                 group=None, fuse_act: bool = False, combine: str = "push"):
+                 group=None, fuse_act: bool = False, combine: str = "push", dispatch: str = "fused"):
         import torch.distributed as dist
         self.L = _lib.lib()
         x_q, xs = data["hidden_states"], data["hidden_states_scale"]
@@ -107,13 +109,16 @@ class EpMoeLayer:
         self.cap = cap
         if combine not in ("push", "pull"):
             raise ValueError("combine must be 'push' or 'pull'")
-        self.combine = combine
+        if dispatch not in ("fused", "kernel"):
+            raise ValueError("dispatch must be 'fused' or 'kernel'")
+        self.combine, self.dispatch = combine, dispatch
         # ---- symmetric region: a | sa | y (pull: [cap,H] expert outputs; push: [T_local*top_k,H] return slots)
         #      | counts | flags | meta
         y_rows = cap if combine == "pull" else n_pairs
         pitch = (H + (H // 128) * 4 + 15) // 16 * 16     # one record per row: e4m3 bytes, then its fp32 scales
         self.pitch = pitch
-        sizes = [cap * pitch, 0, y_rows * H * 2, self.world * E_total * 4, 256, cap * 4]
+        # flags: [0, world) barrier epochs, [64, 64 + E_local) arrival counters of the fused dispatch
+        sizes = [cap * pitch, 0, y_rows * H * 2, self.world * E_total * 4, (64 + E_local) * 4, cap * 4]
         offs, o = [], 0
         for s in sizes:
             offs.append(o)
@@ -132,6 +137,7 @@ class EpMoeLayer:
         self.ids = torch.empty((T_local, top_k), **i32)
         self.weights = torch.empty((T_local, top_k), dtype=torch.float32, device=dev)
         self.pos = torch.empty((T_local, top_k), **i32)
+        self.send_order = torch.empty(n_pairs, **i32)
         self.my_counts = torch.empty(E_total, **i32)
         self.dst_base = torch.empty(E_total, **i32)
         self.counts_local = torch.empty(E_local, **i32)
@@ -164,6 +170,12 @@ class EpMoeLayer:
         else:
             self.gemm2 = grouped_gemm.bind_contiguous(self.a2, self.s2.t(), w2, s2, self.y_t, self.layout, rows_used,
                                                       workspace=False)    # activation scales are amax/448, never 2^e
+        if dispatch == "fused":
+            self._send = _lib.EpSendArgs(
+                peers=ctypes.pointer(self.peers), x_q=x_q.data_ptr(), x_scale=xs.data_ptr(), xs_row=xs.stride(0),
+                xs_blk=xs.stride(1), ids=self.ids.data_ptr(), pos=self.pos.data_ptr(), send_order=self.send_order.data_ptr(),
+                counts_local=self.counts_local.data_ptr(), n_pairs=n_pairs, pitch=pitch, top_k=top_k, E_local=E_local, H=H,
+                cap_rows=cap, rank=self.rank, world=self.world)
         self.epoch = 0
         if self.world > 1:
             dist.barrier(group)
@@ -208,16 +220,23 @@ class EpMoeLayer:
             _lib.check(L.moe_ep_plan(P, _vp(self.ids.data_ptr()), _i64(self.n_pairs), self.rank, self.world, self.E_total,
                                      self.E_local, self.align, self.cap, _vp(self.counts_local.data_ptr()),
                                      _vp(self.offsets.data_ptr()), _vp(self.layout.data_ptr()), _vp(self.dst_base.data_ptr()),
-                                     _vp(self.pos.data_ptr()), _vp(self.ws.data_ptr()), ctypes.c_size_t(self.ws_bytes), st))
+                                     _vp(self.pos.data_ptr()),
+                                     _vp(self.send_order.data_ptr()) if self.dispatch == "fused" else None,
+                                     _vp(self.ws.data_ptr()), ctypes.c_size_t(self.ws_bytes), st))
             mark("plan")
-            _lib.check(L.moe_ep_dispatch(P, _vp(self.x_q.data_ptr()), _vp(self.xs.data_ptr()), _i64(self.xs.stride(0)),
-                                         _i64(self.xs.stride(1)), _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
-                                         _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap,
-                                         _i64(self.pitch), self.rank, self.world, st))
-            self._barrier(st)
-            mark("dispatch+barrier")
-            self.gemm1()
-            mark("gate_up_gemm")
+            if self.dispatch == "fused":
+                act = self.gemm1._act if self.fuse_act else (None, None, _i64(0), _i64(0), _i32(0))
+                _lib.check(L.moe_ep_gate_up_dispatch(ctypes.byref(self.gemm1._args), ctypes.byref(self._send), *act, st))
+                mark("dispatch+gate_up_gemm")
+            else:
+                _lib.check(L.moe_ep_dispatch(P, _vp(self.x_q.data_ptr()), _vp(self.xs.data_ptr()), _i64(self.xs.stride(0)),
+                                             _i64(self.xs.stride(1)), _vp(self.ids.data_ptr()), _vp(self.pos.data_ptr()),
+                                             _i64(self.n_pairs), self.top_k, self.E_local, self.H, self.cap,
+                                             _i64(self.pitch), self.rank, self.world, st))
+                self._barrier(st)
+                mark("dispatch+barrier")
+                self.gemm1()
+                mark("gate_up_gemm")
             if not self.fuse_act:
                 _lib.check(L.moe_silu_mul_requant(_vp(self.g1.data_ptr()), _vp(self.a2.data_ptr()), _vp(self.s2.data_ptr()),
                                                   _i64(1), _i64(self.cap), _vp(self.layout.data_ptr()), _i32(self.cap),
