@@ -72,6 +72,9 @@ extern "C" {
  *           stored at d + r*ldd but at scatter_base[meta >> 24] + (meta & 0xFFFFFF)*ldd, meta = scatter_meta[r]:
  *           the expert-parallel down GEMM uses it to store every output row directly into the slot of the
  *           rank that owns the token (bases may be peer-mapped memory of other GPUs; plain stores).
+ *   scatter_meta_stride  distance in int32 elements between the entries of consecutive rows (0 = 1: a dense array).
+ *           The dispatching GEMM (moe_ep_gate_up_dispatch) leaves every row's return address inside its record, at
+ *           byte H + H/32: pass that word of the first record with a stride of pitch / 4.
  * Requirements: K % 128 == 0, N % 8 == 0, a/b 16-byte aligned, d 16-byte aligned, ldd % 8 == 0.
  */
 typedef struct moe_gg_args {
@@ -96,6 +99,7 @@ typedef struct moe_gg_args {
     int64_t lda;
     int64_t ldb;
     int32_t accumulate;
+    int64_t scatter_meta_stride;
 } moe_gg_args;
 
 /* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With
@@ -369,7 +373,8 @@ int moe_ep_dispatch(const moe_ep_peers* peers, const void* x_q, const float* x_s
 /* gate_up grouped GEMM that carries the dispatch all-to-all itself (ONE kernel: the transfer overlaps the GEMM tile
  * by tile and needs neither moe_ep_dispatch nor the barrier behind it).  One warp of every CTA stores this rank's
  * token records into the owners' receive buffers in `send_order`, and counts each row into the owner's arrival
- * counter of its expert once the store has completed; the GEMM's loader warps wait, per expert and with the usual
+ * counter of its expert once the store has completed (a record = H e4m3 bytes, H/128 fp32 scales, then the row's
+ * return address (rank << 24) | pair as one int32: pitch >= H + H/32 + 4); the GEMM's loader warps wait, per expert and with the usual
  * 2 s bound, until counts_local[expert] rows have arrived, then multiply them.  The counters live at
  * peers->flags[r] + 64 (int32 [E_local]); moe_ep_count_publish clears them at the start of every forward.
  *   gemm   the gate_up GEMM over this rank's receive buffer exactly as moe_gg_fp8_contiguous would get it
@@ -416,11 +421,13 @@ int moe_gg_fp8_gate_up_act(const moe_gg_args* args, void* act_q, float* act_scal
  * Values are read once per call, so a change applies from the next call of any thread. */
 #define MOE_OPT_GG_BLOCK_SCALED 0        /* 1 (default): power-of-two scales take the block-scaled-MMA kernels when
                                           * workspace is given; 0: always the promotion kernel */
-#define MOE_OPT_MX_TILE 1                /* block-scaled kernel: AUTO = CTA pairs for the contiguous layout, one CTA
-                                          * per tile for the masked layout */
+#define MOE_OPT_MX_TILE 1                /* block-scaled kernel: AUTO = CTA pairs (256-column tiles) for the contiguous
+                                          * layout, one CTA per tile for the masked layout */
 #define MOE_MX_TILE_AUTO 0
 #define MOE_MX_TILE_PAIR 1
 #define MOE_MX_TILE_SINGLE 2
+#define MOE_MX_TILE_PAIR_240 3           /* CTA pairs, 240-column tiles, two accumulators (measurement variant) */
+#define MOE_MX_TILE_PAIR_224 4           /* CTA pairs, 224-column tiles, two accumulators (measurement variant) */
 #define MOE_OPT_ALPHA_PATH 2             /* decode-regime layer: AUTO = two CUDA-core kernels up to the route
                                           * threshold, else swapped-operand tensor-core kernels; the others force
                                           * the tensor-core pipeline and choose the tiling of its two projections */

@@ -63,28 +63,23 @@ def grouped_gemm_rows(a, sfa, b, sfb, row_group, d, target_rows=64, model=None, 
     `groups`: restrict the sample to these groups (bounds the cost of decoding B)."""
     model = orc.SIM_CHAIN if model is None else model
     rg = row_group.to(torch.int64)
-    ok_rows = rg >= 0
-    if groups is not None:
-        keep = torch.zeros_like(ok_rows)
-        for g in groups:
-            keep |= rg == int(g)
-        ok_rows &= keep
-    valid = torch.nonzero(ok_rows).flatten()
-    if valid.numel() == 0:
-        return dict(ok=True, rows=0, elements=0, max_rel_err=0.0, identical=1.0, calc_diff=0.0)
-    idx = sample_rows(valid, target_rows)
-    used = torch.unique(rg[idx]).tolist()
-    remap = {int(g): i for i, g in enumerate(used)}
+    present = torch.unique(rg[rg >= 0]).tolist()
+    glist = [int(g) for g in (groups if groups is not None else present) if int(g) in set(present)]
+    if not glist:
+        return dict(ok=True, rows=0, groups=0, elements=0, max_rel_err=0.0, identical=1.0, calc_diff=0.0)
+    per_group = max(1, -(-target_rows // len(glist)))
+    idx = torch.cat([sample_rows(torch.nonzero(rg == g).flatten(), per_group) for g in glist])
+    remap = {g: i for i, g in enumerate(glist)}
     gl = np.array([remap[int(g)] for g in rg[idx].tolist()], np.int32)
-    gsel = torch.tensor(used, device=b.device, dtype=torch.long)
-    A = _u8(a[idx])
+    gsel = torch.tensor(glist, device=b.device, dtype=torch.long)
+    A = a.view(torch.uint8)[idx].cpu().numpy()
     SA = sfa[idx].float().cpu().numpy()
-    B = _u8(b.index_select(0, gsel))
+    B = b.view(torch.uint8).index_select(0, gsel).cpu().numpy()
     SB = sfb.index_select(0, gsel).float().cpu().numpy()
     ref = orc.gg_contiguous(A, B, SA, SB, gl, model=model)
     res = compare_bf16(_bits(d[idx]), ref)
     res["rows"] = int(idx.numel())
-    res["groups"] = len(used)
+    res["groups"] = len(glist)
     return res
 
 
@@ -175,7 +170,9 @@ def ep_layer_check(layer, data: dict, world: int, rank: int, tokens: int = 64, r
     pick = sample_rows(have, experts).tolist() if have.numel() else []
     lay_full = torch.full((layer.cap,), -1, dtype=torch.int32, device=dev)
     lay_full[:used] = lay
-    res["gate_up"] = grouped_gemm_rows(layer.a1_t, layer.s1_t, w13, s13, lay_full, layer.g1, rows, groups=pick)
+    fused = bool(layer.fuse_act)            # SiLU*mul requant inside the gate_up GEMM: no gate_up matrix in memory
+    if not fused:
+        res["gate_up"] = grouped_gemm_rows(layer.a1_t, layer.s1_t, w13, s13, lay_full, layer.g1, rows, groups=pick)
     keep = torch.zeros(layer.cap, dtype=torch.bool, device=dev)
     for g in pick:
         keep |= lay_full == int(g)
@@ -183,12 +180,21 @@ def ep_layer_check(layer, data: dict, world: int, rank: int, tokens: int = 64, r
     n = int(R.numel())
     if n:
         s2_rows = layer.s2.t()[R].float().cpu().numpy()
-        res["act"] = silu_requant_rows(_bits(layer.g1[R]), _u8(layer.a2[R]), s2_rows, layer.gate_first)
+        a2_rows = layer.a2.view(torch.uint8)[R].cpu().numpy()
         used_g = torch.unique(lay_full[R]).tolist()
         remap = {int(g): i for i, g in enumerate(used_g)}
         gl = np.array([remap[int(g)] for g in lay_full[R].tolist()], np.int32)
         gsel = torch.tensor(used_g, device=dev, dtype=torch.long)
-        yref = orc.gg_contiguous(_u8(layer.a2[R]), _u8(w2.index_select(0, gsel)), s2_rows,
+        if fused:
+            # the epilogue requantises the fp32 accumulator: oracle gate_up kept in fp32 (per-K-block promotion model)
+            g32 = orc.gg_contiguous(layer.a1_t.view(torch.uint8)[R].cpu().numpy(),
+                                    w13.view(torch.uint8).index_select(0, gsel).cpu().numpy(),
+                                    layer.s1_t[R].float().cpu().numpy(), s13.index_select(0, gsel).float().cpu().numpy(), gl,
+                                    model=orc.BLOCK_PROMOTE, out_f32=True)
+            res["gate_up+act"] = silu_requant_rows(g32, a2_rows, s2_rows, layer.gate_first)
+        else:
+            res["act"] = silu_requant_rows(_bits(layer.g1[R]), a2_rows, s2_rows, layer.gate_first)
+        yref = orc.gg_contiguous(a2_rows, w2.view(torch.uint8).index_select(0, gsel).cpu().numpy(), s2_rows,
                                  s2w.index_select(0, gsel).float().cpu().numpy(), gl)          # bf16 bits [n, H]
     else:
         res["act"] = dict(ok=True, rows=0)

@@ -25,7 +25,7 @@ class GGArgs(_c.Structure):
         ("workspace", _c.c_void_p), ("workspace_bytes", _c.c_uint64),
         ("scatter_meta", _c.c_void_p), ("scatter_base", _c.c_void_p * 8),
         ("sf_format", _c.c_int32), ("sfb_stride", _c.c_int64 * 3), ("lda", _c.c_int64),
-        ("ldb", _c.c_int64), ("accumulate", _c.c_int32),
+        ("ldb", _c.c_int64), ("accumulate", _c.c_int32), ("scatter_meta_stride", _c.c_int64),
     ]
 
 
@@ -134,7 +134,7 @@ _SIZE_T_RETURN = ("moe_gg_workspace_bytes", "moe_permute_workspace_bytes", "moe_
 
 # moe_set_option keys and values (include/b200moe.h)
 OPT_GG_BLOCK_SCALED, OPT_MX_TILE, OPT_ALPHA_PATH, OPT_ALPHA_GEMV_MAX_ROUTES, OPT_KG_MODE, OPT_EP_WAIT_LIMIT_MS = range(6)
-MX_TILE_AUTO, MX_TILE_PAIR, MX_TILE_SINGLE = range(3)
+MX_TILE_AUTO, MX_TILE_PAIR, MX_TILE_SINGLE, MX_TILE_PAIR_240, MX_TILE_PAIR_224 = range(5)
 ALPHA_PATH_AUTO, ALPHA_PATH_SWAP, ALPHA_PATH_MASKED, ALPHA_PATH_MIXED = range(4)
 KG_MODE_MN_MAJOR, KG_MODE_TRANSPOSE, KG_MODE_PER_GROUP = range(3)
 

@@ -115,15 +115,17 @@ struct MxLayout {
     size_t flag_off, sfa_off, sfb_off, bytes;
     int row_blocks, quads;
 };
+// SFB tiles are packed per column tile of the kernel that will run (240 or 256 columns wide, two 512-byte halves
+// each); the size covers the narrower tile, i.e. the larger count.
 MxLayout mx_layout(int G, long long rows_total, int N, int K) {
     MxLayout l;
     l.row_blocks = (int)((rows_total + 127) / 128);
     l.quads = (K / 128 + 3) / 4;
-    const int nb128 = (N + 127) / 128;
+    const int n_tiles = (N + 223) / 224;          // the narrowest tile any variant of the pair kernel uses
     l.flag_off = 0;
     l.sfa_off = 256;
     l.sfb_off = l.sfa_off + (size_t)l.row_blocks * l.quads * 512;
-    l.bytes = l.sfb_off + (size_t)G * nb128 * l.quads * 512;
+    l.bytes = l.sfb_off + (size_t)G * n_tiles * l.quads * 1024;
     return l;
 }
 
@@ -165,6 +167,10 @@ int device_info(DeviceInfo** out) {
                                       mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute((gg_fp8_mx_kernel<false, false, false, 240>), cudaFuncAttributeMaxDynamicSharedMemorySize, mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute((gg_fp8_mx_kernel<true, false, false, 240>), cudaFuncAttributeMaxDynamicSharedMemorySize, mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute((gg_fp8_mx_kernel<false, false, false, 224>), cudaFuncAttributeMaxDynamicSharedMemorySize, mx::SMEM_BYTES));
+        CUDA_TRY(cudaFuncSetAttribute((gg_fp8_mx_kernel<true, false, false, 224>), cudaFuncAttributeMaxDynamicSharedMemorySize, mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       mx::SMEM_BYTES));
         CUDA_TRY(cudaFuncSetAttribute(gg_fp8_mx_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -263,6 +269,7 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.mode_gen = 0;
     p.act_q = nullptr; p.act_s = nullptr; p.act_ss_r = 0; p.act_ss_b = 0; p.inter = 0; p.gate_first = 0;
     p.scatter_meta = MASKED ? nullptr : a->scatter_meta;
+    p.scatter_meta_stride = a->scatter_meta_stride > 0 ? a->scatter_meta_stride : 1;
     for (int i = 0; i < 8; ++i) p.scatter_base[i] = static_cast<__nv_bfloat16*>(a->scatter_base[i]);
     if (p.scatter_meta != nullptr && a->d_dtype != MOE_DTYPE_BF16)
         return fail(MOE_ERR_INVALID, "scattered output is bf16 only");
@@ -271,6 +278,10 @@ int launch_gg(const moe_gg_args* a, void* stream) {
     p.d_f32 = a->d_dtype == MOE_DTYPE_F32;
     p.d_accumulate = a->accumulate ? 1 : 0;
     p.trace = nullptr;
+#ifdef B200MOE_DEV_TRACE
+    // developer build only: device address of an int64 [grid][8] array of per-role wait-cycle counters
+    if (const char* e = getenv("B200MOE_GG_TRACE")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 10));
+#endif
     p.G = a->G; p.M = a->M; p.N = a->N; p.K = a->K;
     p.rows_total = (int)rows_total;
     p.num_n_blocks = (a->N + gg::BN - 1) / gg::BN;
@@ -292,44 +303,66 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         ws.sfb_packed = reinterpret_cast<uint32_t*>(wsb + ml.sfb_off);
         ws.row_blocks = ml.row_blocks;
         ws.quads = ml.quads;
+        // measured: CTA pairs win on full 256-row blocks (contiguous layout), single CTAs on the masked
+        // layout, where a pair multiplies up to 255 empty rows per group
+        const int mx_tile = opt(MOE_OPT_MX_TILE);
+        const bool mx_single = mx_tile == MOE_MX_TILE_AUTO ? MASKED : mx_tile == MOE_MX_TILE_SINGLE;
+        // column tiles: 256 wide for the single-CTA kernel; for the pair kernel at most 240 wide and balanced in
+        // units of 16 columns (all tiles 224 or 240 wide where N allows it: no narrow last tile)
+        if (mx_single) {
+            ws.n_tiles = (a->N + mx1::BN - 1) / mx1::BN;
+            ws.nt_base = mx1::BN / 16; ws.nt_rem = 0;
+        } else {
+            const int tn = mx_tile == MOE_MX_TILE_PAIR_240 ? 240 : (mx_tile == MOE_MX_TILE_PAIR_224 ? 224 : mx::BN);
+            const int units = (a->N + 15) / 16;
+            ws.n_tiles = (a->N + tn - 1) / tn;
+            ws.nt_base = units / ws.n_tiles; ws.nt_rem = units % ws.n_tiles;
+        }
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         ws.gen = p.mode_gen = next_gen();
-        dim3 pgrid(ml.row_blocks + a->G * p.nb128, ml.quads, 1);
+        dim3 pgrid(ml.row_blocks + a->G * ws.n_tiles * 2, ml.quads, 1);
         if (packed_sf)
             mx_prep_packed_kernel<<<pgrid, 128, 0, st>>>(
                 reinterpret_cast<const uint32_t*>(a->sfa), a->sfa_stride_row, a->sfa_stride_kblk,
                 reinterpret_cast<const uint32_t*>(a->sfb), a->sfb_stride[0], a->sfb_stride[1], a->sfb_stride[2],
-                (int)rows_total, a->N, a->G, p.nb128, ws);
+                (int)rows_total, a->N, a->G, ws);
         else
             mx_prep_kernel<<<pgrid, 128, 0, st>>>(a->sfa, a->sfa_stride_row, a->sfa_stride_kblk, a->sfb, (int)rows_total,
                                                   p.num_k_blocks, a->G, p.nb128, ws, a->layout, MASKED ? a->M : 0,
                                                   p.rows_used);
         CUDA_TRY(cudaGetLastError());
-        // measured: CTA pairs win on full 256-row blocks (contiguous layout), single CTAs on the masked
-        // layout, where a pair multiplies up to 255 empty rows per group
-        const int mx_tile = opt(MOE_OPT_MX_TILE);
-        const bool mx_single = mx_tile == MOE_MX_TILE_AUTO ? MASKED : mx_tile == MOE_MX_TILE_SINGLE;
         CUtensorMap tmap_b2, tmap_sfa, tmap_sfb;
-        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx_single ? mx1::BN : mx::BN / 2,
+        const int pair_tn = mx_tile == MOE_MX_TILE_PAIR_240 ? 240 : (mx_tile == MOE_MX_TILE_PAIR_224 ? 224 : mx::BN);
+        rc = encode_fp8_kmajor(&tmap_b2, a->b, (uint64_t)a->G * a->N, (uint64_t)a->K, mx_single ? mx1::BN : pair_tn / 2,
                                (uint64_t)a->ldb);
         if (rc != MOE_OK) return rc;
         rc = encode_words_1d(&tmap_sfa, ws.sfa_packed, (uint64_t)ml.row_blocks * ml.quads * 128);
         if (rc != MOE_OK) return rc;
-        rc = encode_words_1d(&tmap_sfb, ws.sfb_packed, (uint64_t)a->G * p.nb128 * ml.quads * 128);
+        rc = encode_words_1d(&tmap_sfb, ws.sfb_packed, (uint64_t)a->G * ws.n_tiles * ml.quads * 256);
         if (rc != MOE_OK) return rc;
+        GGParams pm = p;                 // the block-scaled kernels count column tiles of their own width
+        pm.num_n_blocks = ws.n_tiles;
+        pm.nt_base = ws.nt_base; pm.nt_rem = ws.nt_rem;
         if (mx_single) {
-            const long long tiles1 = (MASKED ? (long long)a->G * p.num_m_blocks : (long long)p.num_m_blocks) * p.num_n_blocks;
+            const long long tiles1 = (MASKED ? (long long)a->G * p.num_m_blocks : (long long)p.num_m_blocks) * pm.num_n_blocks;
             int grid1 = (int)(tiles1 < di->num_sms ? tiles1 : di->num_sms);
             if (grid1 < 1) grid1 = 1;
-            gg_fp8_mx1_kernel<MASKED><<<grid1, mx1::THREADS, mx1::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
+            gg_fp8_mx1_kernel<MASKED><<<grid1, mx1::THREADS, mx1::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, pm,
                                                                                    ws.flag, ml.quads, di->status);
         } else {
             const long long row_blocks256 = MASKED ? (long long)a->G * ((a->M + 255) / 256) : (a->M + 255) / 256;
-            const long long tiles = row_blocks256 * p.num_n_blocks;
+            const long long tiles = row_blocks256 * pm.num_n_blocks;
             int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
             if (pairs < 1) pairs = 1;
-            gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, p,
-                                                                                   ws.flag, ml.quads, di->status, KgNone{});
+            if (mx_tile == MOE_MX_TILE_PAIR_240)
+                gg_fp8_mx_kernel<MASKED, false, false, 240><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(
+                    tmap_a, tmap_b2, tmap_sfa, tmap_sfb, pm, ws.flag, ml.quads, di->status, KgNone{});
+            else if (mx_tile == MOE_MX_TILE_PAIR_224)
+                gg_fp8_mx_kernel<MASKED, false, false, 224><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(
+                    tmap_a, tmap_b2, tmap_sfa, tmap_sfb, pm, ws.flag, ml.quads, di->status, KgNone{});
+            else
+                gg_fp8_mx_kernel<MASKED><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(tmap_a, tmap_b2, tmap_sfa, tmap_sfb, pm,
+                                                                                       ws.flag, ml.quads, di->status, KgNone{});
         }
         CUDA_TRY(cudaGetLastError());
         p.mode_flag = ws.flag;           // the promotion kernel below runs only if the flag was raised
@@ -544,7 +577,7 @@ KgWorkspace carve_kg(void* base, int64_t M, int64_t N, int64_t K_total) {
     const size_t max_quads = (size_t)(K_total / 128);
     w.flag = reinterpret_cast<int*>(take(256));
     w.sfa_tiles = reinterpret_cast<uint32_t*>(take((size_t)((M + 127) / 128) * max_quads * 512));
-    w.sfb_tiles = reinterpret_cast<uint32_t*>(take((size_t)((N + 127) / 128) * max_quads * 512));
+    w.sfb_tiles = reinterpret_cast<uint32_t*>(take((size_t)((N + mx::BN_WIDE - 1) / mx::BN_WIDE) * max_quads * 1024));
     w.bytes = off;
     return w;
 }
@@ -872,7 +905,7 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
         p.d = A->d; p.ldd = A->N; p.d_f32 = 1; p.d_accumulate = 1;
         p.G = A->G; p.M = A->M; p.N = A->N; p.K = (int)A->K_total;
         p.rows_total = A->M;
-        p.num_n_blocks = (A->N + mx::BN - 1) / mx::BN;
+        p.num_n_blocks = (A->N + mx::BN_WIDE - 1) / mx::BN_WIDE;
         p.num_k_blocks = 0;
         p.nb128 = (A->N + 127) / 128;
         p.num_m_blocks = (A->M + 127) / 128;
@@ -880,10 +913,12 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
         MxWorkspace ws;
         ws.flag = w.flag; ws.sfa_packed = w.sfa_tiles; ws.sfb_packed = w.sfb_tiles;
         ws.row_blocks = (A->M + 127) / 128; ws.quads = quads;
+        ws.n_tiles = p.num_n_blocks; ws.nt_base = mx::BN_WIDE / 16; ws.nt_rem = 0;
+        p.nt_base = ws.nt_base; p.nt_rem = 0;
         ws.gen = p.mode_gen = next_gen();
-        dim3 pgrid(ws.row_blocks + p.nb128, quads, 1);
+        dim3 pgrid(ws.row_blocks + ws.n_tiles * 2, quads, 1);
         mx_prep_packed_kernel<<<pgrid, 128, 0, st>>>(reinterpret_cast<const uint32_t*>(A->sfa), 1, A->M,
-                                                     reinterpret_cast<const uint32_t*>(A->sfb), 0, 1, A->N, A->M, A->N, 1, p.nb128, ws);
+                                                     reinterpret_cast<const uint32_t*>(A->sfb), 0, 1, A->N, A->M, A->N, 1, ws);
         CUDA_TRY(cudaGetLastError());
         CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
         if (mn_major) {      // the caller's matrices as they are: [K_total rows, M or N bytes], box = 128 K rows x 128 bytes
@@ -894,12 +929,12 @@ int moe_kg_fp8_contiguous(const moe_kg_args* A, void* stream) {
         } else {
             rc = encode_fp8_kmajor(&tm_a, w.at, (uint64_t)A->M, (uint64_t)A->K_total, 128);
             if (rc != MOE_OK) return rc;
-            rc = encode_fp8_kmajor(&tm_b, w.bt, (uint64_t)A->N, (uint64_t)A->K_total, mx::BN / 2);
+            rc = encode_fp8_kmajor(&tm_b, w.bt, (uint64_t)A->N, (uint64_t)A->K_total, mx::BN_WIDE / 2);
             if (rc != MOE_OK) return rc;
         }
         rc = encode_words_1d(&tm_sfa, ws.sfa_packed, (uint64_t)ws.row_blocks * quads * 128);
         if (rc != MOE_OK) return rc;
-        rc = encode_words_1d(&tm_sfb, ws.sfb_packed, (uint64_t)p.nb128 * quads * 128);
+        rc = encode_words_1d(&tm_sfb, ws.sfb_packed, (uint64_t)ws.n_tiles * quads * 256);
         if (rc != MOE_OK) return rc;
         const long long tiles = (long long)kg.n * kg.per_group;
         int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
@@ -1244,9 +1279,9 @@ int moe_ep_gate_up_dispatch(const moe_gg_args* a, const moe_ep_send_args* S, voi
     if (!fused && (a->d_dtype != MOE_DTYPE_BF16 || a->ldd < a->N || a->ldd % 8)) return fail(MOE_ERR_INVALID, "d must be bf16 with ldd >= N, ldd %% 8 == 0");
     if (S->n_pairs < 0 || S->n_pairs > (1ll << 24) || S->top_k <= 0 || S->n_pairs % S->top_k)
         return fail(MOE_ERR_INVALID, "n_pairs must be a multiple of top_k and at most 2^24");
-    const long long rec = ((long long)S->H + S->H / 32 + 15) & ~15ll;
+    const long long rec = ((long long)S->H + S->H / 32 + 4 + 15) & ~15ll;       // row, scales, return address
     if (rec > EP_SEND_RECORD_MAX) return fail(MOE_ERR_UNSUPPORTED, "H=%d: a token record must fit %d bytes", S->H, EP_SEND_RECORD_MAX);
-    if (S->pitch < rec || S->pitch % 16 || a->lda != S->pitch) return fail(MOE_ERR_INVALID, "pitch must be >= H + H/32, a multiple of 16, and equal to lda");
+    if (S->pitch < rec || S->pitch % 16 || a->lda != S->pitch) return fail(MOE_ERR_INVALID, "pitch must be >= H + H/32 + 4, a multiple of 16, and equal to lda");
     if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->b) & 15) || (reinterpret_cast<uintptr_t>(S->x_q) & 15) ||
         (reinterpret_cast<uintptr_t>(fused ? act_q : a->d) & 15))
         return fail(MOE_ERR_INVALID, "a, b, x_q and the output must be 16-byte aligned");
@@ -1281,7 +1316,6 @@ int moe_ep_gate_up_dispatch(const moe_gg_args* a, const moe_ep_send_args* S, voi
     EpSend& e = p.ep;
     for (int i = 0; i < EP_MAX_WORLD; ++i) {
         e.a[i] = static_cast<uint8_t*>(S->peers->a[i]);
-        e.meta[i] = S->peers->meta[i];
         e.arrive[i] = S->peers->flags[i] ? S->peers->flags[i] + EP_ARRIVE_OFFSET : nullptr;
     }
     e.x = static_cast<const uint8_t*>(S->x_q); e.xs = S->x_scale; e.xs_r = S->xs_row; e.xs_b = S->xs_blk; e.pitch = S->pitch;
@@ -1377,7 +1411,7 @@ int moe_set_option(int32_t option, int32_t value) {
     bool ok = true;
     switch (option) {
         case MOE_OPT_GG_BLOCK_SCALED: ok = value == 0 || value == 1; break;
-        case MOE_OPT_MX_TILE: ok = value >= MOE_MX_TILE_AUTO && value <= MOE_MX_TILE_SINGLE; break;
+        case MOE_OPT_MX_TILE: ok = value >= MOE_MX_TILE_AUTO && value <= MOE_MX_TILE_PAIR_224; break;
         case MOE_OPT_ALPHA_PATH: ok = value >= MOE_ALPHA_PATH_AUTO && value <= MOE_ALPHA_PATH_MIXED; break;
         case MOE_OPT_ALPHA_GEMV_MAX_ROUTES: ok = value >= 0 && value <= 32768; break;
         case MOE_OPT_KG_MODE: ok = value >= MOE_KG_MODE_MN_MAJOR && value <= MOE_KG_MODE_PER_GROUP; break;

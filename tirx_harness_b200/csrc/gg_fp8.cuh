@@ -85,7 +85,8 @@ struct GGParams {
     int mode_gen;                // generation number of the call (block-scaled path)
     // scattered output (expert-parallel down GEMM): row r is stored at scatter_base[meta >> 24] + (meta & 0xFFFFFF) * ldd
     // with meta = scatter_meta[r]; the bases may be other GPUs' memory (plain stores only)
-    const int* scatter_meta;
+    const int* scatter_meta;     // meta of row r at scatter_meta[r * scatter_meta_stride]
+    long long scatter_meta_stride;
     __nv_bfloat16* scatter_base[8];
     // fused SiLU*mul requant (FUSE_ACT kernels): N = 2*inter, outputs replace d
     uint8_t* act_q;              // e4m3 [M, inter]
@@ -104,7 +105,18 @@ struct GGParams {
     int num_k_blocks;            // K / 128
     int nb128;                   // ceil(N / 128)
     int num_m_blocks;            // contiguous: ceil(M / BM)
+    // block-scaled kernels: column tiles of balanced width, in units of 16 columns: the first nt_rem tiles are
+    // nt_base + 1 units wide, the others nt_base (all of them 224 or 240 columns where N allows it)
+    int nt_base, nt_rem;
 };
+
+// first column and width of column tile nt of a block-scaled kernel
+__host__ __device__ __forceinline__ int mx_tile_col0(int nt_base, int nt_rem, int nt) {
+    return 16 * (nt * nt_base + (nt < nt_rem ? nt : nt_rem));
+}
+__host__ __device__ __forceinline__ int mx_tile_width(int nt_base, int nt_rem, int nt) {
+    return 16 * (nt_base + (nt < nt_rem ? 1 : 0));
+}
 
 struct Tile {
     int m0;          // first row of the tile in the flattened A / D
@@ -510,76 +522,125 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             cp_async_wait_all();      // nothing may still be writing this CTA's shared memory at exit
         } else if (DISPATCH) {
             // ------------------------------------------------ sender of the dispatch all-to-all (warp 3)
-            // Per pair: the token's record (e4m3 row by a bulk load, scales by the lanes) is assembled in one of
+            // This warp owns pairs order[blockIdx.x + i * gridDim.x].  Per pair the token's record -- e4m3 row (bulk
+            // load), its scales and the row's return address (written by the lanes) -- is assembled in one of
             // EP_SEND_BUFFERS shared-memory buffers and leaves as ONE bulk store into the owner's receive buffer.
-            // Lane 0 issues all bulk operations, so its bulk groups complete in order: once at most
-            // EP_SEND_BUFFERS - 1 groups are pending, the store issued EP_SEND_BUFFERS iterations ago has completed
-            // -- its buffer is free again and its row can be counted as arrived (release at system scope).
+            // Software pipeline: the load of pair i is in flight while pair i-1 is stored and pair i-2's store
+            // drains.  Lane 0 issues every bulk operation and commits exactly one bulk group per pair, so group
+            // numbers are pair numbers: "at most EP_SEND_BUFFERS - 2 groups pending" means the store that used the
+            // buffer about to be refilled has completed -- the buffer is free and the row can be counted as arrived
+            // (fence + release at system scope; consecutive rows for the same counter are counted together).
+            // Routing data of 32 pairs is fetched at once, one pair per lane.
             const EpSend& ep = p.ep;
             uint8_t* stage_base = smem + PREFIX_AT;
-            const int rec = (ep.H + (ep.H >> 5) + 15) & ~15;
-            int* pending[EP_SEND_BUFFERS];
+            const int meta_off = ep.H + (ep.H >> 5);
+            const int rec = (meta_off + 4 + 15) & ~15;
+            const int stride = gridDim.x;
+            const int my_rows = ep.n_pairs > (int)blockIdx.x ? (ep.n_pairs - 1 - (int)blockIdx.x) / stride + 1 : 0;
+            int* pend[EP_SEND_BUFFERS];                  // arrival counter of the row last stored from each buffer
 #pragma unroll
-            for (int b = 0; b < EP_SEND_BUFFERS; ++b) pending[b] = nullptr;
+            for (int b = 0; b < EP_SEND_BUFFERS; ++b) pend[b] = nullptr;
+            int* sig_ptr = nullptr;                      // rows completed but not yet counted in
+            int sig_cnt = 0;
+            auto count_in = [&](int* ctr) {              // lane 0 only
+                if (ctr == nullptr) return;
+                if (ctr != sig_ptr && sig_cnt > 0) {
+                    __threadfence_system();
+                    red_release_sys_add(sig_ptr, sig_cnt);
+                    sig_cnt = 0;
+                }
+                sig_ptr = ctr;
+                ++sig_cnt;
+            };
             bool ok = true;
-            int it = 0;
-            for (int slot = blockIdx.x; ok && slot < ep.n_pairs; slot += gridDim.x, ++it) {
-                const int b = it % EP_SEND_BUFFERS;
-                const uint32_t par = (it / EP_SEND_BUFFERS) & 1;
-                int* done = nullptr;
+            // state of the pair whose load is in flight (finished one step later)
+            int started = -1;                            // last pair whose record load was issued
+            int prev_row = -1, prev_d = 0;
+            int* prev_ctr = nullptr;
+            auto finish = [&](int it_prev) {             // store pair it_prev (its load was started one step earlier)
+                const int b = it_prev % EP_SEND_BUFFERS;
+                ok = mbar_wait_warp(send_bar + 8 * b, (uint32_t)(it_prev / EP_SEND_BUFFERS) & 1u, abort_flag, status,
+                                    STATUS_TIMEOUT_SMEM_FULL);
+                if (lane == 0) {
+                    if (ok)
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                     ::"l"(ep.a[prev_d] + (long long)prev_row * ep.pitch),
+                                       "r"(smem_u32(stage_base + b * EP_SEND_RECORD_MAX)), "r"(rec) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
 #pragma unroll
-                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (i == b) done = pending[i];
-                if (lane == 0) {
-                    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(EP_SEND_BUFFERS - 1) : "memory");
-                    if (done != nullptr) {
-                        __threadfence_system();
-                        red_release_sys_add(done, 1);
+                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (i == b) pend[i] = ok ? prev_ctr : nullptr;
+            };
+            for (int base = 0; ok && base < my_rows; base += 32) {
+                int m_pr = 0, m_row = -1, m_e = 0;
+                if (base + lane < my_rows) {
+                    m_pr = __ldg(ep.order + blockIdx.x + (long long)(base + lane) * stride);
+                    m_row = __ldg(ep.pos + m_pr);
+                    m_e = __ldg(ep.ids + m_pr);
+                }
+                const int cnt = my_rows - base < 32 ? my_rows - base : 32;
+                for (int i = 0; ok && i < cnt; ++i) {
+                    const int it = base + i;
+                    const int b = it % EP_SEND_BUFFERS;
+                    const int pr = __shfl_sync(0xffffffffu, m_pr, i);
+                    const int row = __shfl_sync(0xffffffffu, m_row, i);
+                    const int e = __shfl_sync(0xffffffffu, m_e, i);
+                    if (row < 0 || row >= ep.cap_rows) {            // the owner's buffer is too small: give up, report
+                        if (lane == 0) atomicOr(status, STATUS_CAPACITY);
+                        ok = false;
+                        break;
                     }
-                }
-                __syncwarp();
-                int pr = 0, row = -1, e = 0;
-                if (lane == 0) {
-                    pr = __ldg(ep.order + slot);
-                    row = __ldg(ep.pos + pr);
-                    e = __ldg(ep.ids + pr);
-                }
-                pr = __shfl_sync(0xffffffffu, pr, 0);
-                row = __shfl_sync(0xffffffffu, row, 0);
-                e = __shfl_sync(0xffffffffu, e, 0);
-                const int d = e / ep.E_local, j = e - d * ep.E_local;
-                const long long t = pr / ep.top_k;
-                int* next_pending = nullptr;
-                if (row >= 0 && row < ep.cap_rows) {
-                    uint8_t* buf = stage_base + b * EP_SEND_RECORD_MAX;
-                    const uint32_t bar = send_bar + 8 * b;
+                    // (1) buffer b free again; the row it carried EP_SEND_BUFFERS pairs ago has arrived
+                    int* done = nullptr;
+#pragma unroll
+                    for (int k = 0; k < EP_SEND_BUFFERS; ++k) if (k == b) done = pend[k];
                     if (lane == 0) {
-                        mbar_arrive_expect_tx(bar, (uint32_t)ep.H);
+                        asm volatile("cp.async.bulk.wait_group %0;" ::"n"(EP_SEND_BUFFERS - 2) : "memory");
+                        count_in(done);
+                    }
+                    __syncwarp();
+                    // (2) start assembling pair `it` in buffer b
+                    const long long t = pr / ep.top_k;
+                    uint8_t* buf = stage_base + b * EP_SEND_RECORD_MAX;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(send_bar + 8 * b, (uint32_t)ep.H);
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                     ::"r"(smem_u32(buf)), "l"(ep.x + t * ep.H), "r"(ep.H), "r"(bar) : "memory");
+                                     ::"r"(smem_u32(buf)), "l"(ep.x + t * ep.H), "r"(ep.H), "r"(send_bar + 8 * b) : "memory");
+                        *reinterpret_cast<int*>(buf + meta_off) = (ep.rank << 24) | pr;     // where the result goes back to
                     }
                     float* sbuf = reinterpret_cast<float*>(buf + ep.H);
                     for (int bk = lane; bk < (ep.H >> 7); bk += 32) sbuf[bk] = __ldg(ep.xs + t * ep.xs_r + (long long)bk * ep.xs_b);
                     fence_proxy_async_smem();
-                    ok = mbar_wait_warp(bar, par, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                    if (ok && lane == 0) {
-                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                                     ::"l"(ep.a[d] + (long long)row * ep.pitch), "r"(smem_u32(buf)), "r"(rec) : "memory");
-                        ep.meta[d][row] = (ep.rank << 24) | pr;      // where the row's result has to go back to
-                    }
-                    if (ok) next_pending = ep.arrive[d] + j;
-                } else if (row >= ep.cap_rows && lane == 0) {
-                    atomicOr(status, STATUS_CAPACITY);               // the owner's buffer is too small: row dropped
+                    __syncwarp();
+                    started = it;
+                    // (3) store the pair started one step ago
+                    if (it > 0) finish(it - 1);
+                    prev_row = row;
+                    prev_d = e / ep.E_local;
+                    prev_ctr = ep.arrive[prev_d] + (e - prev_d * ep.E_local);
                 }
-                if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (i == b) pending[i] = next_pending;
             }
-            // drain: every store complete (also on the failure path), then the last rows are counted
+            if (ok && my_rows > 0) finish(my_rows - 1);
+            // Unwinding after a failed wait: a record load that was started but never stored gets a bounded chance
+            // to land before the CTA exits.
+            if (!ok && started >= 0 && lane == 0) {
+                const uint32_t bar = send_bar + 8 * (started % EP_SEND_BUFFERS);
+                const uint32_t par = (uint32_t)(started / EP_SEND_BUFFERS) & 1u;
+                for (int spin = 0; spin < (1 << 20); ++spin)
+                    if (mbar_try_wait(bar, par)) break;
+            }
+            // drain: every store complete (also on the failure path), then the last rows are counted in
             if (lane == 0) {
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                __threadfence_system();
+                int first = my_rows > EP_SEND_BUFFERS ? my_rows - EP_SEND_BUFFERS : 0;
+                for (int it = first; it < my_rows; ++it) {          // oldest first: keeps equal counters adjacent
 #pragma unroll
-                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (pending[i] != nullptr) red_release_sys_add(pending[i], 1);
+                    for (int k = 0; k < EP_SEND_BUFFERS; ++k) if (k == it % EP_SEND_BUFFERS) { count_in(pend[k]); pend[k] = nullptr; }
+                }
+                if (sig_cnt > 0) {
+                    __threadfence_system();
+                    red_release_sys_add(sig_ptr, sig_cnt);
+                }
             }
         }
     } else {
@@ -726,7 +787,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     ok = mbar_wait_warp(filled_bar, stg_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
                     if (!ok) break;
                     if (row_valid) {
-                        const int meta = __ldg(p.scatter_meta + row);
+                        const int meta = __ldg(p.scatter_meta + (long long)row * p.scatter_meta_stride);
                         __nv_bfloat16* drow = p.scatter_base[(meta >> 24) & 7] + (long long)(meta & 0xFFFFFF) * p.ldd + tile.n_blk * BN;
                         asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 512;"
                                      ::"l"(drow), "r"(smem_u32(stg_row)) : "memory");
@@ -737,7 +798,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             } else if (row_valid) {
                 __nv_bfloat16* drow;
                 if (p.scatter_meta != nullptr) {
-                    const int meta = __ldg(p.scatter_meta + row);
+                    const int meta = __ldg(p.scatter_meta + (long long)row * p.scatter_meta_stride);
                     drow = p.scatter_base[(meta >> 24) & 7] + (long long)(meta & 0xFFFFFF) * p.ldd + n0;
                 } else {
                     drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;

@@ -11,10 +11,15 @@
 //                      in the 32x16-byte tile order tcgen05.cp expects; stores the call's generation number
 //                      into a flag if any scale is not a power of two (then this path stands down and the
 //                      promotion kernel runs instead)
-//   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256 x 256 tiles, 6-stage TMA ring; the scale words of
+//   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256 x 256 tiles, 5-stage TMA ring; the scale words of
 //                      four K blocks travel with the first of their stages; the leader issues
 //                      tcgen05.cp (smem -> TMEM) and 16 block-scaled MMAs per group of four K blocks;
-//                      one accumulator drain per tile by the 8 epilogue warps of each CTA
+//                      one accumulator drain per tile by the 8 epilogue warps of each CTA.  bf16 rows
+//                      leave through a shared-memory staging area as bulk stores of up to 128 bytes per
+//                      row: with 16-byte stores per lane (32 rows per instruction) the store phase of a
+//                      tile took longer than a K=2048 tile's MMAs and the epilogue, not the tensor
+//                      pipe, set the pace.  Narrower tiles with two accumulators (240 or 224 columns,
+//                      MOE_OPT_MX_TILE) are kept for measurement: with the old epilogue they were slower.
 #pragma once
 
 #include "pair_common.cuh"
@@ -22,30 +27,42 @@
 namespace b200 {
 
 namespace mx {
-constexpr int BM = 128, BN = 256, BK = 128;
-constexpr int STAGES = 6;
+constexpr int BM = 128, BK = 128;
+constexpr int BN = 256;                               // column tile of the pair kernel: one accumulator
+constexpr int BN_WIDE = 256;
+constexpr int STAGES = 5;
 constexpr int THREADS = 384;
 constexpr int A_STAGE_BYTES = BM * BK;
-constexpr int B_STAGE_BYTES = (BN / 2) * BK;
+constexpr int B_STAGE_BYTES = (BN_WIDE / 2) * BK;     // sized for the wider tile; the 240-column tile uses 120 rows of it
 constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int SFQ_SLOTS = 4;                          // ring of scale tiles, one per group of 4 K blocks
-constexpr int SFQ_SLOT_BYTES = 512 + 2 * 512;         // SFA (this CTA's 128 rows) + SFB (256 columns)
+constexpr int SFQ_SLOT_BYTES = 512 + 2 * 512;         // SFA (this CTA's 128 rows) + SFB (the tile's columns, 2 x 128 entries)
 constexpr int OFF_SFQ = SMEM_TILE_BYTES;
-constexpr int OFF_BARS = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
+// output staging: per epilogue warp 32 rows of 64 bf16 columns, row pitch 144 bytes (an odd number of 16-byte
+// units: the 8 lanes of a 128-bit store phase hit 8 different bank groups)
+constexpr int STG_COLS = 64;
+constexpr int STG_PITCH = STG_COLS * 2 + 16;
+constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
+constexpr int OFF_STG = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
+constexpr int OFF_BARS = OFF_STG + 8 * STG_WARP_BYTES;
 constexpr int OFF_PREFIX = OFF_BARS + 256;
 constexpr int SMEM_BYTES = OFF_PREFIX + (gg::MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_SF_BASE = 256;                     // accumulator: columns [0, 256)
-constexpr int TMEM_SF_STRIDE = 12;                    // per buffer: 4 columns SFA + 8 columns SFB
+constexpr int TMEM_SF_STRIDE = 12;                    // per scale buffer: 4 columns SFA + 8 columns SFB
 }  // namespace mx
 
+// Packed scale tiles in the workspace (units of 128 words = one tcgen05.cp tile of 512 bytes):
+//   SFA  [row block of 128][quad]                      word r = the four K-block bytes of row 128*block + r
+//   SFB  [group][column tile][quad][2]                 word i of half h = those of column (tile's first) + 128*h + i
+// so a kernel finds the scales of its column tile at entry 0 whatever the tile's first column and width are.
 struct MxWorkspace {
     int* flag;                 // == gen after mx_prep_kernel: some scale of THIS call is not a power of two
     int gen;                   // the call's generation number (host counter): no memset between calls, a value left
                                // by an earlier call can never equal it
     uint32_t* sfa_packed;      // [row_blocks128][quads][128]
-    uint32_t* sfb_packed;      // [G][nb128][quads][128]
+    uint32_t* sfb_packed;      // [G][n_tiles][quads][2][128]
     int row_blocks, quads;
+    int n_tiles, nt_base, nt_rem;   // column tiles of the consuming kernel (mx_tile_col0 / mx_tile_width)
 };
 
 // position of row r (0..127) inside a 128-row scale tile: 32 rows of 16 bytes, word r/32 of row r%32
@@ -90,16 +107,21 @@ __global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, 
         }
         ws.sfa_packed[((long long)blockIdx.x * ws.quads + q) * 128 + sf_tile_index(threadIdx.x)] = word;
     } else {
-        const int idx = blockIdx.x - ws.row_blocks;       // (g, nb) pair
-        if (idx < G * nb128) {
-            uint32_t word = 0;
+        const int idx = blockIdx.x - ws.row_blocks;       // (group, column tile, half)
+        if (idx < G * ws.n_tiles * 2) {
+            const int h = idx & 1, gt = idx >> 1, g = gt / ws.n_tiles, nt = gt - g * ws.n_tiles;
+            const int col = mx_tile_col0(ws.nt_base, ws.nt_rem, nt) + 128 * h + threadIdx.x;
+            uint32_t word = 0x7F7F7F7Fu;
+            if (col < nb128 * 128) {
+                word = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int kb = 4 * q + i;
-                const uint32_t b = kb < KB ? ue8m0_of(__ldg(sfb + (long long)idx * KB + kb), &bad) : 0x7Fu;
-                word |= b << (8 * i);
+                for (int i = 0; i < 4; ++i) {
+                    const int kb = 4 * q + i;
+                    const uint32_t b = kb < KB ? ue8m0_of(__ldg(sfb + ((long long)g * nb128 + (col >> 7)) * KB + kb), &bad) : 0x7Fu;
+                    word |= b << (8 * i);
+                }
             }
-            ws.sfb_packed[((long long)idx * ws.quads + q) * 128 + threadIdx.x] = word;
+            ws.sfb_packed[(((long long)gt * ws.quads + q) * 2 + h) * 128 + sf_tile_index(threadIdx.x)] = word;
         }
     }
     if (__syncthreads_or(bad) && threadIdx.x == 0) *reinterpret_cast<volatile int*>(ws.flag) = ws.gen;
@@ -110,18 +132,19 @@ __global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, 
 // at sfb[g*b_sg + n*b_sn + q*b_sq] -- B scales are per column here.  Nothing to check: every byte is 2^e.
 __global__ void mx_prep_packed_kernel(const uint32_t* __restrict__ sfa, long long a_sr, long long a_sq,
                                       const uint32_t* __restrict__ sfb, long long b_sg, long long b_sn, long long b_sq,
-                                      int rows_total, int N, int G, int nb128, MxWorkspace ws) {
+                                      int rows_total, int N, int G, MxWorkspace ws) {
     const int q = blockIdx.y;
     if ((int)blockIdx.x < ws.row_blocks) {
         const int r = blockIdx.x * 128 + threadIdx.x;
         const uint32_t word = r < rows_total ? __ldg(sfa + (long long)r * a_sr + (long long)q * a_sq) : 0x7F7F7F7Fu;
         ws.sfa_packed[((long long)blockIdx.x * ws.quads + q) * 128 + sf_tile_index(threadIdx.x)] = word;
     } else {
-        const int idx = blockIdx.x - ws.row_blocks;       // (g, nb)
-        if (idx < G * nb128) {
-            const int g = idx / nb128, n = (idx % nb128) * 128 + threadIdx.x;
+        const int idx = blockIdx.x - ws.row_blocks;       // (group, column tile, half)
+        if (idx < G * ws.n_tiles * 2) {
+            const int h = idx & 1, gt = idx >> 1, g = gt / ws.n_tiles, nt = gt - g * ws.n_tiles;
+            const int n = mx_tile_col0(ws.nt_base, ws.nt_rem, nt) + 128 * h + threadIdx.x;
             const uint32_t word = n < N ? __ldg(sfb + (long long)g * b_sg + (long long)n * b_sn + (long long)q * b_sq) : 0x7F7F7F7Fu;
-            ws.sfb_packed[((long long)idx * ws.quads + q) * 128 + sf_tile_index(threadIdx.x)] = word;
+            ws.sfb_packed[(((long long)gt * ws.quads + q) * 2 + h) * 128 + sf_tile_index(threadIdx.x)] = word;
         }
     }
 }
@@ -212,7 +235,7 @@ struct MxSched<false, true> {
     static __device__ __forceinline__ int quad_offset(const KgTable& k, int g) { return k.qoff[g]; }
 };
 
-template <bool MASKED, bool KG = false, bool MNMAJOR = false>
+template <bool MASKED, bool KG = false, bool MNMAJOR = false, int TILE_N = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(mx::THREADS, 1)
 gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -224,6 +247,12 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // MNMAJOR: the operands stay as the caller has them, a [K_total, M] and b [K_total, N] (M / N contiguous); a stage
     // holds 128 K rows x 128 bytes of M (or N), the MMAs read it as an MN-major operand (instruction descriptor bits
     // 15 and 16) and step 32 K rows = 4096 bytes per instruction.
+    // Column tile and accumulators: two 240-column accumulators, or (k-grouped modes) one of 256 columns.
+    constexpr int TN = TILE_N ? TILE_N : BN;
+    constexpr int ACCS = 2 * TN + 2 * TMEM_SF_STRIDE <= TMEM_COLS ? 2 : 1;
+    constexpr int HALF = TN / 2;                      // columns drained by one epilogue warpgroup
+    constexpr int SF_BASE = ACCS * TN;                // scale columns behind the accumulators
+    static_assert(SF_BASE + 2 * TMEM_SF_STRIDE <= TMEM_COLS, "accumulators and scale buffers must fit TMEM");
     using Sched = MxSched<MASKED, KG>;
     if (*flag == p.mode_gen) return;      // some scale is not a power of two: the promotion kernel handles this call
     extern __shared__ uint8_t smem_raw[];
@@ -232,19 +261,19 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
     uint8_t* smem_sfq = smem + OFF_SFQ;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
-    // [0,S) full (leader's used), [S,2S) empty, [2S] tmem_full, [2S+1] tmem_empty (leader's used)
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+    // [0,S) full (leader's used), [S,2S) empty, [2S, 2S+2) tmem_full, [2S+2, 2S+4) tmem_empty (leader's used)
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);       // a value the compiler knows to be warp-uniform
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
 
     const uint32_t full_bar = smem_u32(bars);
     const uint32_t empty_bar = smem_u32(bars + STAGES);
     const uint32_t tfull_bar = smem_u32(bars + 2 * STAGES);
-    const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + 1);
+    const uint32_t tempty_bar = smem_u32(bars + 2 * STAGES + 2);
     const uint32_t leader_full_bar = map_to_cta(full_bar, 0);
     const uint32_t leader_tempty_bar = map_to_cta(tempty_bar, 0);
 
@@ -253,8 +282,10 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
-        mbar_init(tfull_bar, 1);
-        mbar_init(tempty_bar, 16);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar + 8 * a, 1);
+            mbar_init(tempty_bar + 8 * a, 16);        // the 16 epilogue warps of the pair
+        }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
@@ -295,36 +326,48 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
     const int KB = p.num_k_blocks;
+    // columns the pair multiplies for column tile n_blk: the full tile, or what is left of N rounded up to 16 (the
+    // MMA's N granularity; columns past N are computed from whatever rows follow in B and never stored)
+    auto tile_col0 = [&](int n_blk) { return mx_tile_col0(p.nt_base, p.nt_rem, n_blk); };
+    auto tile_cols = [&](int n_blk) {
+        if (KG) return TN;                  // MN-major operand stages are 128-byte swizzle rows of N: fixed halves of 128 columns
+        const int w = mx_tile_width(p.nt_base, p.nt_rem, n_blk), left = ((p.N - tile_col0(n_blk)) + 15) & ~15;
+        return left < w ? left : w;
+    };
 
     if (warp < 4) {
         setmaxnreg_dec<72>();
         if (warp == 0) {
             // ------------------------------------------------ TMA producer (both CTAs)
+            // The whole warp runs the loop and one elected lane issues: coordinates, barrier addresses and
+            // descriptors then stay warp-uniform values, which is what the TMA and tcgen05 instructions take.
             Sched sched(p, prefix, lane, rank, kg);
             Tile tile;
             uint32_t stage = 0, phase = 0, qcount = 0;
             long long tr_wait = 0;
-            const long long tr_t0 = clock64();
+            const long long tr_t0 = B200_TRACE(p.trace) ? clock64() : 0;
             bool ok = true;
             while (ok && sched.next(tile)) {
-                // k-grouped: every group multiplies the same rows of A and B over its own K window
-                const int b_row = (KG ? 0 : tile.g * p.N) + tile.n_blk * BN + (int)rank * (BN / 2);
+                // this CTA stages its half of the tile's columns; k-grouped: every group multiplies the same rows of
+                // A and B over its own K window
+                const int b_row = (KG ? 0 : tile.g * p.N) + tile_col0(tile.n_blk) + (int)rank * (tile_cols(tile.n_blk) >> 1);
                 const int k0 = Sched::k_offset(kg, tile.g);
                 const int KBt = Sched::k_blocks(kg, tile.g, KB);
                 const int q0 = Sched::quad_offset(kg, tile.g);
                 const int sfa_chunk = (tile.m0 >> 7) * quads + q0;                  // this CTA's 128 rows
-                const int sfb_chunk = ((KG ? 0 : tile.g * p.nb128) + tile.n_blk * 2) * quads + q0;  // first of the two column blocks
-                const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
+                const int n_tiles = p.num_n_blocks;
+                const int sfb_chunk = (((KG ? 0 : tile.g * n_tiles) + tile.n_blk) * quads + q0) * 2;  // two 128-entry halves per quad
                 for (int kb = 0; kb < KBt; ++kb) {
                     const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
                                         STATUS_TIMEOUT_SMEM_EMPTY);
                     if (B200_TRACE(p.trace)) tr_wait += clock64() - c0;
                     if (!ok) break;
-                    if (lane == 0) {
+                    const bool with_sf = (kb & 3) == 0;
+                    if (elect_one_sync()) {
                         const uint32_t fb = leader_full_bar + 8 * stage;
-                        const bool with_sf = (kb & 3) == 0;
-                        if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * (A_STAGE_BYTES + B_STAGE_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0)));
+                        constexpr int B_BYTES = (TN / 2) * BK;                          // bytes one TMA box of B delivers
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * (A_STAGE_BYTES + B_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0)));
                         if (MNMAJOR) {
                             tma_load_2d_pair(smem_u32(smem_a + stage * A_STAGE_BYTES), &tmap_a, fb, tile.m0, k0 + kb * BK);
                             tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, b_row, k0 + kb * BK);
@@ -336,87 +379,86 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             const int q = kb >> 2;
                             const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
                             tma_load_1d_pair(dst, &tmap_sfa, fb, (sfa_chunk + q) * 128);
-                            tma_load_1d_pair(dst + 512, &tmap_sfb, fb, (sfb_chunk + q) * 128);
-                            // a last, half-wide column block has no second scale block: reuse the first
-                            tma_load_1d_pair(dst + 1024, &tmap_sfb, fb, (sfb_chunk + (second_nb ? quads : 0) + q) * 128);
+                            tma_load_1d_pair(dst + 512, &tmap_sfb, fb, (sfb_chunk + 2 * q) * 128);
+                            tma_load_1d_pair(dst + 1024, &tmap_sfb, fb, (sfb_chunk + 2 * q + 1) * 128);
                         }
                     }
-                    __syncwarp();
-                    if ((kb & 3) == 0) ++qcount;
+                    if (with_sf) ++qcount;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
             if (B200_TRACE(p.trace) && lane == 0) {
-                p.trace[blockIdx.x * 8 + 0] = tr_wait;
-                p.trace[blockIdx.x * 8 + 1] = clock64() - tr_t0;
+                p.trace[blockIdx.x * 16 + 0] = tr_wait;
+                p.trace[blockIdx.x * 16 + 1] = clock64() - tr_t0;
             }
         } else if (warp == 1 && rank == 0) {
             // ------------------------------------------------ MMA issuer (leader)
-            // The tile sequence is computed by the whole warp; a tile's K loop is run by lane 0 alone with
-            // single-thread waits and incrementally updated descriptors.  The tensor pipe only queues a
-            // couple of MMAs, so every instruction this thread spends between two K blocks is a bubble.
+            // Warp-uniform loop, one elected lane issues.  The tensor pipe only queues a couple of MMAs, so what
+            // this warp spends between two K blocks is a bubble: with the loop state in uniform registers a K block
+            // costs the issuer well under the 512 cycles the pipe needs for it; a single diverged lane (every
+            // operand moved from a vector register) needed more than that.
             Sched sched(p, prefix, lane, rank, kg);
             Tile tile;
-            uint32_t stage = 0, phase = 0, tile_phase = 0, qcount = 0;
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, qcount = 0;
             bool ok = true;
             const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem_a));
             const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
-            const uint32_t idesc0 = make_idesc_mxf8(2 * BM, BN, 0) | (MNMAJOR ? (1u << 15) | (1u << 16) : 0u);
             constexpr uint64_t KSTEP = MNMAJOR ? (32 * 128) >> 4 : 2;      // descriptor units (16 bytes) per K = 32
             long long tr_te = 0, tr_full = 0, tr_issue = 0;
+            const long long tr_m0 = B200_TRACE(p.trace) ? clock64() : 0;
             while (ok && sched.next(tile)) {
-                if (lane == 0) {
-                    // the single accumulator must have been drained by both CTAs' epilogues
-                    const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
-                    ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
-                    if (B200_TRACE(p.trace)) tr_te += clock64() - c0;
-                    const int KBt = Sched::k_blocks(kg, tile.g, KB);
-                    for (int kb = 0; ok && kb < KBt; ++kb) {
-                        const long long c1 = B200_TRACE(p.trace) ? clock64() : 0;
-                        ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                        const long long c2 = B200_TRACE(p.trace) ? clock64() : 0;
-                        tr_full += c2 - c1;
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t sub = kb & 3;
+                // this tile's accumulator must have been drained by both CTAs' epilogues
+                const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
+                ok = mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                if (B200_TRACE(p.trace)) tr_te += clock64() - c0;
+                if (!ok) break;
+                tc_fence_after();
+                const int KBt = Sched::k_blocks(kg, tile.g, KB);
+                const uint32_t idesc0 = make_idesc_mxf8(2 * BM, tile_cols(tile.n_blk), 0) | (MNMAJOR ? (1u << 15) | (1u << 16) : 0u);
+                const uint32_t tmem_d = tmem_base + acc * TN;
+                for (int kb = 0; kb < KBt; ++kb) {
+                    const long long c1 = B200_TRACE(p.trace) ? clock64() : 0;
+                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                    const long long c2 = B200_TRACE(p.trace) ? clock64() : 0;
+                    tr_full += c2 - c1;
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sub = kb & 3;
+                    if (elect_one_sync()) {
                         if (sub == 0) {
                             const uint32_t src = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
-                            const uint32_t tsf = tmem_base + TMEM_SF_BASE + (qcount & 1) * TMEM_SF_STRIDE;
+                            const uint32_t tsf = tmem_base + SF_BASE + (qcount & 1) * TMEM_SF_STRIDE;
                             tmem_cp_sf_pair(tsf, make_sf_desc(src));
                             tmem_cp_sf_pair(tsf + 4, make_sf_desc(src + 512));
                             tmem_cp_sf_pair(tsf + 8, make_sf_desc(src + 1024));
-                            ++qcount;
                         }
-                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + ((qcount - 1) & 1) * TMEM_SF_STRIDE;
+                        const uint32_t tsfa = tmem_base + SF_BASE + ((qcount - (sub == 0 ? 0u : 1u)) & 1) * TMEM_SF_STRIDE;
                         const uint32_t tsfb = tsfa + 4;
                         const uint32_t idesc = idesc0 | (sub << 4) | (sub << 29);
                         const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
                         const uint64_t bdesc = bdesc0 + stage * (B_STAGE_BYTES >> 4);
-                        umma_mxf8_pair(tmem_base, adesc, bdesc, idesc, tsfa, tsfb, kb > 0 ? 1u : 0u);
-                        umma_mxf8_pair(tmem_base, adesc + KSTEP, bdesc + KSTEP, idesc, tsfa, tsfb, 1u);
-                        umma_mxf8_pair(tmem_base, adesc + 2 * KSTEP, bdesc + 2 * KSTEP, idesc, tsfa, tsfb, 1u);
-                        umma_mxf8_pair(tmem_base, adesc + 3 * KSTEP, bdesc + 3 * KSTEP, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_d, adesc, bdesc, idesc, tsfa, tsfb, kb > 0 ? 1u : 0u);
+                        umma_mxf8_pair(tmem_d, adesc + KSTEP, bdesc + KSTEP, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_d, adesc + 2 * KSTEP, bdesc + 2 * KSTEP, idesc, tsfa, tsfb, 1u);
+                        umma_mxf8_pair(tmem_d, adesc + 3 * KSTEP, bdesc + 3 * KSTEP, idesc, tsfa, tsfb, 1u);
                         umma_commit_pair(empty_bar + 8 * stage, 3);
-                        if (kb == KBt - 1) umma_commit_pair(tfull_bar, 3);
-                        if (B200_TRACE(p.trace)) tr_issue += clock64() - c2;
-                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        if (kb == KBt - 1) umma_commit_pair(tfull_bar + 8 * acc, 3);
                     }
-                    tile_phase ^= 1;
+                    if (sub == 0) ++qcount;
+                    if (B200_TRACE(p.trace)) tr_issue += clock64() - c2;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                stage = __shfl_sync(0xffffffffu, stage, 0);
-                phase = __shfl_sync(0xffffffffu, phase, 0);
-                tile_phase = __shfl_sync(0xffffffffu, tile_phase, 0);
-                qcount = __shfl_sync(0xffffffffu, qcount, 0);
+                if (++acc == ACCS) { acc = 0; acc_phase ^= 1; }
             }
             if (B200_TRACE(p.trace) && lane == 0) {
-                p.trace[blockIdx.x * 8 + 2] = tr_te;
-                p.trace[blockIdx.x * 8 + 3] = tr_full;
-                p.trace[blockIdx.x * 8 + 4] = tr_issue;
+                p.trace[blockIdx.x * 16 + 2] = tr_te;
+                p.trace[blockIdx.x * 16 + 3] = tr_full;
+                p.trace[blockIdx.x * 16 + 4] = tr_issue;
+                p.trace[blockIdx.x * 16 + 5] = clock64() - tr_m0;
             }
         }
     } else {
-        // ---------------------------------------------------- epilogue (both CTAs): one drain per tile
+        // ---------------------------------------------------- epilogue (both CTAs): drains tile i while tile i+1 is multiplied
         setmaxnreg_inc<208>();
         const int ew = warp - 4;
         const int quarter = warp & 3;
@@ -424,57 +466,81 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int row_in_tile = quarter * 32 + lane;
         Sched sched(p, prefix, lane, rank, kg);
         Tile tile;
-        uint32_t tile_phase = 0;
+        uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         while (ok && sched.next(tile)) {
-            const int n0 = tile.n_blk * BN + half * 128;
+            // this warpgroup's columns: the first or the second half of the tile (112, 120 or 128 columns)
+            const int half_w = tile_cols(tile.n_blk) >> 1;
+            const int n0 = tile_col0(tile.n_blk) + half * half_w;
+            const int n_end = n0 + half_w < p.N ? n0 + half_w : p.N;
             int row = tile.m0 + row_in_tile;
             bool row_valid;
             if (MASKED) row_valid = row_in_tile < tile.rows;
             else if (KG) row_valid = row < p.M;
             else row_valid = (row < p.M) && (__ldg(p.layout + row) == tile.g);
             if (KG) row += tile.g * p.M;          // d is [G, M, N]
-            ok = mbar_wait_warp(tfull_bar, tile_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
             if (!ok) break;
-            tile_phase ^= 1;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + half * 128;
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TN + half * half_w;
+            // HALF columns = 3 x 32 + (32 | 16 + 8 | 16)
             uint32_t v[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
+            for (int c = 0; c < 3; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
+            if (HALF == 128) {
+                tmem_ld_32x32b_x32(taddr + 96, v[3]);
+            } else {
+                tmem_ld_32x32b_x16(taddr + 96, *reinterpret_cast<uint32_t(*)[16]>(&v[3][0]));
+                if (HALF > 112) tmem_ld_32x32b_x8(taddr + 112, *reinterpret_cast<uint32_t(*)[8]>(&v[3][16]));
+            }
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_wait(v[c]);
-            // the accumulator is in registers: the next tile's MMAs may overwrite it
+            // the accumulator is in registers: the MMAs of the tile after next may overwrite it
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_tempty_bar);
+            if (lane == 0) mbar_arrive_cluster(leader_tempty_bar + 8 * acc);
+            if (++acc == ACCS) { acc = 0; acc_phase ^= 1; }
             if (row_valid && p.d_f32) {
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
-                for (int j = 0; j < 128; j += 4) {
-                    if (n0 + j + 4 <= p.N) {
+                for (int j = 0; j < HALF; j += 4) {
+                    if (n0 + j + 4 <= n_end) {
                         float4 o = make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
                                                __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
                         if (p.d_accumulate) red_add_f32x4(drow + j, o);      // one contributor per element: same as load+add+store
                         else *reinterpret_cast<float4*>(drow + j) = o;
                     }
                 }
-            } else if (row_valid) {
+            } else {
+                // bf16: every thread converts its row in chunks of 64 columns into its own 144-byte slot of the warp's
+                // staging area and sends each chunk with one bulk store (a lane only ever touches its own slot, so
+                // the only ordering needed is "my previous store has read the slot")
+                uint8_t* slot = smem + OFF_STG + ew * STG_WARP_BYTES + lane * STG_PITCH;
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
-                for (int j = 0; j < 128; j += 8) {
-                    if (n0 + j + 8 <= p.N) {
+                for (int c0 = 0; c0 < HALF; c0 += STG_COLS) {
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll
+                    for (int j = c0; j < c0 + STG_COLS && j < HALF; j += 8) {
                         uint4 out;
                         const uint32_t* s = &v[j / 32][j % 32];
                         out.x = cvt_bf16x2(pack_f32x2(__uint_as_float(s[0]), __uint_as_float(s[1])));
                         out.y = cvt_bf16x2(pack_f32x2(__uint_as_float(s[2]), __uint_as_float(s[3])));
                         out.z = cvt_bf16x2(pack_f32x2(__uint_as_float(s[4]), __uint_as_float(s[5])));
                         out.w = cvt_bf16x2(pack_f32x2(__uint_as_float(s[6]), __uint_as_float(s[7])));
-                        *reinterpret_cast<uint4*>(drow + j) = out;
+                        *reinterpret_cast<uint4*>(slot + (j - c0) * 2) = out;
                     }
+                    fence_proxy_async_smem();
+                    int cols = n_end - (n0 + c0);                 // columns of this chunk that exist (multiple of 8)
+                    cols = cols > STG_COLS ? STG_COLS : cols;
+                    if (row_valid && cols > 0)
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                     ::"l"(drow + c0), "r"(smem_u32(slot)), "r"(cols * 2) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
         }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");       // this thread's stores are complete
     }
 
     tc_fence_before();
@@ -503,6 +569,8 @@ constexpr int OFF_BARS = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
 constexpr int OFF_PREFIX = OFF_BARS + 256;
 constexpr int SMEM_BYTES = OFF_PREFIX + gg::MASKED_TABLE_INTS * 4 + 12 + 1024;
 }  // namespace mx1
+// (the single-CTA kernel keeps 256-column tiles and one accumulator: its use is the masked decode layout, which is
+// bound by streaming the weights from HBM, not by the tensor pipe)
 
 __device__ __forceinline__ void tma_load_1d(uint32_t smem_dst, const void* tmap, uint32_t bar, int32_t c0) {
     asm volatile(
@@ -562,6 +630,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tma_prefetch_desc(&tmap_sfb);
     }
     if (MASKED) build_masked_tables(p, prefix, 3);
+    constexpr int TMEM_SF_BASE = BN;          // one 256-column accumulator, scale columns behind it
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_base_slot), mx::TMEM_COLS);
         tmem_relinquish();
@@ -583,8 +652,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             while (ok && sched.next(tile)) {
                 const int b_row = tile.g * p.N + tile.n_blk * BN;
                 const int sfa_chunk = (tile.m0 >> 7) * quads;
-                const int sfb_chunk = (tile.g * p.nb128 + tile.n_blk * 2) * quads;
-                const bool second_nb = tile.n_blk * 2 + 1 < p.nb128;
+                const int sfb_chunk = ((tile.g * p.num_n_blocks + tile.n_blk) * quads) * 2;      // two 128-entry halves per quad
                 for (int kb = 0; kb < KB; ++kb) {
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status, STATUS_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
@@ -598,8 +666,8 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             const int q = kb >> 2;
                             const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
                             tma_load_1d(dst, &tmap_sfa, fb, (sfa_chunk + q) * 128);
-                            tma_load_1d(dst + 512, &tmap_sfb, fb, (sfb_chunk + q) * 128);
-                            tma_load_1d(dst + 1024, &tmap_sfb, fb, (sfb_chunk + (second_nb ? quads : 0) + q) * 128);
+                            tma_load_1d(dst + 512, &tmap_sfb, fb, (sfb_chunk + 2 * q) * 128);
+                            tma_load_1d(dst + 1024, &tmap_sfb, fb, (sfb_chunk + 2 * q + 1) * 128);
                         }
                     }
                     __syncwarp();
@@ -626,13 +694,13 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         const uint32_t sub = kb & 3;
                         if (sub == 0) {
                             const uint32_t src = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
-                            const uint32_t tsf = tmem_base + mx::TMEM_SF_BASE + (qcount & 1) * mx::TMEM_SF_STRIDE;
+                            const uint32_t tsf = tmem_base + TMEM_SF_BASE + (qcount & 1) * mx::TMEM_SF_STRIDE;
                             tmem_cp_sf(tsf, make_sf_desc(src));
                             tmem_cp_sf(tsf + 4, make_sf_desc(src + 512));
                             tmem_cp_sf(tsf + 8, make_sf_desc(src + 1024));
                             ++qcount;
                         }
-                        const uint32_t tsfa = tmem_base + mx::TMEM_SF_BASE + ((qcount - 1) & 1) * mx::TMEM_SF_STRIDE;
+                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + ((qcount - 1) & 1) * mx::TMEM_SF_STRIDE;
                         const uint32_t tsfb = tsfa + 4;
                         const uint32_t idesc = idesc0 | (sub << 4) | (sub << 29);
                         const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);

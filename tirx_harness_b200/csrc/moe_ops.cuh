@@ -435,7 +435,8 @@ struct EpPeers {
     const __nv_bfloat16* y[EP_MAX_WORLD];// bf16 [cap_rows, H] expert outputs of each rank
     int* counts[EP_MAX_WORLD];           // int32 [world, E_total]: row s = pairs rank s routes to each expert
     int* flags[EP_MAX_WORLD];            // int32 [world]: barrier epochs written by each peer
-    int* meta[EP_MAX_WORLD];             // int32 [cap_rows]: (source rank << 24) | source pair index of each row
+    int* meta[EP_MAX_WORLD];             // int32 [cap_rows]: (source rank << 24) | source pair index of each row (written
+                                         // by ep_dispatch_kernel; the dispatching GEMM keeps it inside the record instead)
 };
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
@@ -455,14 +456,13 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
 // the rows that have landed for local expert j in the current forward.
 constexpr int EP_ARRIVE_OFFSET = 64;
 constexpr int EP_SEND_BUFFERS = 3;                 // token records in flight per sending warp
-constexpr int EP_SEND_RECORD_MAX = 7424;           // bytes: H + H/32 for H <= 7168, rounded up to 128
+constexpr int EP_SEND_RECORD_MAX = 7424;           // bytes: H + H/32 + 4 for H <= 7168, rounded up to 128
 
 // What the gate_up GEMM needs to carry the dispatch all-to-all itself (one sending warp per CTA): this rank's
 // tokens and routes, where every pair goes (pos, from the exchange plan), the order to send them in (local
 // expert index first, so that every rank's first expert is complete first), and both sides' arrival counters.
 struct EpSend {
-    uint8_t* a[EP_MAX_WORLD];            // receive buffers of all ranks (records of `pitch` bytes)
-    int* meta[EP_MAX_WORLD];             // return address of every received row
+    uint8_t* a[EP_MAX_WORLD];            // receive buffers of all ranks (records of `pitch` bytes: row, scales, return address)
     int* arrive[EP_MAX_WORLD];           // arrival counters of all ranks, [E_local] each
     const uint8_t* x;                    // this rank's tokens, e4m3 [T, H]
     const float* xs;                     // their scales at [t * xs_r + b * xs_b]

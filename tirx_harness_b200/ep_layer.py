@@ -115,7 +115,8 @@ class EpMoeLayer:
         # ---- symmetric region: a | sa | y (pull: [cap,H] expert outputs; push: [T_local*top_k,H] return slots)
         #      | counts | flags | meta
         y_rows = cap if combine == "pull" else n_pairs
-        pitch = (H + (H // 128) * 4 + 15) // 16 * 16     # one record per row: e4m3 bytes, then its fp32 scales
+        # one record per row: e4m3 bytes, its fp32 scales, and (fused dispatch) the row's return address
+        pitch = (H + (H // 128) * 4 + 4 + 15) // 16 * 16
         self.pitch = pitch
         # flags: [0, world) barrier epochs, [64, 64 + E_local) arrival counters of the fused dispatch
         sizes = [cap * pitch, 0, y_rows * H * 2, self.world * E_total * 4, (64 + E_local) * 4, cap * 4]
@@ -154,7 +155,10 @@ class EpMoeLayer:
         self.a1_t = rec[:, :H].view(torch.float8_e4m3fn)                    # [cap, H], row pitch = record size
         self.s1_t = rec.view(torch.float32)[:, H // 4:H // 4 + H // 128]     # [cap, H/128], row stride = pitch/4
         self.y_t = self._wrap(self._local["y"], (y_rows, H), torch.bfloat16)
-        self.meta_t = self._wrap(self.symm.local + offs[5], (cap,), torch.int32)
+        if dispatch == "fused":      # return addresses travel inside the records: word (H + H/32) / 4 of every row
+            self.meta_t = rec.view(torch.int32)[:, (H + H // 32) // 4]
+        else:
+            self.meta_t = self._wrap(self.symm.local + offs[5], (cap,), torch.int32)
         rows_used = self.offsets[E_local:E_local + 1]
         if fuse_act:
             self.gemm1 = grouped_gemm.bind_gate_up_act(self.a1_t, self.s1_t, w13, s13, self.a2, self.s2.t(), self.layout,

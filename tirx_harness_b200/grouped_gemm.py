@@ -66,6 +66,7 @@ class _BoundGG:
             meta, bases = scatter
             self._keep = self._keep + (meta,)
             self._args.scatter_meta = _ptr(meta)
+            self._args.scatter_meta_stride = meta.stride(0)
             for i, b_ in enumerate(bases):
                 self._args.scatter_base[i] = b_
         self._argp = ctypes.byref(self._args)
