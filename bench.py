@@ -145,9 +145,35 @@ class Timer:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def back_to_back(self, fn, steps: int) -> float:
+    SPIN_UP_MS = 30.0
+
+    def spin_up(self, fn) -> None:
+        """Untimed calls worth about SPIN_UP_MS of device time before a timed region: after host-side work (data
+        generation, the oracle, a JIT build) the SM clock needs milliseconds under load to come back up, and a region
+        timed during that ramp is slow by tens of percent.  The call count is the same on every rank."""
+        torch = self.torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        fn()
+        e1.record()
+        e1.synchronize()
+        per_call = max(e0.elapsed_time(e1) / 2.0, 1e-3)
+        n = int(min(500, max(0, math.ceil(self.SPIN_UP_MS / per_call) - 2)))
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([n], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            n = int(t.item())
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+
+    def back_to_back(self, fn, steps: int, spin_up: bool = True) -> float:
         """ms per step of `steps` calls issued back to back, barrier + synchronize on both sides."""
         torch = self.torch
+        if spin_up:
+            self.spin_up(fn)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         self.barrier()
         e0.record()
@@ -165,6 +191,7 @@ class Timer:
             self._flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.device)
         for _ in range(warmup):
             fn()
+        self.spin_up(fn)
         ts = []
         for _ in range(iters):
             self._flush.zero_()

@@ -110,8 +110,10 @@ def _all_gather(t: torch.Tensor, world: int):
     if world == 1:
         return t.unsqueeze(0)
     import torch.distributed as dist
-    out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(out, t.contiguous())
+    # bytes on the wire: NCCL has no 16-bit integer type
+    src = t.contiguous()
+    out = torch.empty((world,) + tuple(src.shape), dtype=src.dtype, device=src.device)
+    dist.all_gather_into_tensor(out.view(torch.uint8).reshape(world, -1), src.view(torch.uint8).reshape(-1))
     return out
 
 

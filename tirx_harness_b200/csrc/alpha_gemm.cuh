@@ -245,7 +245,7 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     float* amax_s = reinterpret_cast<float*>(smem + C::OFF_AMAX);       // [2 parity][4 warps][NT]
     int* tables = reinterpret_cast<int*>(smem + C::OFF_TABLES);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);       // a value the compiler knows to be warp-uniform
     const int lane = threadIdx.x & 31;
     const uint32_t full_bar = smem_u32(bars);
     const uint32_t empty_bar = smem_u32(bars + STAGES);
@@ -294,16 +294,16 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         AlphaUnit u;
         uint32_t stage = 0, phase = 0, issued = 0, issued_parity = 0;
         long long tr_wait = 0;
-        const long long tr_t0 = clock64();
+        const long long tr_t0 = B200_TRACE(p.trace) ? clock64() : 0;
         bool ok = true;
         while (ok && sched.next(u)) {
             const int w_row = PHASE == 1 ? u.e * 256 : u.e * p.H + u.f * 128;
             for (int kb = 0; kb < KB; ++kb) {
-                const long long c0 = clock64();
+                const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
                 ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status, STATUS_TIMEOUT_SMEM_EMPTY);
-                tr_wait += clock64() - c0;
+                if (B200_TRACE(p.trace)) tr_wait += clock64() - c0;
                 if (!ok) break;
-                if (lane == 0) {
+                if (elect_one_sync()) {
                     const uint32_t fb = full_bar + 8 * stage;
                     const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
                     mbar_arrive_expect_tx(fb, C::STAGE_BYTES);
@@ -311,7 +311,6 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
                     if (PHASE == 1) tma_load_2d(base + W_TILE_BYTES, &tmap_w, fb, kb * BK, w_row + 128);
                     tma_load_2d(base + C::W_TILES * W_TILE_BYTES, &tmap_x, fb, kb * BK, u.row0);
                 }
-                __syncwarp();
                 issued |= 1u << stage;
                 issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -331,7 +330,7 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer: lane 0 alone
+        // ------------------------------------------------ MMA issuer: warp-uniform loop, one elected lane issues
         AlphaSched sched(tables, p.NF, p.max_m);
         AlphaUnit u;
         constexpr uint32_t idesc = make_idesc_e4m3_f32(128, NT);
@@ -339,18 +338,18 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         long long tr_te = 0, tr_full = 0, tr_issue = 0;
         bool ok = true;
         while (ok && sched.next(u)) {
-            if (lane == 0) {
-                for (int kb = 0; ok && kb < KB; ++kb) {
-                    const long long c0 = clock64();
-                    ok = mbar_wait_thread(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
-                    if (!ok) break;
-                    const long long c1 = clock64();
-                    ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                    if (!ok) break;
-                    const long long c2 = clock64();
-                    tr_te += c1 - c0;
-                    tr_full += c2 - c1;
-                    tc_fence_after();
+            for (int kb = 0; kb < KB; ++kb) {
+                const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
+                ok = mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                const long long c1 = B200_TRACE(p.trace) ? clock64() : 0;
+                ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                if (!ok) break;
+                const long long c2 = B200_TRACE(p.trace) ? clock64() : 0;
+                tr_te += c1 - c0;
+                tr_full += c2 - c1;
+                tc_fence_after();
+                if (elect_one_sync()) {
                     const uint32_t base = smem_u32(smem + stage * C::STAGE_BYTES);
                     const uint64_t wdesc = make_smem_desc_sw128(base);
                     const uint64_t xdesc = make_smem_desc_sw128(base + C::W_TILES * W_TILE_BYTES);
@@ -365,16 +364,11 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
                     }
                     umma_commit(empty_bar + 8 * stage);
                     umma_commit(tfull_bar + 8 * acc);
-                    tr_issue += clock64() - c2;
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                    if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
                 }
+                if (B200_TRACE(p.trace)) tr_issue += clock64() - c2;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
             }
-            ok = __all_sync(0xffffffffu, ok);
-            stage = __shfl_sync(0xffffffffu, stage, 0);
-            phase = __shfl_sync(0xffffffffu, phase, 0);
-            acc = __shfl_sync(0xffffffffu, acc, 0);
-            acc_phase = __shfl_sync(0xffffffffu, acc_phase, 0);
         }
         if (B200_TRACE(p.trace) && lane == 0) {
             p.trace[blockIdx.x * 8 + 2] = tr_te;

@@ -1303,6 +1303,9 @@ int moe_ep_gate_up_dispatch(const moe_gg_args* a, const moe_ep_send_args* S, voi
     p.num_k_blocks = a->K / 128;
     p.nb128 = (a->N + 127) / 128;
     p.num_m_blocks = (a->M + gg::BM - 1) / gg::BM;
+#ifdef B200MOE_DEV_TRACE
+    if (const char* ev = getenv("B200MOE_GG_TRACE")) p.trace = reinterpret_cast<long long*>(strtoull(ev, nullptr, 10));
+#endif
     if (fused) {
         p.inter = a->N / 2;
         p.num_n_blocks = p.inter / 128;

@@ -72,7 +72,7 @@ constexpr int MASKED_TABLE_INTS = (MAX_MASKED_GROUPS + 1) + MAX_MASKED_GROUPS + 
 constexpr int SMEM_BYTES_MASKED = OFF_PREFIX + MASKED_TABLE_INTS * 4 + 12 + 1024;
 constexpr int SMEM_BYTES_SCATTER = SMEM_BYTES - (A_STAGE_BYTES + B_STAGE_BYTES) + STAGING_BYTES;
 // dispatching variant (contiguous layout: no prefix table): the sending warp's record buffers take that place
-constexpr int SMEM_BYTES_DISPATCH = OFF_PREFIX + EP_SEND_BUFFERS * EP_SEND_RECORD_MAX + 1024;
+constexpr int SMEM_BYTES_DISPATCH = OFF_PREFIX + EP_SEND_BUFFERS * EP_SEND_RECORD_MAX + EP_SEND_RING * 8 + 1024;
 }  // namespace gg
 
 struct GGParams {
@@ -325,7 +325,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     float* sf_ring = reinterpret_cast<float*>(smem + SF_AT);
     int* prefix = reinterpret_cast<int*>(smem + PREFIX_AT);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);       // a value the compiler knows to be warp-uniform
     const int lane = threadIdx.x & 31;
 
     const uint32_t full_bar = smem_u32(bars);
@@ -402,7 +402,7 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status,
                                         STATUS_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
-                    if (lane == 0) {
+                    if (elect_one_sync()) {
                         const uint32_t fb = full_bar + 8 * stage;
                         // masked tiles with few valid rows (decode) fetch a SMALL_A_ROWS-row box of A only: the
                         // other rows of the stage keep stale bytes whose products land in rows nobody stores
@@ -424,7 +424,6 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                             tma_load_2d(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, kb * BK, b_row);
                         }
                     }
-                    __syncwarp();
                     issued |= 1u << stage;
                     issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
@@ -442,9 +441,9 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             }
         } else if (warp == 1) {
             // ------------------------------------------------ MMA issuer
-            // The tile sequence is computed by the whole warp; a tile's K loop is run by lane 0 alone with
-            // single-thread waits: every instruction between "accumulator handed back" and "MMA issued" is a
-            // bubble in the tensor pipe, and a warp-wide vote per wait is such a bubble.
+            // Warp-uniform loop, one elected lane issues: stage, phase and descriptors stay in uniform registers, which
+            // is what the tcgen05 instructions take.  (A single diverged lane needed more issue time per K block
+            // than the tensor pipe needs to multiply it.)
             Scheduler<MASKED> sched(p, prefix, lane);
             Tile tile;
             constexpr uint32_t idesc = make_idesc_e4m3_f32(BM, BN);
@@ -453,13 +452,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             while (ok && sched.next(tile)) {
-                if (lane == 0) {
-                    for (int kb = 0; kb < KB; ++kb) {
-                        ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                        if (!ok) break;
-                        ok = mbar_wait_thread(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
-                        if (!ok) break;
-                        tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    ok = mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (elect_one_sync()) {
                         const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
                         const uint64_t bdesc = bdesc0 + stage * (B_STAGE_BYTES >> 4);
                         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -470,15 +469,10 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                         umma_f8f6f4(tmem_d, adesc + 6, bdesc + 6, idesc, 1u);
                         umma_commit(empty_bar + 8 * stage);   // stage reusable once the MMAs have read it
                         umma_commit(tfull_bar + 8 * acc);     // accumulator of this K block complete
-                        if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
-                        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                     }
+                    if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
+                    if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                stage = __shfl_sync(0xffffffffu, stage, 0);
-                phase = __shfl_sync(0xffffffffu, phase, 0);
-                acc = __shfl_sync(0xffffffffu, acc, 0);
-                acc_phase = __shfl_sync(0xffffffffu, acc_phase, 0);
             }
         } else if (warp == 2) {
             // ------------------------------------------------ scale loader
@@ -525,11 +519,13 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             // This warp owns pairs order[blockIdx.x + i * gridDim.x].  Per pair the token's record -- e4m3 row (bulk
             // load), its scales and the row's return address (written by the lanes) -- is assembled in one of
             // EP_SEND_BUFFERS shared-memory buffers and leaves as ONE bulk store into the owner's receive buffer.
-            // Software pipeline: the load of pair i is in flight while pair i-1 is stored and pair i-2's store
-            // drains.  Lane 0 issues every bulk operation and commits exactly one bulk group per pair, so group
-            // numbers are pair numbers: "at most EP_SEND_BUFFERS - 2 groups pending" means the store that used the
-            // buffer about to be refilled has completed -- the buffer is free and the row can be counted as arrived
-            // (fence + release at system scope; consecutive rows for the same counter are counted together).
+            // Software pipeline: the load of pair i is in flight while pair i-1 is stored.  Lane 0 issues every bulk
+            // operation and commits exactly one bulk group per pair, so group numbers are pair numbers.  A buffer is
+            // refilled as soon as its last store has READ it (wait_group.read); a row is counted as arrived only when
+            // its store is COMPLETE (wait_group), up to EP_SEND_INFLIGHT stores later, so the round trip of a store over
+            // NVLink is not part of a row's issue time.  Counting = one fence at system scope for EP_SEND_BATCH complete
+            // rows, then a relaxed add per counter (a fence per row cost more than sending the row).  A row's scales are
+            // requested one step ahead.
             // Routing data of 32 pairs is fetched at once, one pair per lane.
             const EpSend& ep = p.ep;
             uint8_t* stage_base = smem + PREFIX_AT;
@@ -537,40 +533,56 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
             const int rec = (meta_off + 4 + 15) & ~15;
             const int stride = gridDim.x;
             const int my_rows = ep.n_pairs > (int)blockIdx.x ? (ep.n_pairs - 1 - (int)blockIdx.x) / stride + 1 : 0;
-            int* pend[EP_SEND_BUFFERS];                  // arrival counter of the row last stored from each buffer
-#pragma unroll
-            for (int b = 0; b < EP_SEND_BUFFERS; ++b) pend[b] = nullptr;
-            int* sig_ptr = nullptr;                      // rows completed but not yet counted in
-            int sig_cnt = 0;
-            auto count_in = [&](int* ctr) {              // lane 0 only
-                if (ctr == nullptr) return;
-                if (ctr != sig_ptr && sig_cnt > 0) {
-                    __threadfence_system();
-                    red_release_sys_add(sig_ptr, sig_cnt);
-                    sig_cnt = 0;
+            // arrival counter of every stored row until it has been counted in (lane 0 only)
+            int** ring = reinterpret_cast<int**>(stage_base + EP_SEND_BUFFERS * EP_SEND_RECORD_MAX);
+            int counted = 0;                             // rows [0, counted) have been counted in
+            // Counts rows [counted, upto) in: ONE fence at system scope (the expensive part: it also waits for what
+            // the rest of the SM has in flight), then one relaxed add per run of rows with the same counter.
+            auto count_rows = [&](int upto) {            // lane 0 only
+                if (upto <= counted) return;
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                int* cur = nullptr;
+                int n = 0;
+                for (; counted < upto; ++counted) {
+                    int* c = ring[counted % EP_SEND_RING];
+                    if (c != cur) {
+                        if (cur != nullptr && n > 0) red_relaxed_sys_add(cur, n);
+                        cur = c;
+                        n = 0;
+                    }
+                    ++n;
                 }
-                sig_ptr = ctr;
-                ++sig_cnt;
+                if (cur != nullptr && n > 0) red_relaxed_sys_add(cur, n);
+            };
+            const int nblk = ep.H >> 7;                  // scales per row (at most 64: two per lane)
+            auto load_scales = [&](long long t, float& s0, float& s1) {
+                s0 = lane < nblk ? __ldg(ep.xs + t * ep.xs_r + (long long)lane * ep.xs_b) : 0.0f;
+                s1 = lane + 32 < nblk ? __ldg(ep.xs + t * ep.xs_r + (long long)(lane + 32) * ep.xs_b) : 0.0f;
             };
             bool ok = true;
             // state of the pair whose load is in flight (finished one step later)
             int started = -1;                            // last pair whose record load was issued
             int prev_row = -1, prev_d = 0;
             int* prev_ctr = nullptr;
+            long long tr_load = 0, tr_read = 0, tr_done = 0;
+            const long long tr_s0 = B200_TRACE(p.trace) ? clock64() : 0;
             auto finish = [&](int it_prev) {             // store pair it_prev (its load was started one step earlier)
                 const int b = it_prev % EP_SEND_BUFFERS;
+                const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
                 ok = mbar_wait_warp(send_bar + 8 * b, (uint32_t)(it_prev / EP_SEND_BUFFERS) & 1u, abort_flag, status,
                                     STATUS_TIMEOUT_SMEM_FULL);
+                if (B200_TRACE(p.trace)) tr_load += clock64() - c0;
                 if (lane == 0) {
                     if (ok)
                         asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
                                      ::"l"(ep.a[prev_d] + (long long)prev_row * ep.pitch),
                                        "r"(smem_u32(stage_base + b * EP_SEND_RECORD_MAX)), "r"(rec) : "memory");
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");       // group number = pair number
+                    ring[it_prev % EP_SEND_RING] = ok ? prev_ctr : nullptr;
                 }
-#pragma unroll
-                for (int i = 0; i < EP_SEND_BUFFERS; ++i) if (i == b) pend[i] = ok ? prev_ctr : nullptr;
             };
+            float sc0 = 0.0f, sc1 = 0.0f;
+            bool have_sc = false;
             for (int base = 0; ok && base < my_rows; base += 32) {
                 int m_pr = 0, m_row = -1, m_e = 0;
                 if (base + lane < my_rows) {
@@ -585,18 +597,25 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     const int pr = __shfl_sync(0xffffffffu, m_pr, i);
                     const int row = __shfl_sync(0xffffffffu, m_row, i);
                     const int e = __shfl_sync(0xffffffffu, m_e, i);
+                    const int pr_next = __shfl_sync(0xffffffffu, m_pr, (i + 1) & 31);
                     if (row < 0 || row >= ep.cap_rows) {            // the owner's buffer is too small: give up, report
                         if (lane == 0) atomicOr(status, STATUS_CAPACITY);
                         ok = false;
                         break;
                     }
-                    // (1) buffer b free again; the row it carried EP_SEND_BUFFERS pairs ago has arrived
-                    int* done = nullptr;
-#pragma unroll
-                    for (int k = 0; k < EP_SEND_BUFFERS; ++k) if (k == b) done = pend[k];
+                    // (1) Groups 0 .. it-2 have been committed.  Buffer b was last read by the store of pair it-3: "all
+                    // but the latest group have been read" frees it.  Rows whose stores are COMPLETE (all but the latest
+                    // EP_SEND_INFLIGHT groups) are counted in; this also bounds the stores in flight.
                     if (lane == 0) {
-                        asm volatile("cp.async.bulk.wait_group %0;" ::"n"(EP_SEND_BUFFERS - 2) : "memory");
-                        count_in(done);
+                        const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        const long long c1 = B200_TRACE(p.trace) ? clock64() : 0;
+                        asm volatile("cp.async.bulk.wait_group %0;" ::"n"(EP_SEND_INFLIGHT) : "memory");
+                        if (B200_TRACE(p.trace)) { tr_read += c1 - c0; tr_done += clock64() - c1; }
+                        // complete rows are reported EP_SEND_BATCH at a time (the first few in small batches: the
+                        // receivers' first experts are waiting for them)
+                        const int batch = counted < 2 * EP_SEND_BATCH ? 4 : EP_SEND_BATCH;
+                        if (it - 1 - EP_SEND_INFLIGHT - counted >= batch) count_rows(it - 1 - EP_SEND_INFLIGHT);
                     }
                     __syncwarp();
                     // (2) start assembling pair `it` in buffer b
@@ -608,11 +627,16 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                                      ::"r"(smem_u32(buf)), "l"(ep.x + t * ep.H), "r"(ep.H), "r"(send_bar + 8 * b) : "memory");
                         *reinterpret_cast<int*>(buf + meta_off) = (ep.rank << 24) | pr;     // where the result goes back to
                     }
+                    if (!have_sc) load_scales(t, sc0, sc1);
                     float* sbuf = reinterpret_cast<float*>(buf + ep.H);
-                    for (int bk = lane; bk < (ep.H >> 7); bk += 32) sbuf[bk] = __ldg(ep.xs + t * ep.xs_r + (long long)bk * ep.xs_b);
+                    if (lane < nblk) sbuf[lane] = sc0;
+                    if (lane + 32 < nblk) sbuf[lane + 32] = sc1;
                     fence_proxy_async_smem();
                     __syncwarp();
                     started = it;
+                    // the next pair's scales are requested now and used one step later (their latency overlaps the wait below)
+                    have_sc = i + 1 < cnt;
+                    if (have_sc) load_scales(pr_next / ep.top_k, sc0, sc1);
                     // (3) store the pair started one step ago
                     if (it > 0) finish(it - 1);
                     prev_row = row;
@@ -629,18 +653,19 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 for (int spin = 0; spin < (1 << 20); ++spin)
                     if (mbar_try_wait(bar, par)) break;
             }
-            // drain: every store complete (also on the failure path), then the last rows are counted in
+            if (B200_TRACE(p.trace) && lane == 0) {
+                p.trace[blockIdx.x * 8 + 0] = clock64() - tr_s0;
+                p.trace[blockIdx.x * 8 + 1] = tr_load;
+                p.trace[blockIdx.x * 8 + 2] = tr_read;
+                p.trace[blockIdx.x * 8 + 3] = tr_done;
+                p.trace[blockIdx.x * 8 + 4] = my_rows;
+            }
+            // drain: every store complete (also on the failure path), then the rows not yet counted are counted in
             if (lane == 0) {
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                int first = my_rows > EP_SEND_BUFFERS ? my_rows - EP_SEND_BUFFERS : 0;
-                for (int it = first; it < my_rows; ++it) {          // oldest first: keeps equal counters adjacent
-#pragma unroll
-                    for (int k = 0; k < EP_SEND_BUFFERS; ++k) if (k == it % EP_SEND_BUFFERS) { count_in(pend[k]); pend[k] = nullptr; }
-                }
-                if (sig_cnt > 0) {
-                    __threadfence_system();
-                    red_release_sys_add(sig_ptr, sig_cnt);
-                }
+                const int stored = ok ? my_rows : (started < 0 ? 0 : started);     // pairs whose ring entry was written
+                if (counted < stored - EP_SEND_RING) counted = stored - EP_SEND_RING;
+                count_rows(stored);
             }
         }
     } else {

@@ -608,7 +608,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
     int* prefix = reinterpret_cast<int*>(smem + OFF_PREFIX);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);       // a value the compiler knows to be warp-uniform
     const int lane = threadIdx.x & 31;
     const uint32_t full_bar = smem_u32(bars);
     const uint32_t empty_bar = smem_u32(bars + STAGES);
@@ -656,7 +656,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 for (int kb = 0; kb < KB; ++kb) {
                     ok = mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, status, STATUS_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
-                    if (lane == 0) {
+                    if (elect_one_sync()) {
                         const uint32_t fb = full_bar + 8 * stage;
                         const bool with_sf = (kb & 3) == 0;
                         mbar_arrive_expect_tx(fb, A_STAGE_BYTES + B_STAGE_BYTES + (with_sf ? SFQ_SLOT_BYTES : 0));
@@ -676,7 +676,7 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
             }
         } else if (warp == 1) {
-            // ------------------------------------------------ MMA issuer (lane 0 runs the K loop alone)
+            // ------------------------------------------------ MMA issuer (warp-uniform loop, one elected lane issues)
             Scheduler<MASKED> sched(p, prefix, lane);
             Tile tile;
             uint32_t stage = 0, phase = 0, tile_phase = 0, qcount = 0;
@@ -685,22 +685,23 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem_b));
             const uint32_t idesc0 = make_idesc_mxf8(BM, BN, 0);
             while (ok && sched.next(tile)) {
-                if (lane == 0) {
-                    ok = mbar_wait_thread(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
-                    for (int kb = 0; ok && kb < KB; ++kb) {
-                        ok = mbar_wait_thread(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t sub = kb & 3;
+                ok = mbar_wait_warp(tempty_bar, tile_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb) {
+                    ok = mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, status, STATUS_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sub = kb & 3;
+                    if (elect_one_sync()) {
                         if (sub == 0) {
                             const uint32_t src = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
                             const uint32_t tsf = tmem_base + TMEM_SF_BASE + (qcount & 1) * mx::TMEM_SF_STRIDE;
                             tmem_cp_sf(tsf, make_sf_desc(src));
                             tmem_cp_sf(tsf + 4, make_sf_desc(src + 512));
                             tmem_cp_sf(tsf + 8, make_sf_desc(src + 1024));
-                            ++qcount;
                         }
-                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + ((qcount - 1) & 1) * mx::TMEM_SF_STRIDE;
+                        const uint32_t tsfa = tmem_base + TMEM_SF_BASE + ((qcount - (sub == 0 ? 0u : 1u)) & 1) * mx::TMEM_SF_STRIDE;
                         const uint32_t tsfb = tsfa + 4;
                         const uint32_t idesc = idesc0 | (sub << 4) | (sub << 29);
                         const uint64_t adesc = adesc0 + stage * (A_STAGE_BYTES >> 4);
@@ -711,15 +712,11 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         umma_mxf8(tmem_base, adesc + 6, bdesc + 6, idesc, tsfa, tsfb, 1u);
                         umma_commit(empty_bar + 8 * stage);
                         if (kb == KB - 1) umma_commit(tfull_bar);
-                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
-                    tile_phase ^= 1;
+                    if (sub == 0) ++qcount;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                stage = __shfl_sync(0xffffffffu, stage, 0);
-                phase = __shfl_sync(0xffffffffu, phase, 0);
-                tile_phase = __shfl_sync(0xffffffffu, tile_phase, 0);
-                qcount = __shfl_sync(0xffffffffu, qcount, 0);
+                tile_phase ^= 1;
             }
         }
     } else {

@@ -448,6 +448,9 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     return v;
 }
 
+__device__ __forceinline__ void red_relaxed_sys_add(int* p, int v) {
+    asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
     asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -456,6 +459,9 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
 // the rows that have landed for local expert j in the current forward.
 constexpr int EP_ARRIVE_OFFSET = 64;
 constexpr int EP_SEND_BUFFERS = 3;                 // token records in flight per sending warp
+constexpr int EP_SEND_INFLIGHT = 6;                // bulk stores of a sending warp that may be on their way at once
+constexpr int EP_SEND_BATCH = 24;                  // complete rows reported per system-scope fence
+constexpr int EP_SEND_RING = 64;                   // arrival counters remembered until their rows are counted in (> INFLIGHT + BATCH + 2)
 constexpr int EP_SEND_RECORD_MAX = 7424;           // bytes: H + H/32 + 4 for H <= 7168, rounded up to 128
 
 // What the gate_up GEMM needs to carry the dispatch all-to-all itself (one sending warp per CTA): this rank's
