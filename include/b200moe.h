@@ -421,13 +421,13 @@ int moe_gg_fp8_gate_up_act(const moe_gg_args* args, void* act_q, float* act_scal
  * Values are read once per call, so a change applies from the next call of any thread. */
 #define MOE_OPT_GG_BLOCK_SCALED 0        /* 1 (default): power-of-two scales take the block-scaled-MMA kernels when
                                           * workspace is given; 0: always the promotion kernel */
-#define MOE_OPT_MX_TILE 1                /* block-scaled kernel: AUTO = CTA pairs (256-column tiles) for the contiguous
-                                          * layout, one CTA per tile for the masked layout */
+#define MOE_OPT_MX_TILE 1                /* block-scaled kernel: AUTO = CTA pairs with 240-column tiles and two
+                                          * accumulators for the contiguous layout, one CTA per tile for the masked layout */
 #define MOE_MX_TILE_AUTO 0
-#define MOE_MX_TILE_PAIR 1
+#define MOE_MX_TILE_PAIR 1               /* CTA pairs, 256-column tiles, one accumulator (measurement variant) */
 #define MOE_MX_TILE_SINGLE 2
-#define MOE_MX_TILE_PAIR_240 3           /* CTA pairs, 240-column tiles, two accumulators (measurement variant) */
-#define MOE_MX_TILE_PAIR_224 4           /* CTA pairs, 224-column tiles, two accumulators (measurement variant) */
+#define MOE_MX_TILE_PAIR_240 3           /* CTA pairs, column tiles of at most 240 (balanced in units of 16), two accumulators */
+#define MOE_MX_TILE_PAIR_224 4           /* CTA pairs, column tiles of at most 224, two accumulators (measurement variant) */
 #define MOE_OPT_ALPHA_PATH 2             /* decode-regime layer: AUTO = two CUDA-core kernels up to the route
                                           * threshold, else swapped-operand tensor-core kernels; the others force
                                           * the tensor-core pipeline and choose the tiling of its two projections */

@@ -11,15 +11,17 @@
 //                      in the 32x16-byte tile order tcgen05.cp expects; stores the call's generation number
 //                      into a flag if any scale is not a power of two (then this path stands down and the
 //                      promotion kernel runs instead)
-//   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256 x 256 tiles, 5-stage TMA ring; the scale words of
-//                      four K blocks travel with the first of their stages; the leader issues
-//                      tcgen05.cp (smem -> TMEM) and 16 block-scaled MMAs per group of four K blocks;
-//                      one accumulator drain per tile by the 8 epilogue warps of each CTA.  bf16 rows
-//                      leave through a shared-memory staging area as bulk stores of up to 128 bytes per
-//                      row: with 16-byte stores per lane (32 rows per instruction) the store phase of a
-//                      tile took longer than a K=2048 tile's MMAs and the epilogue, not the tensor
-//                      pipe, set the pace.  Narrower tiles with two accumulators (240 or 224 columns,
-//                      MOE_OPT_MX_TILE) are kept for measurement: with the old epilogue they were slower.
+//   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256-row tiles of at most 240 columns (column tiles balanced in
+//                      units of 16), 5-stage TMA ring; the scale words of four K blocks travel with the first
+//                      of their stages; the leader's issuing warp runs tcgen05.cp (smem -> TMEM) and 16
+//                      block-scaled MMAs per group of four K blocks.  Two accumulators in TMEM: the 8 epilogue
+//                      warps of each CTA drain tile i while tile i+1 is multiplied.  bf16 rows leave through a
+//                      shared-memory staging area as bulk stores of up to 128 bytes per row.  256-column tiles
+//                      with one accumulator (MOE_OPT_MX_TILE) are kept for measurement: the serialised drain
+//                      costs them 4 to 25 % (most on short K).
+//                      The producer and the MMA issuer are warp-uniform loops in which ONE ELECTED LANE issues:
+//                      a single diverged lane has every TMA / tcgen05 operand moved from vector registers and
+//                      needed about 880 cycles per K block where the tensor pipe needs 512.
 #pragma once
 
 #include "pair_common.cuh"
@@ -28,7 +30,7 @@ namespace b200 {
 
 namespace mx {
 constexpr int BM = 128, BK = 128;
-constexpr int BN = 256;                               // column tile of the pair kernel: one accumulator
+constexpr int BN = 256;                               // widest column tile of the pair kernel (one accumulator)
 constexpr int BN_WIDE = 256;
 constexpr int STAGES = 5;
 constexpr int THREADS = 384;
@@ -406,7 +408,11 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             constexpr uint64_t KSTEP = MNMAJOR ? (32 * 128) >> 4 : 2;      // descriptor units (16 bytes) per K = 32
             long long tr_te = 0, tr_full = 0, tr_issue = 0;
             const long long tr_m0 = B200_TRACE(p.trace) ? clock64() : 0;
-            while (ok && sched.next(tile)) {
+            // The schedule of the NEXT tile is worked out right after the first K block of the current one has been
+            // issued: the tensor pipe then has that block's MMAs to run, and the warp is not in the way at the tile border.
+            Tile next_tile;
+            bool have = sched.next(tile), have_next = false;
+            while (ok && have) {
                 // this tile's accumulator must have been drained by both CTAs' epilogues
                 const long long c0 = B200_TRACE(p.trace) ? clock64() : 0;
                 ok = mbar_wait_warp(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_TMEM_EMPTY);
@@ -447,7 +453,10 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (sub == 0) ++qcount;
                     if (B200_TRACE(p.trace)) tr_issue += clock64() - c2;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (kb == 0) have_next = sched.next(next_tile);
                 }
+                tile = next_tile;
+                have = have_next;
                 if (++acc == ACCS) { acc = 0; acc_phase ^= 1; }
             }
             if (B200_TRACE(p.trace) && lane == 0) {
