@@ -212,6 +212,20 @@ int device_info(DeviceInfo** out) {
     return MOE_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream
+// still runs and orders itself with pdl_wait() (ptx.cuh).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <bool MASKED>
 int launch_gg(const moe_gg_args* a, void* stream) {
     if (!a) return fail(MOE_ERR_INVALID, "args is NULL");
@@ -357,7 +371,13 @@ int launch_gg(const moe_gg_args* a, void* stream) {
             const long long tiles = row_blocks256 * pm.num_n_blocks;
             int pairs = (int)(tiles < di->max_pairs ? tiles : di->max_pairs);
             if (pairs < 1) pairs = 1;
-            if (mx_tile == MOE_MX_TILE_PAIR_240)
+            if (mx_tile == MOE_MX_TILE_PAIR_240 && packed_sf) {
+                // packed scales: nothing but the re-tiled scale words comes from the kernel just launched, and no flag
+                pm.pdl_scales = 1;
+                CUDA_TRY(launch_pdl(gg_fp8_mx_kernel<MASKED, false, false, 240>, dim3(2 * pairs), dim3(mx::THREADS),
+                                    (size_t)mx::SMEM_BYTES, st, tmap_a, tmap_b2, tmap_sfa, tmap_sfb, pm,
+                                    (const int*)nullptr, ml.quads, di->status, KgNone{}));
+            } else if (mx_tile == MOE_MX_TILE_PAIR_240)
                 gg_fp8_mx_kernel<MASKED, false, false, 240><<<2 * pairs, mx::THREADS, mx::SMEM_BYTES, st>>>(
                     tmap_a, tmap_b2, tmap_sfa, tmap_sfb, pm, ws.flag, ml.quads, di->status, KgNone{});
             else if (mx_tile == MOE_MX_TILE_PAIR_224)
@@ -499,20 +519,6 @@ int launch_gg_fused_act(const moe_gg_args* a, void* act_q, float* act_scales, in
 constexpr int ALPHA_FUSED_PLAN_MAX_ROUTES = 512;    // measured: the per-warp scan of the route list wins up to a few hundred routes
 constexpr bool ALPHA_SWAP_GATE_UP_DEFAULT = true;
 constexpr bool ALPHA_SWAP_DOWN_DEFAULT = true;
-
-// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream
-// still runs and orders itself with pdl_wait() (ptx.cuh).
-template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
 
 // out[c * R + r] = in[r * C + c] for a byte matrix in [R, C]; 128 x 128 tiles, full 128-byte lines in and out.
 // Phase 1: the tile lands in shared memory as 32-bit words (row pitch 33 words); phase 2: thread (segment, column)

@@ -108,6 +108,10 @@ struct GGParams {
     // block-scaled kernels: column tiles of balanced width, in units of 16 columns: the first nt_rem tiles are
     // nt_base + 1 units wide, the others nt_base (all of them 224 or 240 columns where N allows it)
     int nt_base, nt_rem;
+    // block-scaled pair kernel launched with programmatic stream serialization behind the kernel that re-tiles packed
+    // scales: only the packed scale tiles come from that kernel, so the prologue and the first operand loads run
+    // beside it and the producer waits (griddepcontrol.wait) right before its first scale load
+    int pdl_scales;
 };
 
 // first column and width of column tile nt of a block-scaled kernel

@@ -135,6 +135,7 @@ __global__ void mx_prep_kernel(const float* __restrict__ sfa, long long sfa_sr, 
 __global__ void mx_prep_packed_kernel(const uint32_t* __restrict__ sfa, long long a_sr, long long a_sq,
                                       const uint32_t* __restrict__ sfb, long long b_sg, long long b_sn, long long b_sq,
                                       int rows_total, int N, int G, MxWorkspace ws) {
+    pdl_launch_dependents();      // a GEMM launched with programmatic serialization may start its prologue now
     const int q = blockIdx.y;
     if ((int)blockIdx.x < ws.row_blocks) {
         const int r = blockIdx.x * 128 + threadIdx.x;
@@ -256,7 +257,8 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     constexpr int SF_BASE = ACCS * TN;                // scale columns behind the accumulators
     static_assert(SF_BASE + 2 * TMEM_SF_STRIDE <= TMEM_COLS, "accumulators and scale buffers must fit TMEM");
     using Sched = MxSched<MASKED, KG>;
-    if (*flag == p.mode_gen) return;      // some scale is not a power of two: the promotion kernel handles this call
+    // some scale is not a power of two: the promotion kernel handles this call (packed UE8M0 scales: no flag to read)
+    if (flag != nullptr && *flag == p.mode_gen) return;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;
@@ -346,6 +348,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             Sched sched(p, prefix, lane, rank, kg);
             Tile tile;
             uint32_t stage = 0, phase = 0, qcount = 0;
+            bool pdl_pending = p.pdl_scales != 0;
             long long tr_wait = 0;
             const long long tr_t0 = B200_TRACE(p.trace) ? clock64() : 0;
             bool ok = true;
@@ -378,6 +381,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             tma_load_2d_pair(smem_u32(smem_b + stage * B_STAGE_BYTES), &tmap_b, fb, k0 + kb * BK, b_row);
                         }
                         if (with_sf) {
+                            if (pdl_pending) pdl_wait();          // the packed scale tiles are the predecessor's output
                             const int q = kb >> 2;
                             const uint32_t dst = smem_u32(smem_sfq + (qcount % SFQ_SLOTS) * SFQ_SLOT_BYTES);
                             tma_load_1d_pair(dst, &tmap_sfa, fb, (sfa_chunk + q) * 128);
@@ -385,7 +389,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             tma_load_1d_pair(dst + 1024, &tmap_sfb, fb, (sfb_chunk + 2 * q + 1) * 128);
                         }
                     }
-                    if (with_sf) ++qcount;
+                    if (with_sf) { ++qcount; pdl_pending = false; }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
