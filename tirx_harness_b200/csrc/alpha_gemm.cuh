@@ -405,7 +405,7 @@ alpha_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         const int team = (warp - 4) >> 2;
         AlphaSched sched(tables, p.NF, p.max_m);
         AlphaUnit u;
-        const long long tr_e0 = clock64();
+        const long long tr_e0 = B200_TRACE(p.trace) ? clock64() : 0;
         bool ok = true;
         for (int i = 0; ok && sched.next(u); ++i) {
             if (C::TEAMS > 1 && (i % C::TEAMS) != team) {

@@ -832,15 +832,20 @@ gg_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                 } else {
                     drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
                 }
+                // one 32-byte sector per thread and store where the row is 32-byte aligned, else 16-byte stores
+                const bool wide = (reinterpret_cast<uintptr_t>(drow) & 31u) == 0;
 #pragma unroll
-                for (int j = 0; j < GROUP_COLS; j += 8) {
-                    if (n0 + j + 8 <= p.N) {
-                        uint4 out;
-                        out.x = cvt_bf16x2(accr[j / 2 + 0]);
-                        out.y = cvt_bf16x2(accr[j / 2 + 1]);
-                        out.z = cvt_bf16x2(accr[j / 2 + 2]);
-                        out.w = cvt_bf16x2(accr[j / 2 + 3]);
-                        *reinterpret_cast<uint4*>(drow + j) = out;
+                for (int j = 0; j < GROUP_COLS; j += 16) {
+                    if (n0 + j < p.N) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = cvt_bf16x2(accr[j / 2 + i]);
+                        if (wide && n0 + j + 16 <= p.N) {
+                            st_global_v8(drow + j, o);
+                        } else {
+                            if (n0 + j + 8 <= p.N) *reinterpret_cast<uint4*>(drow + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                            if (n0 + j + 16 <= p.N) *reinterpret_cast<uint4*>(drow + j + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
                     }
                 }
             }

@@ -15,8 +15,11 @@
 //                      units of 16), 5-stage TMA ring; the scale words of four K blocks travel with the first
 //                      of their stages; the leader's issuing warp runs tcgen05.cp (smem -> TMEM) and 16
 //                      block-scaled MMAs per group of four K blocks.  Two accumulators in TMEM: the 8 epilogue
-//                      warps of each CTA drain tile i while tile i+1 is multiplied.  bf16 rows leave through a
-//                      shared-memory staging area as bulk stores of up to 128 bytes per row.  256-column tiles
+//                      warps of each CTA drain tile i while tile i+1 is multiplied (the first warpgroup the tile's
+//                      first 128 columns, the second the rest); every thread stores its row as 32-byte sectors
+//                      (st.global.v8: 32 full sectors per warp instruction, no staging, no wait).  Staging rows in
+//                      shared memory for 128-byte bulk stores took 6400 cycles per tile, most of it waiting for the
+//                      previous store to have read the staging slot: more than a K=2048 tile's MMAs.  256-column tiles
 //                      with one accumulator (MOE_OPT_MX_TILE) are kept for measurement: the serialised drain
 //                      costs them 4 to 25 % (most on short K).
 //                      The producer and the MMA issuer are warp-uniform loops in which ONE ELECTED LANE issues:
@@ -40,13 +43,7 @@ constexpr int SMEM_TILE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int SFQ_SLOTS = 4;                          // ring of scale tiles, one per group of 4 K blocks
 constexpr int SFQ_SLOT_BYTES = 512 + 2 * 512;         // SFA (this CTA's 128 rows) + SFB (the tile's columns, 2 x 128 entries)
 constexpr int OFF_SFQ = SMEM_TILE_BYTES;
-// output staging: per epilogue warp 32 rows of 64 bf16 columns, row pitch 144 bytes (an odd number of 16-byte
-// units: the 8 lanes of a 128-bit store phase hit 8 different bank groups)
-constexpr int STG_COLS = 64;
-constexpr int STG_PITCH = STG_COLS * 2 + 16;
-constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
-constexpr int OFF_STG = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
-constexpr int OFF_BARS = OFF_STG + 8 * STG_WARP_BYTES;
+constexpr int OFF_BARS = OFF_SFQ + SFQ_SLOTS * SFQ_SLOT_BYTES;
 constexpr int OFF_PREFIX = OFF_BARS + 256;
 constexpr int SMEM_BYTES = OFF_PREFIX + (gg::MAX_MASKED_GROUPS + 1) * 4 + 12 + 1024;
 constexpr int TMEM_COLS = 512;
@@ -253,7 +250,6 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // Column tile and accumulators: two 240-column accumulators, or (k-grouped modes) one of 256 columns.
     constexpr int TN = TILE_N ? TILE_N : BN;
     constexpr int ACCS = 2 * TN + 2 * TMEM_SF_STRIDE <= TMEM_COLS ? 2 : 1;
-    constexpr int HALF = TN / 2;                      // columns drained by one epilogue warpgroup
     constexpr int SF_BASE = ACCS * TN;                // scale columns behind the accumulators
     static_assert(SF_BASE + 2 * TMEM_SF_STRIDE <= TMEM_COLS, "accumulators and scale buffers must fit TMEM");
     using Sched = MxSched<MASKED, KG>;
@@ -482,10 +478,12 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         while (ok && sched.next(tile)) {
-            // this warpgroup's columns: the first or the second half of the tile (112, 120 or 128 columns)
-            const int half_w = tile_cols(tile.n_blk) >> 1;
-            const int n0 = tile_col0(tile.n_blk) + half * half_w;
-            const int n_end = n0 + half_w < p.N ? n0 + half_w : p.N;
+            // this warpgroup's columns: the first 128 of the tile, or what follows them (80 to 128 columns): both ranges
+            // start on a multiple of 16 columns, i.e. on a 32-byte boundary of the bf16 output row
+            const int tw = tile_cols(tile.n_blk);
+            const int n0 = tile_col0(tile.n_blk) + half * 128;
+            const int n_tile_end = tile_col0(tile.n_blk) + tw;
+            const int n_end = n_tile_end < p.N ? n_tile_end : p.N;      // first column this thread must not store
             int row = tile.m0 + row_in_tile;
             bool row_valid;
             if (MASKED) row_valid = row_in_tile < tile.rows;
@@ -495,17 +493,12 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = mbar_wait_warp(tfull_bar + 8 * acc, acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TN + half * half_w;
-            // HALF columns = 3 x 32 + (32 | 16 + 8 | 16)
+            // 128 columns from the accumulator's column 128 * half on (for the second warpgroup of a narrower tile the
+            // last of them belong to whatever follows the accumulator in TMEM; they are loaded and never stored)
+            const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * TN + half * 128;
             uint32_t v[4][32];
 #pragma unroll
-            for (int c = 0; c < 3; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
-            if (HALF == 128) {
-                tmem_ld_32x32b_x32(taddr + 96, v[3]);
-            } else {
-                tmem_ld_32x32b_x16(taddr + 96, *reinterpret_cast<uint32_t(*)[16]>(&v[3][0]));
-                if (HALF > 112) tmem_ld_32x32b_x8(taddr + 112, *reinterpret_cast<uint32_t(*)[8]>(&v[3][16]));
-            }
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_wait(v[c]);
             // the accumulator is in registers: the MMAs of the tile after next may overwrite it
@@ -516,7 +509,7 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (row_valid && p.d_f32) {
                 float* drow = reinterpret_cast<float*>(p.d) + (long long)row * p.ldd + n0;
 #pragma unroll
-                for (int j = 0; j < HALF; j += 4) {
+                for (int j = 0; j < 128; j += 4) {
                     if (n0 + j + 4 <= n_end) {
                         float4 o = make_float4(__uint_as_float(v[j / 32][j % 32]), __uint_as_float(v[j / 32][j % 32 + 1]),
                                                __uint_as_float(v[j / 32][j % 32 + 2]), __uint_as_float(v[j / 32][j % 32 + 3]));
@@ -524,36 +517,31 @@ gg_fp8_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         else *reinterpret_cast<float4*>(drow + j) = o;
                     }
                 }
-            } else {
-                // bf16: every thread converts its row in chunks of 64 columns into its own 144-byte slot of the warp's
-                // staging area and sends each chunk with one bulk store (a lane only ever touches its own slot, so
-                // the only ordering needed is "my previous store has read the slot")
-                uint8_t* slot = smem + OFF_STG + ew * STG_WARP_BYTES + lane * STG_PITCH;
+            } else if (row_valid) {
+                // bf16: every thread converts its row 16 columns at a time and stores them as ONE 32-byte sector
+                // (st.global.v8): 32 lanes = 32 full sectors per instruction, nothing to stage and nothing to wait for.
+                // Rows whose address is not 32-byte aligned (odd leading dimensions) take 16-byte stores.
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+                const bool wide = (reinterpret_cast<uintptr_t>(drow) & 31u) == 0;
 #pragma unroll
-                for (int c0 = 0; c0 < HALF; c0 += STG_COLS) {
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                for (int j = 0; j < 128; j += 16) {
+                    if (n0 + j < n_end) {
+                        uint32_t o[8];
 #pragma unroll
-                    for (int j = c0; j < c0 + STG_COLS && j < HALF; j += 8) {
-                        uint4 out;
-                        const uint32_t* s = &v[j / 32][j % 32];
-                        out.x = cvt_bf16x2(pack_f32x2(__uint_as_float(s[0]), __uint_as_float(s[1])));
-                        out.y = cvt_bf16x2(pack_f32x2(__uint_as_float(s[2]), __uint_as_float(s[3])));
-                        out.z = cvt_bf16x2(pack_f32x2(__uint_as_float(s[4]), __uint_as_float(s[5])));
-                        out.w = cvt_bf16x2(pack_f32x2(__uint_as_float(s[6]), __uint_as_float(s[7])));
-                        *reinterpret_cast<uint4*>(slot + (j - c0) * 2) = out;
+                        for (int i = 0; i < 8; ++i) {
+                            const uint32_t* sp = &v[(j + 2 * i) / 32][(j + 2 * i) % 32];
+                            o[i] = cvt_bf16x2(pack_f32x2(__uint_as_float(sp[0]), __uint_as_float(sp[1])));
+                        }
+                        if (wide && n0 + j + 16 <= n_end) {
+                            st_global_v8(drow + j, o);
+                        } else {
+                            if (n0 + j + 8 <= n_end) *reinterpret_cast<uint4*>(drow + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                            if (n0 + j + 16 <= n_end) *reinterpret_cast<uint4*>(drow + j + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
                     }
-                    fence_proxy_async_smem();
-                    int cols = n_end - (n0 + c0);                 // columns of this chunk that exist (multiple of 8)
-                    cols = cols > STG_COLS ? STG_COLS : cols;
-                    if (row_valid && cols > 0)
-                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                                     ::"l"(drow + c0), "r"(smem_u32(slot)), "r"(cols * 2) : "memory");
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
         }
-        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");       // this thread's stores are complete
     }
 
     tc_fence_before();
@@ -774,17 +762,24 @@ gg_fp8_mx1_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                 }
             } else if (row_valid) {
+                // one 32-byte sector per thread and store where the row is 32-byte aligned, else 16-byte stores
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + (long long)row * p.ldd + n0;
+                const bool wide = (reinterpret_cast<uintptr_t>(drow) & 31u) == 0;
 #pragma unroll
-                for (int j = 0; j < 128; j += 8) {
-                    if (n0 + j + 8 <= p.N) {
-                        uint4 out;
-                        const uint32_t* s = &v[j / 32][j % 32];
-                        out.x = cvt_bf16x2(pack_f32x2(__uint_as_float(s[0]), __uint_as_float(s[1])));
-                        out.y = cvt_bf16x2(pack_f32x2(__uint_as_float(s[2]), __uint_as_float(s[3])));
-                        out.z = cvt_bf16x2(pack_f32x2(__uint_as_float(s[4]), __uint_as_float(s[5])));
-                        out.w = cvt_bf16x2(pack_f32x2(__uint_as_float(s[6]), __uint_as_float(s[7])));
-                        *reinterpret_cast<uint4*>(drow + j) = out;
+                for (int j = 0; j < 128; j += 16) {
+                    if (n0 + j < p.N) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const uint32_t* sp = &v[(j + 2 * i) / 32][(j + 2 * i) % 32];
+                            o[i] = cvt_bf16x2(pack_f32x2(__uint_as_float(sp[0]), __uint_as_float(sp[1])));
+                        }
+                        if (wide && n0 + j + 16 <= p.N) {
+                            st_global_v8(drow + j, o);
+                        } else {
+                            if (n0 + j + 8 <= p.N) *reinterpret_cast<uint4*>(drow + j) = make_uint4(o[0], o[1], o[2], o[3]);
+                            if (n0 + j + 16 <= p.N) *reinterpret_cast<uint4*>(drow + j + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
                     }
                 }
             }

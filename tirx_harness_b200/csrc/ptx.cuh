@@ -107,6 +107,12 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, ok);
 }
 
+// one 32-byte sector per thread (256-bit store); the address must be 32-byte aligned
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&o)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+}
+
 // d[0..3] += v, performed by the L2 (no read back into the SM); 16-byte aligned
 __device__ __forceinline__ void red_add_f32x4(float* d, float4 v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
