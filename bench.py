@@ -16,7 +16,10 @@ one GPU, with the four registered grouped-GEMM workloads (`registered`), the reg
 After every timed region, outside it, the outputs the timed calls left behind are checked against the CPU oracle on a
 sample (`parity_check`); a failed check makes the process exit non-zero.  On one GPU the kernels the reference scores
 candidates against -- DeepGEMM's m-grouped FP8 GEMMs and flashinfer's TRT-LLM fused MoE, as installed in this image --
-are timed on the same inputs with the same protocol (`comparators`).
+are timed on the same inputs with the same protocol (`comparators`); every speed-up quoted against them comes from the
+two timed ALTERNATELY, call by call, so that both see the same SM clock of a power-capped GPU.  Every timed region is
+preceded by about 30 ms of untimed calls of the same function (the clock needs that long to come back up after
+host-side work).
 """
 from __future__ import annotations
 
@@ -38,7 +41,7 @@ DATASHEET_HBM_GBS = 8000.0
 
 # DRAM bytes per launch of the dominant kernel (gg_fp8_mx_kernel on the `gemm` workload): dram__bytes_read.sum +
 # dram__bytes_write.sum of the committed ncu capture of that kernel; not re-measured by this script.
-NCU_TRAFFIC_BYTES = {"gemm": 764.7e6}
+NCU_TRAFFIC_BYTES = {"gemm": 809.8e6}
 
 WORKLOADS = {
     # contiguous layout: G groups of m rows (or `sizes` rows each, padded to 128)
