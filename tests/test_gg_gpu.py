@@ -288,6 +288,18 @@ def test_power_of_two_scale_path_equals_promotion_path(gg):
     assert rel_err(d32.cpu().numpy()[valid], _oracle_contig(data, orc.SIM_CHAIN, out_f32=True)[valid]) <= TOL
 
 
+def test_output_rows_off_the_32_byte_grid(gg):
+    """N a multiple of 8 but not of 16: every other bf16 output row starts 16 bytes off a 32-byte boundary, so the
+    epilogues must take their 16-byte stores there (and 32-byte sectors on the aligned rows); last column tile ragged.
+    All three kernels: block-scaled pairs (2^e scales), promotion (other scales), single-CTA block-scaled (masked)."""
+    from tirx_harness_b200.workloads import make_contiguous_case, make_masked_case
+    for law in ("pow2", "uniform_exp"):
+        _check_contig(gg, make_contiguous_case(2, [256, 77], 520, 512, seed=41, law=law))
+        _check_contig(gg, make_contiguous_case(1, [130], 264, 256, seed=42, law=law))
+    _check_masked(gg, make_masked_case(3, 128, 520, 512, seed=43, law="pow2", masked_m=[128, 5, 64]))
+    _check_masked(gg, make_masked_case(2, 64, 264, 256, seed=44, law="uniform_exp", masked_m=[64, 33]))
+
+
 def test_masked_power_of_two_path(gg):
     from tirx_harness_b200.workloads import make_masked_case
     _check_masked(gg, make_masked_case(5, 256, 512, 1024, seed=31, law="pow2", masked_m=[256, 0, 129, 77, 255]))
