@@ -12,7 +12,7 @@
 //                      into a flag if any scale is not a power of two (then this path stands down and the
 //                      promotion kernel runs instead)
 //   gg_fp8_mx_kernel   CTA pairs (cta_group::2), 256-row tiles of at most 240 columns (column tiles balanced in
-//                      units of 16), 5-stage TMA ring; the scale words of four K blocks travel with the first
+//                      units of 16), 6-stage TMA ring; the scale words of four K blocks travel with the first
 //                      of their stages; the leader's issuing warp runs tcgen05.cp (smem -> TMEM) and 16
 //                      block-scaled MMAs per group of four K blocks.  Two accumulators in TMEM: the 8 epilogue
 //                      warps of each CTA drain tile i while tile i+1 is multiplied (the first warpgroup the tile's
@@ -35,7 +35,7 @@ namespace mx {
 constexpr int BM = 128, BK = 128;
 constexpr int BN = 256;                               // widest column tile of the pair kernel (one accumulator)
 constexpr int BN_WIDE = 256;
-constexpr int STAGES = 5;
+constexpr int STAGES = 6;
 constexpr int THREADS = 384;
 constexpr int A_STAGE_BYTES = BM * BK;
 constexpr int B_STAGE_BYTES = (BN_WIDE / 2) * BK;     // sized for the wider tile; the 240-column tile uses 120 rows of it
