@@ -75,6 +75,10 @@ extern "C" {
  *   scatter_meta_stride  distance in int32 elements between the entries of consecutive rows (0 = 1: a dense array).
  *           The dispatching GEMM (moe_ep_gate_up_dispatch) leaves every row's return address inside its record, at
  *           byte H + H/32: pass that word of the first record with a stride of pitch / 4.
+ *   mx_tile  tiling of the block-scaled kernels for THIS call (a MOE_MX_TILE_* value); 0 = the process-wide option
+ *           MOE_OPT_MX_TILE.  (Measured on a Zipf-distributed batch of 64 groups, where CTA pairs multiply 15 % more
+ *           rows than 128-row tiles would: the pairs are still 3 to 9 % faster, so the default does not look at the
+ *           group sizes.)
  * Requirements: K % 128 == 0, N % 8 == 0, a/b 16-byte aligned, d 16-byte aligned, ldd % 8 == 0.
  */
 typedef struct moe_gg_args {
@@ -100,6 +104,7 @@ typedef struct moe_gg_args {
     int64_t ldb;
     int32_t accumulate;
     int64_t scatter_meta_stride;
+    int32_t mx_tile;
 } moe_gg_args;
 
 /* Scratch for the power-of-two-scale path (rows_total = M contiguous, G*M masked).  With

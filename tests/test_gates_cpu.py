@@ -72,3 +72,4 @@ def test_calc_diff_equals_the_installed_deepgemm_helper():
     y = _bf16(x + 1e-3 * rng.standard_normal(x.shape))
     want = float(numeric.calc_diff(torch.from_numpy(x), torch.from_numpy(y)))
     assert calc_diff(x, y) == pytest.approx(want, rel=1e-9, abs=1e-15)
+

@@ -26,6 +26,7 @@ class GGArgs(_c.Structure):
         ("scatter_meta", _c.c_void_p), ("scatter_base", _c.c_void_p * 8),
         ("sf_format", _c.c_int32), ("sfb_stride", _c.c_int64 * 3), ("lda", _c.c_int64),
         ("ldb", _c.c_int64), ("accumulate", _c.c_int32), ("scatter_meta_stride", _c.c_int64),
+        ("mx_tile", _c.c_int32),
     ]
 
 

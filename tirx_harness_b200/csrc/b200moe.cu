@@ -321,7 +321,8 @@ int launch_gg(const moe_gg_args* a, void* stream) {
         // layout, where a pair multiplies up to 255 empty rows per group; among the pair tiles 240 columns with two
         // accumulators (the drain of tile i under the MMAs of tile i+1) beat 256 columns with one on every shape
         // measured against the same comparator, by 4 to 25 %, most on short K
-        int mx_tile = opt(MOE_OPT_MX_TILE);
+        int mx_tile = a->mx_tile != 0 ? a->mx_tile : opt(MOE_OPT_MX_TILE);     // per call, else process-wide
+        if (mx_tile < MOE_MX_TILE_AUTO || mx_tile > MOE_MX_TILE_PAIR_224) return fail(MOE_ERR_INVALID, "mx_tile out of range");
         if (mx_tile == MOE_MX_TILE_AUTO) mx_tile = MASKED ? MOE_MX_TILE_SINGLE : MOE_MX_TILE_PAIR_240;
         const bool mx_single = mx_tile == MOE_MX_TILE_SINGLE;
         // column tiles: 256 wide for the single-CTA kernel; for the pair kernel at most 240 wide and balanced in

@@ -47,7 +47,7 @@ class _BoundGG:
     """A validated argument block; ``__call__`` launches on the current stream of the tensors' device."""
 
     def __init__(self, fn_name, a, b, sfa, sfa_strides, sfb, layout, d, G, M, N, K, rows_used=None,
-                 workspace=True, scatter=None):
+                 workspace=True, scatter=None, mx_tile=0):
         rows_total = M if fn_name.endswith("contiguous") else G * M
         ws_bytes = _lib.lib().moe_gg_workspace_bytes(ctypes.c_int32(G), ctypes.c_int64(rows_total), ctypes.c_int32(N),
                                                     ctypes.c_int32(K)) if workspace else 0
@@ -61,7 +61,7 @@ class _BoundGG:
             sfb=_ptr(sfb), layout=_ptr(layout), d=_ptr(d), ldd=d.stride(-2), G=G, M=M, N=N, K=K,
             d_dtype=1 if d.dtype == torch.float32 else 0, lda=a.stride(-2) if a.dim() == 2 else 0,
             rows_used=_ptr(rows_used) if rows_used is not None else None,
-            workspace=_ptr(self._ws) if self._ws is not None else None, workspace_bytes=ws_bytes)
+            workspace=_ptr(self._ws) if self._ws is not None else None, workspace_bytes=ws_bytes, mx_tile=mx_tile)
         if scatter is not None:          # (meta int32[M] tensor, list of up to 8 base addresses)
             meta, bases = scatter
             self._keep = self._keep + (meta,)
@@ -79,10 +79,12 @@ class _BoundGG:
         return self.out
 
 
-def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace=True, scatter=None) -> _BoundGG:
+def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace=True, scatter=None,
+                    mx_tile: int = 0) -> _BoundGG:
     """a fp8[M,K] (row pitch may exceed K), sfa f32[M,K/128] (any strides), b fp8[G,N,K], sfb
     f32[G,ceil(N/128),K/128], d bf16[M,N], grouped_layout int32[M] (group id per row, negative = padding row);
-    rows_used: optional int32[1] device tensor with the number of leading rows in use."""
+    rows_used: optional int32[1] device tensor with the number of leading rows in use; mx_tile: a
+    ``_lib.MX_TILE_*`` value for this binding (0 = the process-wide option)."""
     _check_fp8(a, "a", allow_pitch=True); _check_fp8(b, "b")
     M, K = a.shape
     G, N, Kb = b.shape
@@ -101,7 +103,7 @@ def bind_contiguous(a, sfa, b, sfb, d, grouped_layout, rows_used=None, workspace
     if rows_used is not None and (rows_used.dtype != torch.int32 or not rows_used.is_cuda):
         raise ValueError("rows_used must be an int32 CUDA tensor")
     return _BoundGG("moe_gg_fp8_contiguous", a, b, sfa, strides, sfb, grouped_layout, d, G, M, N, K, rows_used,
-                    workspace and scatter is None, scatter)
+                    workspace and scatter is None, scatter, mx_tile)
 
 
 def bind_masked(a, sfa, b, sfb, d, masked_m, workspace=True) -> _BoundGG:
@@ -166,7 +168,7 @@ def bind_gate_up_act(a, sfa, b, sfb, act_q, act_s, grouped_layout, gate_first=Fa
     return _BoundGateUpAct(a, sfa, strides, b, sfb, act_q, act_s, grouped_layout, gate_first, rows_used, G, M, N, K)
 
 
-def bind_contiguous_packed(a, sfa_words, b, sfb_words, d, grouped_layout) -> _BoundGG:
+def bind_contiguous_packed(a, sfa_words, b, sfb_words, d, grouped_layout, mx_tile: int = 0) -> _BoundGG:
     """The registered workload's own scale format: UE8M0 bytes packed four per int32.
     sfa_words int32 [M, ceil(K/512)] (any strides; DeepGEMM stores it MN-major), sfb_words int32
     [G, N, ceil(K/512)] (any strides).  Always runs the block-scaled-MMA kernel."""
@@ -181,7 +183,7 @@ def bind_contiguous_packed(a, sfa_words, b, sfb_words, d, grouped_layout) -> _Bo
     if d.dtype != torch.bfloat16 and d.dtype != torch.float32 or tuple(d.shape) != (M, N):
         raise ValueError(f"d must be [{M}, {N}] bf16 or f32")
     bound = _BoundGG("moe_gg_fp8_contiguous", a, b, sfa_words, (sfa_words.stride(0), sfa_words.stride(1)), sfb_words,
-                     grouped_layout, d, G, M, N, K, None, True)
+                     grouped_layout, d, G, M, N, K, None, True, None, mx_tile)
     bound._args.sf_format = 1
     for i in range(3):
         bound._args.sfb_stride[i] = sfb_words.stride(i)
