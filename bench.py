@@ -41,7 +41,7 @@ DATASHEET_HBM_GBS = 8000.0
 
 # DRAM bytes per launch of the dominant kernel (gg_fp8_mx_kernel on the `gemm` workload): dram__bytes_read.sum +
 # dram__bytes_write.sum of the committed ncu capture of that kernel; not re-measured by this script.
-NCU_TRAFFIC_BYTES = {"gemm": 809.8e6}
+NCU_TRAFFIC_BYTES = {"gemm": 781.5e6}
 
 WORKLOADS = {
     # contiguous layout: G groups of m rows (or `sizes` rows each, padded to 128)

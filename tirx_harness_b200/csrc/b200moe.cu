@@ -334,22 +334,6 @@ int launch_gg(const moe_gg_args* a, void* stream) {
             const int tn = mx_tile == MOE_MX_TILE_PAIR_240 ? 240 : (mx_tile == MOE_MX_TILE_PAIR_224 ? 224 : mx::BN);
             const int units = (a->N + 15) / 16;
             ws.n_tiles = (a->N + tn - 1) / tn;
-            if (tn == 240 && !MASKED && di->max_pairs > 0) {
-                // wave quantisation: one or two more (narrower) column tiles can fill the last wave of the persistent
-                // pairs, e.g. 128 row blocks x 18 tiles = 31.1 waves of 74 pairs, x 19 tiles = 32.9.  Cost = waves x
-                // average tile width; more tiles only where that is at least 1.5 % cheaper.  (The scale workspace
-                // holds ceil(N / 224) column tiles.)
-                const long long rb = (a->M + 255) / 256;
-                const int nt_max = (a->N + 223) / 224;
-                double best_cost = 0.0;
-                int best = ws.n_tiles;
-                for (int nt = ws.n_tiles; nt <= nt_max; ++nt) {
-                    const long long waves = (rb * nt + di->max_pairs - 1) / di->max_pairs;
-                    const double cost = (double)waves * units / nt;
-                    if (nt == ws.n_tiles || cost < best_cost * 0.985) { best_cost = cost; best = nt; }
-                }
-                ws.n_tiles = best;
-            }
             ws.nt_base = units / ws.n_tiles; ws.nt_rem = units % ws.n_tiles;
         }
         cudaStream_t st = static_cast<cudaStream_t>(stream);
